@@ -1,0 +1,140 @@
+// Host launcher of the tcgen05 bf16 GEMM: builds (and caches) the TMA tensor maps, picks tile
+// width / pipeline depth / split-K cluster size, and launches the kernel from gemm_tcgen05.cuh.
+#include "gemm.h"
+#include "gemm_tcgen05.cuh"
+#include "tma_desc.h"
+
+#include <atomic>
+#include <cstdio>
+
+namespace ccl {
+
+namespace {
+std::atomic<uint64_t> g_launches{0};
+}
+uint64_t launch_count() { return g_launches.load(); }
+void launch_count_add(uint64_t n) { g_launches.fetch_add(n); }
+void launch_count_reset() { g_launches.store(0); }
+
+namespace gemm {
+
+template <int BN, bool DUAL, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                const Params p) {
+  gemm_tile_body<BN, DUAL>(&tma_a, &tma_b, p, StoreEpilogue<OutT>{});
+}
+
+template <int BN, bool DUAL, typename OutT>
+cudaError_t launch(const GemmDesc& d, int splitk, cudaStream_t stream) {
+  const int m_tiles = (int)((d.M + kBM - 1) / kBM);
+  const int n_tiles = (int)((d.N + BN - 1) / BN);
+  const int k_iters = (int)((d.K + kBK - 1) / kBK);
+
+  constexpr size_t kSmemBudget = 200 * 1024;
+  // split-K: bounded by the cluster limit, the reduce buffer and the amount of K work
+  const int max_split = DUAL ? 4 : 8;
+  if (splitk > max_split) splitk = max_split;
+  while (splitk > 1 && (smem_bytes<BN, DUAL>(3, splitk) > kSmemBudget || k_iters / splitk < 2))
+    --splitk;
+  if (splitk < 1) splitk = 1;
+  int stages = kMaxStages;
+  while (stages > 2 && smem_bytes<BN, DUAL>(stages, splitk) > kSmemBudget) --stages;
+  const int per = (k_iters + splitk - 1) / splitk;
+  if (stages > per && per >= 2) stages = per;
+  const size_t smem = smem_bytes<BN, DUAL>(stages, splitk);
+
+  CUtensorMap ta, tb;
+  const int64_t a_rows = DUAL ? (d.dual_off + d.M) : d.M;
+  if (!tma::make_2d_bf16(&ta, d.a, (uint64_t)a_rows, (uint64_t)d.K, (uint64_t)d.lda, kBM, kBK))
+    return cudaErrorInvalidValue;
+  if (!tma::make_2d_bf16(&tb, d.b, (uint64_t)d.N, (uint64_t)d.K, (uint64_t)d.ldb, BN, kBK))
+    return cudaErrorInvalidValue;
+
+  Params p;
+  p.M = (int)d.M;
+  p.N = (int)d.N;
+  p.K = (int)d.K;
+  p.out = d.out;
+  p.ldo = d.ldo;
+  p.trans_out = d.trans_out;
+  p.dual_off = (int)d.dual_off;
+  p.stages = stages;
+  p.splitk = splitk;
+  p.status = d.status;
+
+  auto kern = gemm_kernel<BN, DUAL, OutT>;
+  static thread_local size_t configured = 0;
+  if (configured < smem) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget + 2048);
+    if (e != cudaSuccess) return e;
+    configured = kSmemBudget + 2048;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(m_tiles, n_tiles, splitk);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = splitk;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
+  if (e == cudaSuccess) g_launches.fetch_add(1);
+  return e;
+}
+
+template <int BN>
+cudaError_t dispatch_bn(const GemmDesc& d, int splitk, cudaStream_t s) {
+  if (d.dual_off > 0) {
+    if constexpr (BN <= 128) {
+      return d.out_fp32 ? launch<BN, true, float>(d, splitk, s)
+                        : launch<BN, true, __nv_bfloat16>(d, splitk, s);
+    } else {
+      return cudaErrorInvalidValue;
+    }
+  }
+  return d.out_fp32 ? launch<BN, false, float>(d, splitk, s)
+                    : launch<BN, false, __nv_bfloat16>(d, splitk, s);
+}
+
+}  // namespace gemm
+
+cudaError_t gemm_bf16_tn(const GemmDesc& d, cudaStream_t stream) {
+  if (!d.a || !d.b || !d.out || d.M <= 0 || d.N <= 0 || d.K <= 0) return cudaErrorInvalidValue;
+  if ((d.lda % 8) || (d.ldb % 8)) return cudaErrorInvalidValue;  // TMA strides: 16-byte multiples
+  if ((reinterpret_cast<uintptr_t>(d.a) & 15) || (reinterpret_cast<uintptr_t>(d.b) & 15))
+    return cudaErrorInvalidValue;
+  int bn = d.bn;
+  if (bn == 0) {
+    if (d.N <= 16) bn = 16;
+    else if (d.N <= 32) bn = 32;
+    else if (d.N <= 64) bn = 64;
+    else if (d.N <= 128 || d.dual_off > 0) bn = 128;
+    else bn = 256;
+  }
+  int splitk = d.splitk;
+  if (splitk == 0) {
+    const int64_t tiles = ((d.M + 127) / 128) * ((d.N + bn - 1) / bn);
+    int sm = 148;
+    splitk = 1;
+    if (tiles < sm) {
+      splitk = (int)((sm + tiles - 1) / tiles);
+      if (splitk > 8) splitk = 8;
+      if (bn > 64) splitk = 1;  // the DSMEM reduce buffer only pays off for narrow tiles
+    }
+  }
+  switch (bn) {
+    case 16: return gemm::dispatch_bn<16>(d, splitk, stream);
+    case 32: return gemm::dispatch_bn<32>(d, splitk, stream);
+    case 64: return gemm::dispatch_bn<64>(d, splitk, stream);
+    case 128: return gemm::dispatch_bn<128>(d, splitk, stream);
+    case 256: return gemm::dispatch_bn<256>(d, splitk, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace ccl

@@ -1,0 +1,32 @@
+// Host interface of the tcgen05 bf16 GEMM family (no torch dependency).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ccl {
+
+// D[M, N] = A[M, K] · B[N, K]^T with bf16 operands (K contiguous) and fp32 accumulation.
+// A occupies the 128-row UMMA M side, B the UMMA N side (tile width `bn`, a multiple of 16).
+struct GemmDesc {
+  const void* a = nullptr;  // [M, K], row stride lda elements
+  const void* b = nullptr;  // [N, K], row stride ldb elements
+  void* out = nullptr;      // bf16 (out_fp32 = 0) or fp32 (out_fp32 = 1)
+  int64_t M = 0, N = 0, K = 0;
+  int64_t lda = 0, ldb = 0, ldo = 0;
+  int out_fp32 = 0;
+  int trans_out = 0;   // 1: out[n*ldo + m] (swap-AB decode: weights are A, activations are B)
+  int64_t dual_off = 0;  // >0: SwiGLU mode, out = silu(A[m]·B) * (A[m+dual_off]·B); M counts gate rows
+  int splitk = 0;      // 0 = choose automatically
+  int bn = 0;          // 0 = choose automatically from N
+  int* status = nullptr;  // optional device error word
+};
+
+// Launches on `stream`; returns cudaSuccess or the launch / argument error.
+cudaError_t gemm_bf16_tn(const GemmDesc& d, cudaStream_t stream);
+
+// Number of kernels of this library launched since the last call to reset (per process).
+uint64_t launch_count();
+void launch_count_add(uint64_t n);
+void launch_count_reset();
+
+}  // namespace ccl

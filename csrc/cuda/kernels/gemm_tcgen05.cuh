@@ -1,0 +1,321 @@
+// Device side of the bf16 "TN" GEMM on 5th-generation tensor cores:
+//
+//     D[M, N] = A[M, K] · B[N, K]^T          (both operands K-contiguous, fp32 accumulation)
+//
+// One CTA computes one 128 x BN output tile. TMA (cp.async.bulk.tensor, 128-byte swizzle, never
+// multicast) streams 128x64 A tiles and BNx64 B tiles into a multi-stage shared-memory ring;
+// one elected thread issues tcgen05.mma (UMMA 128 x BN x 16) with the accumulator in TMEM; four
+// epilogue warps read the accumulator back with tcgen05.ld. Warp roles:
+//
+//     warp 0      TMA producer (one elected lane)
+//     warp 1      TMEM allocator + MMA issuer (one elected lane)
+//     warps 2..5  epilogue; warp w owns TMEM lanes 32*(w%4) .. 32*(w%4)+31
+//
+// Optional features, all used by the tensor-parallel decode / training paths:
+//   * split-K across a thread-block cluster (cluster dim z): non-leader CTAs push their fp32
+//     partial tiles into the leader's shared memory over DSMEM, the leader sums in a fixed
+//     order (deterministic) and runs the epilogue once;
+//   * "dual A": a second A tile `dual_off` rows further down shares the same B tile and gets
+//     its own TMEM columns; the epilogue then emits silu(acc0) * acc1 (SwiGLU with the gate and
+//     up projections stacked in one weight matrix);
+//   * transposed output for the swap-AB decode trick (weights on the 128-row UMMA M side, the
+//     few activation rows on the N side), row-major output otherwise;
+//   * `EpiFn`: a functor invoked per 16-column accumulator chunk instead of the plain store —
+//     this is the hook the GEMM->reduce-scatter kernel uses to scatter tiles into peer memory.
+//
+// All waits are bounded; on expiry the kernel records an error code in `status` and drains.
+#pragma once
+#include <cuda.h>
+#include "ptx.cuh"
+
+namespace ccl {
+namespace gemm {
+
+constexpr int kBM = 128;         // UMMA M
+constexpr int kBK = 64;          // 64 bf16 = one 128-byte swizzle row
+constexpr int kMaxStages = 12;
+constexpr int kThreads = 192;
+
+struct Params {
+  int M, N, K;          // logical problem (A rows, B rows, reduction)
+  void* out;            // bf16 or fp32
+  long long ldo;        // leading dimension of out, in elements
+  int trans_out;        // 0: out[m*ldo + n]; 1: out[n*ldo + m]
+  int dual_off;         // row offset of the second A operand (DUAL only)
+  int stages;           // pipeline depth
+  int splitk;           // cluster size along z (1 = no split)
+  int* status;          // device-visible error word (0 = ok)
+};
+
+struct __align__(8) Barriers {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t accum;
+  uint32_t tmem_base;
+  uint32_t failed;
+};
+
+template <typename OutT>
+__device__ __forceinline__ void store_elem(OutT* p, float v);
+template <>
+__device__ __forceinline__ void store_elem<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_elem<__nv_bfloat16>(__nv_bfloat16* p, float v) {
+  *p = __float2bfloat16(v);
+}
+
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+// Default epilogue: plain (optionally transposed) store with tail guards.
+template <typename OutT>
+struct StoreEpilogue {
+  __device__ __forceinline__ void operator()(const Params& p, int m, int n0, const float (&v)[16]) const {
+    if (m >= p.M) return;
+    OutT* out = reinterpret_cast<OutT*>(p.out);
+    if (p.trans_out) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (n0 + j < p.N) store_elem<OutT>(out + (long long)(n0 + j) * p.ldo + m, v[j]);
+      }
+    } else {
+      OutT* row = out + (long long)m * p.ldo + n0;
+      if (n0 + 16 <= p.N && ((reinterpret_cast<uintptr_t>(row) & 15) == 0)) {
+        if constexpr (sizeof(OutT) == 2) {
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+            w[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          reinterpret_cast<uint4*>(row)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+          reinterpret_cast<uint4*>(row)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            reinterpret_cast<float4*>(row)[j] =
+                make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (n0 + j < p.N) store_elem<OutT>(row + j, v[j]);
+      }
+    }
+  }
+};
+
+template <int BN, bool DUAL>
+__host__ __device__ constexpr int stage_bytes() {
+  return kBM * kBK * 2 * (DUAL ? 2 : 1) + BN * kBK * 2;
+}
+template <int BN, bool DUAL>
+__host__ __device__ constexpr int acc_cols() { return BN * (DUAL ? 2 : 1); }
+template <int BN, bool DUAL>
+__host__ __device__ constexpr int tmem_cols() {
+  int c = acc_cols<BN, DUAL>();
+  int a = 32;
+  while (a < c) a <<= 1;
+  return a;
+}
+// Dynamic shared memory: [<=1023 B alignment slack][stages][split-K reduce buffer][barriers]
+template <int BN, bool DUAL>
+__host__ __device__ constexpr size_t smem_bytes(int stages, int splitk) {
+  return 1024 + (size_t)stages * stage_bytes<BN, DUAL>() +
+         (size_t)(splitk > 1 ? (splitk - 1) : 0) * kBM * acc_cols<BN, DUAL>() * 4 + sizeof(Barriers);
+}
+
+template <int BN, bool DUAL, typename EpiFn>
+__device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
+                                               const Params& p, const EpiFn& epi) {
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA M=128 needs N % 16 == 0");
+  static_assert(acc_cols<BN, DUAL>() <= 512, "TMEM has 512 columns");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  constexpr int kStage = stage_bytes<BN, DUAL>();
+  constexpr int kABytes = kBM * kBK * 2;
+  constexpr int kAcc = acc_cols<BN, DUAL>();
+  constexpr uint32_t kTmemCols = tmem_cols<BN, DUAL>();
+  const int stages = p.stages;
+  float* red = reinterpret_cast<float*>(smem + (size_t)stages * kStage);
+  const int nred = p.splitk > 1 ? p.splitk - 1 : 0;
+  Barriers* bars = reinterpret_cast<Barriers*>(reinterpret_cast<uint8_t*>(red) +
+                                               (size_t)nred * kBM * kAcc * 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * kBM;
+  const int n0 = blockIdx.y * BN;
+  const uint32_t crank = p.splitk > 1 ? ptx::cluster_ctarank() : 0;
+
+  // K range of this split.
+  const int k_iters_total = (p.K + kBK - 1) / kBK;
+  const int per = (k_iters_total + p.splitk - 1) / p.splitk;
+  const int it_begin = (int)crank * per;
+  int it_end = it_begin + per;
+  if (it_end > k_iters_total) it_end = k_iters_total;
+  const int n_iters = it_end > it_begin ? it_end - it_begin : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(&bars->full[s], 1);
+      ptx::mbar_init(&bars->empty[s], 1);
+    }
+    ptx::mbar_init(&bars->accum, 1);
+    bars->failed = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&bars->tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      ptx::prefetch_tmap(tma_a);
+      ptx::prefetch_tmap(tma_b);
+      for (int i = 0; i < n_iters; ++i) {
+        const int s = i % stages;
+        const uint32_t ph = (i / stages) & 1;
+        if (!ptx::mbar_wait(&bars->empty[s], ph ^ 1)) {
+          bars->failed = 1;
+          if (p.status) atomicExch(p.status, 101);
+          break;
+        }
+        uint8_t* st = smem + (size_t)s * kStage;
+        ptx::mbar_arrive_expect_tx(&bars->full[s], kStage);
+        const int kx = (it_begin + i) * kBK;
+        ptx::tma_load_2d(st, tma_a, &bars->full[s], kx, m0);
+        if (DUAL) ptx::tma_load_2d(st + kABytes, tma_a, &bars->full[s], kx, m0 + p.dual_off);
+        ptx::tma_load_2d(st + kABytes * (DUAL ? 2 : 1), tma_b, &bars->full[s], kx, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::make_idesc_bf16(kBM, BN);
+      bool ok = true;
+      for (int i = 0; i < n_iters && ok; ++i) {
+        const int s = i % stages;
+        const uint32_t ph = (i / stages) & 1;
+        if (!ptx::mbar_wait(&bars->full[s], ph)) {
+          bars->failed = 1;
+          if (p.status) atomicExch(p.status, 102);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t a_addr = ptx::smem_u32(smem + (size_t)s * kStage);
+        const uint32_t b_addr = a_addr + kABytes * (DUAL ? 2 : 1);
+#pragma unroll
+        for (int k = 0; k < kBK / 16; ++k) {
+          const uint64_t db = ptx::make_desc_sw128(b_addr + k * 32);
+          const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+          ptx::umma_bf16_ss(tmem_base, ptx::make_desc_sw128(a_addr + k * 32), db, idesc, acc);
+          if (DUAL)
+            ptx::umma_bf16_ss(tmem_base + BN, ptx::make_desc_sw128(a_addr + kABytes + k * 32), db,
+                              idesc, acc);
+        }
+        ptx::umma_commit(&bars->empty[s]);  // frees the stage once these MMAs have read it
+      }
+      ptx::umma_commit(&bars->accum);
+    }
+  } else {
+    // ---- epilogue warps -------------------------------------------------------------------
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    bool ok = ptx::mbar_wait(&bars->accum, 0);
+    if (!ok) {
+      bars->failed = 1;
+      if (p.status) atomicExch(p.status, 103);
+    }
+    ptx::tc_fence_after();
+    if (p.splitk > 1 && crank != 0) {
+      // push the partial tile into the leader's reduce buffer: [crank-1][col/4][row] float4
+      const uint32_t base = ptx::mapa(ptx::smem_u32(red), 0) + (crank - 1) * (kBM * kAcc * 4);
+      for (int c = 0; c < kAcc; c += 16) {
+        uint32_t r[16];
+        if (n_iters > 0 && ok) {
+          ptx::tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + c, r);
+          ptx::tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = 0;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float4 v = make_float4(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
+                                 __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
+          ptx::st_cluster_v4(base + (((c >> 2) + g) * kBM + row) * 16, v);
+        }
+      }
+    }
+  }
+
+  if (p.splitk > 1) {
+    ptx::tc_fence_before();
+    __syncwarp();
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+    ptx::tc_fence_after();
+  }
+
+  if (warp >= 2 && crank == 0) {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const bool ok = (bars->failed == 0);
+    for (int c = 0; c < BN; c += 16) {
+      float v[16], u[16];
+      {
+        uint32_t r[16];
+        if (n_iters > 0 && ok) {
+          ptx::tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + c, r);
+          ptx::tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = 0;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+        if (DUAL) {
+          if (n_iters > 0 && ok) {
+            ptx::tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + BN + c, r);
+            ptx::tmem_ld_wait();
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) u[j] = __uint_as_float(r[j]);
+        }
+      }
+      for (int s = 0; s < nred; ++s) {
+        const float4* pr = reinterpret_cast<const float4*>(red + (size_t)s * kBM * kAcc);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float4 t = pr[((c >> 2) + g) * kBM + row];
+          v[4 * g] += t.x; v[4 * g + 1] += t.y; v[4 * g + 2] += t.z; v[4 * g + 3] += t.w;
+        }
+        if (DUAL) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float4 t = pr[(((BN + c) >> 2) + g) * kBM + row];
+            u[4 * g] += t.x; u[4 * g + 1] += t.y; u[4 * g + 2] += t.z; u[4 * g + 3] += t.w;
+          }
+        }
+      }
+      if (DUAL) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = silu(v[j]) * u[j];
+      }
+      if (ok) epi(p, m0 + row, n0 + c, v);
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) ptx::tmem_dealloc(tmem_base, kTmemCols);
+}
+
+}  // namespace gemm
+}  // namespace ccl

@@ -1,0 +1,66 @@
+"""Numerics of the tcgen05 bf16 GEMM against a plain fp32 PyTorch reference."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _C():
+    import torch_ccl_b200._C as C
+
+    return C
+
+
+def _ref(a, b):
+    return a.float() @ b.float().t()
+
+
+def _check(out, ref, k):
+    tol = 2e-2 * (k ** 0.5) * 0.05 + 1e-2
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err <= 1e-2 * scale + tol * 0.1, f"max err {err} (scale {scale})"
+
+
+@pytest.mark.parametrize("M,N,K,bn", [
+    (128, 16, 64, 16), (128, 16, 256, 16), (256, 128, 512, 128), (300, 72, 328, 0),
+    (1024, 256, 4096, 256), (512, 64, 1024, 64), (128, 32, 2048, 32),
+])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_plain(M, N, K, bn, out_dtype):
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=out_dtype)
+    _C().gemm_bf16_tn(a, b, out, False, 0, 1, bn)
+    torch.cuda.synchronize()
+    _check(out, _ref(a, b), K)
+
+
+@pytest.mark.parametrize("batch", [1, 4, 16])
+@pytest.mark.parametrize("splitk", [1, 2, 4, 8, 0])
+def test_gemm_swap_ab_splitk(batch, splitk):
+    """Decode shape: weights on the UMMA M side, the few activation rows on the N side."""
+    torch.manual_seed(1)
+    n_out, K = 1536, 4096
+    w = torch.randn(n_out, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    x = torch.randn(batch, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(batch, n_out, device="cuda", dtype=torch.bfloat16)
+    _C().gemm_bf16_tn(w, x, out, True, 0, splitk, 16)
+    torch.cuda.synchronize()
+    _check(out, _ref(x, w), K)
+
+
+@pytest.mark.parametrize("splitk", [1, 2, 4])
+def test_gemm_dual_swiglu(splitk):
+    torch.manual_seed(2)
+    inter, K, batch = 1376, 4096, 16
+    w = torch.randn(2 * inter, K, device="cuda", dtype=torch.bfloat16) * 0.03
+    x = torch.randn(batch, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(batch, inter, device="cuda", dtype=torch.bfloat16)
+    _C().gemm_bf16_tn(w, x, out, True, inter, splitk, 16)
+    torch.cuda.synchronize()
+    g = x.float() @ w[:inter].float().t()
+    u = x.float() @ w[inter:].float().t()
+    ref = torch.nn.functional.silu(g) * u
+    _check(out, ref, K)
