@@ -1,0 +1,14 @@
+// Shared helpers of the Python binding translation units.
+#pragma once
+#include <torch/csrc/distributed/c10d/Store.hpp>
+#include <torch/extension.h>
+
+#include "cuda/CudaComm.h"
+
+namespace ccl_py {
+
+int to_ccl_dtype(at::ScalarType t);
+ccl::KvStore make_kv(const c10::intrusive_ptr<c10d::Store>& store);
+void bind_cuda_comm(py::module& m);
+
+}  // namespace ccl_py

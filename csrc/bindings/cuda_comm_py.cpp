@@ -1,0 +1,270 @@
+// Python bindings of ccl::CudaComm for direct (non-c10d) use: the single-GPU emulated
+// communicator that the kernel tests drive, and a real one-rank/one-process communicator for
+// tensor-parallel model code that wants the fused ops on its own stream.
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/csrc/distributed/c10d/Store.hpp>
+#include <torch/extension.h>
+
+#include "bindings/common.h"
+#include "cuda/CudaComm.h"
+
+namespace ccl_py {
+
+using ccl::CollArgs;
+using ccl::CudaComm;
+
+int to_ccl_dtype(at::ScalarType t) {
+  switch (t) {
+    case at::kByte: case at::kBool: return ccl::kU8;
+    case at::kChar: return ccl::kI8;
+    case at::kShort: return ccl::kI16;
+    case at::kInt: return ccl::kI32;
+    case at::kLong: return ccl::kI64;
+    case at::kHalf: return ccl::kF16;
+    case at::kBFloat16: return ccl::kBF16;
+    case at::kFloat: return ccl::kF32;
+    case at::kDouble: return ccl::kF64;
+    default: TORCH_CHECK(false, "ccl: unsupported dtype ", t);
+  }
+}
+
+ccl::KvStore make_kv(const c10::intrusive_ptr<c10d::Store>& store) {
+  ccl::KvStore kv;
+  kv.set = [store](const std::string& k, const std::vector<uint8_t>& v) { store->set(k, v); };
+  kv.get = [store](const std::string& k) { return store->get(k); };
+  kv.add = [store](const std::string& k, int64_t v) { return store->add(k, v); };
+  return kv;
+}
+
+namespace {
+
+void cu(cudaError_t e, const char* what) {
+  TORCH_CHECK(e == cudaSuccess, "ccl: ", what, " failed: ", cudaGetErrorString(e));
+}
+
+struct PyComm {
+  std::unique_ptr<CudaComm> comm;
+
+  cudaStream_t stream() const { return c10::cuda::getCurrentCUDAStream(comm->device()).stream(); }
+  void check_n(size_t n) const {
+    TORCH_CHECK((int)n == comm->nctx(), "expected ", comm->nctx(), " per-rank entries, got ", n);
+  }
+
+  std::string allreduce(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, int op, double scale,
+                        int has_scale, int algo) {
+    check_n(ins.size());
+    check_n(outs.size());
+    std::vector<CollArgs> args(ins.size());
+    for (size_t i = 0; i < ins.size(); ++i) {
+      TORCH_CHECK(ins[i].is_contiguous() && outs[i].is_contiguous(), "contiguous tensors required");
+      args[i].in = ins[i].data_ptr();
+      args[i].out = outs[i].data_ptr();
+      args[i].count = ins[i].numel();
+      args[i].op = op;
+      args[i].scale = (float)scale;
+      args[i].has_scale = has_scale;
+    }
+    auto saved = comm->config().algo;
+    comm->mutable_config().algo = static_cast<ccl::Algo>(algo);
+    ccl::AlgoChoice ch{};
+    cudaError_t e = comm->allreduce(to_ccl_dtype(ins[0].scalar_type()), args, stream(), &ch);
+    comm->mutable_config().algo = saved;
+    cu(e, "allreduce");
+    return std::string(ch.algo == ccl::Algo::kOneShot ? "oneshot" : "twoshot") + ":" + std::to_string(ch.nblocks);
+  }
+
+  void reduce(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, int op, int root) {
+    check_n(ins.size());
+    std::vector<CollArgs> args(ins.size());
+    for (size_t i = 0; i < ins.size(); ++i) {
+      args[i].in = ins[i].data_ptr();
+      args[i].out = outs[i].data_ptr();
+      args[i].count = ins[i].numel();
+      args[i].op = op;
+      args[i].root = root;
+    }
+    cu(comm->reduce(to_ccl_dtype(ins[0].scalar_type()), args, stream()), "reduce");
+  }
+
+  // ins[r]: list of `world` pieces (piece p goes to rank p); outs[r]: rank r's reduced piece
+  void reduce_scatter(std::vector<std::vector<at::Tensor>> ins, std::vector<at::Tensor> outs, int op,
+                      double scale, int has_scale) {
+    check_n(ins.size());
+    std::vector<CollArgs> args(ins.size());
+    const int W = comm->world();
+    for (size_t i = 0; i < ins.size(); ++i) {
+      TORCH_CHECK((int)ins[i].size() == W, "need one piece per rank");
+      for (int p = 0; p < W; ++p) {
+        args[i].in_piece[p] = ins[i][p].data_ptr();
+        args[i].in_cnt[p] = ins[i][p].numel();
+      }
+      args[i].out = outs[i].data_ptr();
+      args[i].op = op;
+      args[i].scale = (float)scale;
+      args[i].has_scale = has_scale;
+    }
+    cu(comm->reduce_scatter(to_ccl_dtype(ins[0][0].scalar_type()), to_ccl_dtype(outs[0].scalar_type()), args, stream()),
+       "reduce_scatter");
+  }
+
+  void all_gather(std::vector<at::Tensor> ins, std::vector<std::vector<at::Tensor>> outs) {
+    check_n(ins.size());
+    std::vector<CollArgs> args(ins.size());
+    const int W = comm->world();
+    for (size_t i = 0; i < ins.size(); ++i) {
+      args[i].in = ins[i].data_ptr();
+      for (int p = 0; p < W; ++p) {
+        args[i].out_piece[p] = outs[i][p].data_ptr();
+        args[i].out_cnt[p] = outs[i][p].numel() * outs[i][p].element_size();
+      }
+    }
+    cu(comm->all_gather(args, stream()), "all_gather");
+  }
+
+  void all_to_all(std::vector<std::vector<at::Tensor>> ins, std::vector<std::vector<at::Tensor>> outs, bool uneven) {
+    check_n(ins.size());
+    std::vector<CollArgs> args(ins.size());
+    const int W = comm->world();
+    for (size_t i = 0; i < ins.size(); ++i) {
+      for (int p = 0; p < W; ++p) {
+        args[i].in_piece[p] = ins[i][p].data_ptr();
+        args[i].in_cnt[p] = ins[i][p].numel() * ins[i][p].element_size();
+        args[i].out_piece[p] = outs[i][p].data_ptr();
+        args[i].out_cnt[p] = outs[i][p].numel() * outs[i][p].element_size();
+      }
+    }
+    cu(comm->all_to_all(args, uneven, stream()), "all_to_all");
+  }
+
+  void broadcast(std::vector<at::Tensor> bufs, int root) {
+    check_n(bufs.size());
+    std::vector<CollArgs> args(bufs.size());
+    for (size_t i = 0; i < bufs.size(); ++i) {
+      args[i].out = bufs[i].data_ptr();
+      args[i].count = bufs[i].numel() * bufs[i].element_size();
+      args[i].root = root;
+      args[i].mode = ccl::kBroadcast;
+    }
+    cu(comm->rooted(args, stream()), "broadcast");
+  }
+  // ins[r]: rank r's piece; outs: root's list of `world` tensors
+  void gather(std::vector<at::Tensor> ins, std::vector<at::Tensor> root_outs, int root) {
+    check_n(ins.size());
+    std::vector<CollArgs> args(ins.size());
+    const int W = comm->world();
+    for (size_t i = 0; i < ins.size(); ++i) {
+      args[i].in = ins[i].data_ptr();
+      args[i].count = ins[i].numel() * ins[i].element_size();
+      args[i].root = root;
+      args[i].mode = ccl::kGather;
+      const bool is_root = comm->emulated() ? ((int)i == root) : (comm->rank() == root);
+      if (is_root)
+        for (int p = 0; p < W; ++p) args[i].out_piece[p] = root_outs[p].data_ptr();
+    }
+    cu(comm->rooted(args, stream()), "gather");
+  }
+  void scatter(std::vector<at::Tensor> root_ins, std::vector<at::Tensor> outs, int root) {
+    check_n(outs.size());
+    std::vector<CollArgs> args(outs.size());
+    const int W = comm->world();
+    for (size_t i = 0; i < outs.size(); ++i) {
+      args[i].out = outs[i].data_ptr();
+      args[i].count = outs[i].numel() * outs[i].element_size();
+      args[i].root = root;
+      args[i].mode = ccl::kScatter;
+      const bool is_root = comm->emulated() ? ((int)i == root) : (comm->rank() == root);
+      if (is_root)
+        for (int p = 0; p < W; ++p) args[i].in_piece[p] = root_ins[p].data_ptr();
+    }
+    cu(comm->rooted(args, stream()), "scatter");
+  }
+  void barrier() { cu(comm->barrier(stream()), "barrier"); }
+
+  void allreduce_residual_rmsnorm(std::vector<at::Tensor> xs, std::vector<at::Tensor> residuals,
+                                  std::vector<at::Tensor> weights, std::vector<at::Tensor> outs, double eps) {
+    check_n(xs.size());
+    std::vector<ccl::FusedNormArgs> args(xs.size());
+    for (size_t i = 0; i < xs.size(); ++i) {
+      TORCH_CHECK(xs[i].is_contiguous() && residuals[i].is_contiguous() && outs[i].is_contiguous(),
+                  "contiguous tensors required");
+      TORCH_CHECK(xs[i].dim() == 2, "x must be [rows, hidden]");
+      args[i].x = xs[i].data_ptr();
+      args[i].residual = residuals[i].data_ptr();
+      args[i].weight = weights[i].data_ptr();
+      args[i].out = outs[i].data_ptr();
+      args[i].rows = (int)xs[i].size(0);
+      args[i].hidden = (int)xs[i].size(1);
+      args[i].eps = (float)eps;
+    }
+    cu(comm->allreduce_residual_rmsnorm(to_ccl_dtype(xs[0].scalar_type()), args, stream()),
+       "allreduce_residual_rmsnorm");
+  }
+
+  std::vector<int> status() {
+    int r = 0, p = 0, ph = 0;
+    int code = comm->poll_status(&r, &p, &ph);
+    return {code, r, p, ph};
+  }
+};
+
+}  // namespace
+
+void bind_cuda_comm(py::module& m) {
+  m.def("emu_missing_peer_probe", [](PyComm& c) {
+    return c.comm->barrier_single_rank(0, c.stream()) == cudaSuccess;
+  });
+  py::class_<PyComm>(m, "CudaComm")
+      .def_static(
+          "emulated",
+          [](int world, int64_t half_bytes, int64_t spin_ms, int max_blocks) {
+            ccl::CommConfig cfg;
+            cfg.half_bytes = (size_t)half_bytes;
+            cfg.spin_timeout_ms = (uint64_t)spin_ms;
+            cfg.max_blocks = max_blocks;
+            auto p = std::make_unique<PyComm>();
+            p->comm = std::make_unique<CudaComm>(world, (int)c10::cuda::current_device(), cfg);
+            return p;
+          },
+          py::arg("world"), py::arg("half_bytes") = (int64_t)(8 << 20), py::arg("spin_ms") = 2000,
+          py::arg("max_blocks") = 8)
+      .def_static(
+          "create",
+          [](const c10::intrusive_ptr<c10d::Store>& store, int rank, int world, int64_t half_bytes,
+             int64_t spin_ms, const std::string& prefix) {
+            ccl::CommConfig cfg;
+            cfg.half_bytes = (size_t)half_bytes;
+            cfg.spin_timeout_ms = (uint64_t)spin_ms;
+            auto p = std::make_unique<PyComm>();
+            py::gil_scoped_release nogil;
+            p->comm = std::make_unique<CudaComm>(rank, world, (int)c10::cuda::current_device(), cfg,
+                                                 store ? make_kv(store) : ccl::KvStore{}, prefix);
+            return p;
+          },
+          py::arg("store"), py::arg("rank"), py::arg("world"), py::arg("half_bytes") = (int64_t)(64 << 20),
+          py::arg("spin_ms") = 30000, py::arg("prefix") = "ccl/direct")
+      .def_property_readonly("world", [](PyComm& c) { return c.comm->world(); })
+      .def_property_readonly("rank", [](PyComm& c) { return c.comm->rank(); })
+      .def_property_readonly("nctx", [](PyComm& c) { return c.comm->nctx(); })
+      .def_property_readonly("launches", [](PyComm& c) { return c.comm->launches(); })
+      .def("set_oneshot_max_bytes", [](PyComm& c, int64_t b) { c.comm->mutable_config().oneshot_max_bytes = (size_t)b; })
+      .def("set_ag_push_max_bytes", [](PyComm& c, int64_t b) { c.comm->mutable_config().ag_push_max_bytes = (size_t)b; })
+      .def("set_max_blocks", [](PyComm& c, int b) { c.comm->mutable_config().max_blocks = b; })
+      .def("set_ablate", [](PyComm& c, int a) { c.comm->mutable_config().ablate = a; })
+      .def("allreduce", &PyComm::allreduce, py::arg("ins"), py::arg("outs"), py::arg("op") = 0,
+           py::arg("scale") = 1.0, py::arg("has_scale") = 0, py::arg("algo") = 0)
+      .def("reduce", &PyComm::reduce)
+      .def("reduce_scatter", &PyComm::reduce_scatter, py::arg("ins"), py::arg("outs"), py::arg("op") = 0,
+           py::arg("scale") = 1.0, py::arg("has_scale") = 0)
+      .def("all_gather", &PyComm::all_gather)
+      .def("all_to_all", &PyComm::all_to_all, py::arg("ins"), py::arg("outs"), py::arg("uneven") = false)
+      .def("broadcast", &PyComm::broadcast)
+      .def("gather", &PyComm::gather)
+      .def("scatter", &PyComm::scatter)
+      .def("barrier", &PyComm::barrier)
+      .def("allreduce_residual_rmsnorm", &PyComm::allreduce_residual_rmsnorm)
+      .def("status", &PyComm::status)
+      .def("clear_status", [](PyComm& c) { c.comm->clear_status(); });
+}
+
+}  // namespace ccl_py

@@ -3,6 +3,7 @@
 #include <c10/cuda/CUDAStream.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include "bindings/common.h"
 #include "cuda/kernels/gemm.h"
 
 namespace {
@@ -53,6 +54,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16_tn", &gemm_bf16_tn, py::arg("a"), py::arg("b"), py::arg("out"),
         py::arg("trans_out") = false, py::arg("dual_off") = 0, py::arg("splitk") = 0,
         py::arg("bn") = 0);
+  ccl_py::bind_cuda_comm(m);
   m.def("launch_count", &ccl::launch_count);
   m.def("launch_count_reset", &ccl::launch_count_reset);
 }

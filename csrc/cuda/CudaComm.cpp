@@ -1,0 +1,387 @@
+#include "cuda/CudaComm.h"
+
+#include <algorithm>
+#include <chrono>
+#include <cstring>
+#include <stdexcept>
+#include <thread>
+
+namespace ccl {
+
+namespace {
+
+void check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) {
+    throw std::runtime_error(std::string("ccl: ") + what + " failed: " + cudaGetErrorString(e));
+  }
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) cudaSetDevice(dev);
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+size_t arena_size(size_t half) { return 2 * half + kFlagBytes + kStateBytes; }
+
+void fill_ctx(RankCtx& c, int rank, int world, const std::vector<void*>& bases, size_t half,
+              uint64_t spin_ms, int* status) {
+  std::memset(&c, 0, sizeof(c));
+  for (int p = 0; p < world; ++p) {
+    c.data[p] = static_cast<char*>(bases[p]);
+    c.flags[p] = reinterpret_cast<uint32_t*>(static_cast<char*>(bases[p]) + 2 * half);
+  }
+  c.state = reinterpret_cast<uint32_t*>(static_cast<char*>(bases[rank]) + 2 * half + kFlagBytes);
+  c.status = status;
+  c.half_bytes = half;
+  c.spin_ns = spin_ms * 1000000ull;
+  c.mc_data = nullptr;
+  c.rank = rank;
+  c.world = world;
+}
+
+void barrier_kv(KvStore& kv, const std::string& key, int world, uint64_t timeout_ms) {
+  if (!kv.add) return;
+  kv.add(key, 1);
+  const auto t0 = std::chrono::steady_clock::now();
+  while (kv.add(key, 0) < world) {
+    if (std::chrono::steady_clock::now() - t0 > std::chrono::milliseconds(timeout_ms))
+      throw std::runtime_error("ccl: timeout in bootstrap barrier '" + key + "'");
+    std::this_thread::sleep_for(std::chrono::milliseconds(1));
+  }
+}
+
+}  // namespace
+
+CudaComm::CudaComm(int rank, int world, int device, const CommConfig& cfg, KvStore kv,
+                   const std::string& prefix)
+    : rank_(rank), world_(world), device_(device), emulated_(false), cfg_(cfg), kv_(std::move(kv)),
+      prefix_(prefix) {
+  if (world < 1 || world > kMaxRanks) throw std::runtime_error("ccl: CUDA communicators support 1..8 ranks");
+  DeviceGuard g(device_);
+  cfg_.half_bytes = round_up(cfg_.half_bytes, 1 << 20);
+  arena_bytes_ = arena_size(cfg_.half_bytes);
+  void* base = nullptr;
+  check(cudaMalloc(&base, arena_bytes_), "cudaMalloc(arena)");
+  check(cudaMemset(base, 0, arena_bytes_), "cudaMemset(arena)");
+  check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+  local_arenas_.push_back(base);
+  peer_arenas_.assign(world_, nullptr);
+  peer_arenas_[rank_] = base;
+
+  check(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped | cudaHostAllocPortable),
+        "cudaHostAlloc(status)");
+  std::memset(status_host_, 0, 64);
+  check(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev_), status_host_, 0), "cudaHostGetDevicePointer");
+
+  if (world_ > 1) {
+    cudaIpcMemHandle_t h;
+    check(cudaIpcGetMemHandle(&h, base), "cudaIpcGetMemHandle");
+    std::vector<uint8_t> blob(sizeof(h) + sizeof(int));
+    std::memcpy(blob.data(), &h, sizeof(h));
+    std::memcpy(blob.data() + sizeof(h), &device_, sizeof(int));
+    kv_.set(prefix_ + "/ipc/" + std::to_string(rank_), blob);
+    for (int p = 0; p < world_; ++p) {
+      if (p == rank_) continue;
+      std::vector<uint8_t> pb = kv_.get(prefix_ + "/ipc/" + std::to_string(p));
+      if (pb.size() != blob.size()) throw std::runtime_error("ccl: malformed IPC handle from peer");
+      cudaIpcMemHandle_t ph;
+      int pdev = 0;
+      std::memcpy(&ph, pb.data(), sizeof(ph));
+      std::memcpy(&pdev, pb.data() + sizeof(ph), sizeof(int));
+      int can = 0;
+      check(cudaDeviceCanAccessPeer(&can, device_, pdev), "cudaDeviceCanAccessPeer");
+      if (!can && pdev != device_)
+        throw std::runtime_error("ccl: GPU " + std::to_string(device_) + " cannot access peer GPU " + std::to_string(pdev));
+      void* pp = nullptr;
+      check(cudaIpcOpenMemHandle(&pp, ph, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+      peer_arenas_[p] = pp;
+    }
+    // nobody may signal into an arena before its owner has zeroed it and everyone has mapped it
+    barrier_kv(kv_, prefix_ + "/ready", world_, 120000);
+  }
+  init_tables();
+}
+
+CudaComm::CudaComm(int world, int device, const CommConfig& cfg)
+    : rank_(0), world_(world), device_(device), emulated_(true), cfg_(cfg) {
+  if (world < 1 || world > kMaxRanks) throw std::runtime_error("ccl: CUDA communicators support 1..8 ranks");
+  DeviceGuard g(device_);
+  cfg_.half_bytes = round_up(cfg_.half_bytes, 1 << 20);
+  arena_bytes_ = arena_size(cfg_.half_bytes);
+  for (int r = 0; r < world_; ++r) {
+    void* base = nullptr;
+    check(cudaMalloc(&base, arena_bytes_), "cudaMalloc(arena)");
+    check(cudaMemset(base, 0, arena_bytes_), "cudaMemset(arena)");
+    local_arenas_.push_back(base);
+  }
+  peer_arenas_ = local_arenas_;
+  check(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped | cudaHostAllocPortable),
+        "cudaHostAlloc(status)");
+  std::memset(status_host_, 0, 64);
+  check(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev_), status_host_, 0), "cudaHostGetDevicePointer");
+  check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+  init_tables();
+}
+
+void CudaComm::init_tables() {
+  const int n = nctx();
+  host_ctx_.resize(n);
+  for (int i = 0; i < n; ++i) {
+    const int r = emulated_ ? i : rank_;
+    fill_ctx(host_ctx_[i], r, world_, peer_arenas_, cfg_.half_bytes, cfg_.spin_timeout_ms, status_dev_);
+  }
+  if (emulated_) {
+    check(cudaMalloc(reinterpret_cast<void**>(&dev_ctx_table_), sizeof(RankCtx) * n), "cudaMalloc(ctx table)");
+    check(cudaMemcpy(dev_ctx_table_, host_ctx_.data(), sizeof(RankCtx) * n, cudaMemcpyHostToDevice), "cudaMemcpy(ctx table)");
+    check(cudaMalloc(&dev_args_table_, 64 << 10), "cudaMalloc(args table)");
+  }
+}
+
+CudaComm::~CudaComm() {
+  cudaSetDevice(device_);
+  cudaDeviceSynchronize();
+  if (!emulated_ && world_ > 1) {
+    // peers may still be reading this arena: wait for them (best effort) before unmapping
+    try {
+      barrier_kv(kv_, prefix_ + "/bye", world_, 5000);
+    } catch (...) {
+    }
+    for (int p = 0; p < world_; ++p)
+      if (p != rank_ && peer_arenas_[p]) cudaIpcCloseMemHandle(peer_arenas_[p]);
+  }
+  for (void* a : local_arenas_) cudaFree(a);
+  if (dev_ctx_table_) cudaFree(dev_ctx_table_);
+  if (dev_args_table_) cudaFree(dev_args_table_);
+  if (status_host_) cudaFreeHost(status_host_);
+}
+
+int CudaComm::poll_status(int* rank, int* peer, int* phase) const {
+  volatile int* s = status_host_;
+  const int code = s[0];
+  if (code) {
+    if (rank) *rank = s[1];
+    if (peer) *peer = s[2];
+    if (phase) *phase = s[3];
+  }
+  return code;
+}
+void CudaComm::clear_status() {
+  volatile int* s = status_host_;
+  s[1] = s[2] = s[3] = 0;
+  s[0] = 0;
+}
+
+template <typename ArgsT>
+const ArgsT* CudaComm::upload(const std::vector<ArgsT>& args, cudaStream_t stream) {
+  if (!emulated_) return args.data();
+  if (sizeof(ArgsT) * args.size() > (64u << 10)) throw std::runtime_error("ccl: args table too large");
+  // emulation is a test vehicle: a synchronous copy keeps lifetimes trivial
+  check(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+  check(cudaMemcpy(dev_args_table_, args.data(), sizeof(ArgsT) * args.size(), cudaMemcpyHostToDevice), "cudaMemcpy(args)");
+  return static_cast<const ArgsT*>(dev_args_table_);
+}
+
+LaunchCfg CudaComm::launch_cfg(int nblocks, int nthreads, cudaStream_t stream) const {
+  LaunchCfg c;
+  c.nblocks = std::max(1, std::min(nblocks, kMaxBlocks));
+  c.nthreads = nthreads;
+  c.nctx = nctx();
+  c.cooperative = emulated_;
+  c.stream = stream;
+  if (emulated_) c.nblocks = std::min(c.nblocks, std::max(1, 128 / world_));  // keep every CTA co-resident
+  return c;
+}
+
+int CudaComm::blocks_for(size_t vecs, int cap) const {
+  const size_t per_block = (size_t)cfg_.threads * 4;
+  size_t b = (vecs + per_block - 1) / per_block;
+  if (b < 1) b = 1;
+  if (b > (size_t)cap) b = cap;
+  return (int)b;
+}
+
+#define CCL_CHECK_ARGS(v)                                                             \
+  if ((int)(v).size() != nctx()) return cudaErrorInvalidValue;
+
+cudaError_t CudaComm::allreduce(int dtype, std::vector<CollArgs> args, cudaStream_t stream, AlgoChoice* chosen) {
+  CCL_CHECK_ARGS(args)
+  DeviceGuard g(device_);
+  const size_t esz = dtype_size(dtype);
+  const size_t count = args[0].count;
+  const size_t bytes = count * esz;
+  const size_t nvec = (bytes + 15) / 16;
+  Algo algo = cfg_.algo;
+  const size_t slot = round_up(nvec * 16, 128);
+  const bool fits_oneshot = slot * world_ <= cfg_.half_bytes;
+  if (algo == Algo::kAuto || algo == Algo::kNvls)
+    algo = (bytes <= cfg_.oneshot_max_bytes && fits_oneshot) ? Algo::kOneShot : Algo::kTwoShot;
+  if (algo == Algo::kOneShot && !fits_oneshot) algo = Algo::kTwoShot;
+  for (auto& a : args) {
+    a.ablate = cfg_.ablate;
+    a.root = -1;
+  }
+  cudaError_t e;
+  LaunchCfg lc;
+  if (algo == Algo::kOneShot) {
+    lc = launch_cfg(blocks_for(nvec, 32), cfg_.threads, stream);
+    e = launch_allreduce_oneshot(dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  } else {
+    size_t stride = cfg_.half_bytes / (16 * (size_t)(world_ + 1));
+    stride = stride / 8 * 8;
+    for (auto& a : args) a.chunk_vecs = stride;
+    lc = launch_cfg(blocks_for((nvec + world_ - 1) / world_, cfg_.max_blocks), cfg_.threads, stream);
+    e = launch_allreduce_twoshot(dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  }
+  if (chosen) *chosen = AlgoChoice{algo, lc.nblocks, lc.nthreads};
+  if (e == cudaSuccess) ++launches_;
+  return e;
+}
+
+cudaError_t CudaComm::reduce(int dtype, std::vector<CollArgs> args, cudaStream_t stream) {
+  CCL_CHECK_ARGS(args)
+  DeviceGuard g(device_);
+  const size_t nvec = (args[0].count * dtype_size(dtype) + 15) / 16;
+  size_t stride = cfg_.half_bytes / (16 * (size_t)(world_ + 1));
+  stride = stride / 8 * 8;
+  for (auto& a : args) {
+    a.chunk_vecs = stride;
+    a.ablate = cfg_.ablate;
+  }
+  LaunchCfg lc = launch_cfg(blocks_for((nvec + world_ - 1) / world_, cfg_.max_blocks), cfg_.threads, stream);
+  cudaError_t e = launch_allreduce_twoshot(dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  if (e == cudaSuccess) ++launches_;
+  return e;
+}
+
+cudaError_t CudaComm::reduce_scatter(int in_dtype, int out_dtype, std::vector<CollArgs> args, cudaStream_t stream) {
+  CCL_CHECK_ARGS(args)
+  DeviceGuard g(device_);
+  const size_t esz = dtype_size(in_dtype);
+  const size_t per_vec = 16 / esz;
+  size_t stride = cfg_.half_bytes / (16 * (size_t)world_);
+  stride = stride / 8 * 8;
+  size_t maxv = 0;
+  for (auto& a : args)
+    for (int p = 0; p < world_; ++p) maxv = std::max(maxv, ((size_t)a.in_cnt[p] + per_vec - 1) / per_vec);
+  const int rounds = (int)((maxv + stride - 1) / stride);
+  for (auto& a : args) {
+    a.chunk_vecs = stride;
+    a.rounds = rounds;
+    a.ablate = cfg_.ablate;
+  }
+  LaunchCfg lc = launch_cfg(blocks_for(std::min(maxv, stride), cfg_.max_blocks), cfg_.threads, stream);
+  cudaError_t e = launch_reduce_scatter(in_dtype, out_dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  if (e == cudaSuccess) ++launches_;
+  return e;
+}
+
+cudaError_t CudaComm::all_gather(std::vector<CollArgs> args, cudaStream_t stream) {
+  CCL_CHECK_ARGS(args)
+  DeviceGuard g(device_);
+  size_t maxb = 0;
+  for (auto& a : args)
+    for (int p = 0; p < world_; ++p) maxb = std::max(maxb, (size_t)a.out_cnt[p]);
+  const size_t maxv = (maxb + 15) / 16;
+  const int mode = (maxb <= cfg_.ag_push_max_bytes) ? 1 : 0;
+  size_t stride = mode == 1 ? cfg_.half_bytes / (16 * (size_t)world_) : cfg_.half_bytes / 16;
+  stride = stride / 8 * 8;
+  const int rounds = (int)((maxv + stride - 1) / stride);
+  for (auto& a : args) {
+    a.chunk_vecs = stride;
+    a.rounds = rounds;
+    a.mode = mode;
+    a.ablate = cfg_.ablate;
+  }
+  LaunchCfg lc = launch_cfg(blocks_for(std::min(maxv, stride), cfg_.max_blocks), cfg_.threads, stream);
+  cudaError_t e = launch_all_gather(emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  if (e == cudaSuccess) ++launches_;
+  return e;
+}
+
+cudaError_t CudaComm::all_to_all(std::vector<CollArgs> args, bool uneven, cudaStream_t stream) {
+  CCL_CHECK_ARGS(args)
+  DeviceGuard g(device_);
+  size_t stride = cfg_.half_bytes / (16 * (size_t)world_);
+  stride = stride / 8 * 8;
+  size_t maxb = 0;
+  for (auto& a : args)
+    for (int p = 0; p < world_; ++p) maxb = std::max(maxb, std::max((size_t)a.in_cnt[p], (size_t)a.out_cnt[p]));
+  const size_t maxv = (maxb + 15) / 16;
+  // With uneven splits the number of rounds is agreed on the device (rounds = 0); the emulated
+  // communicator sees every rank's sizes, the real one only its own.
+  const int rounds = uneven ? 0 : (int)((maxv + stride - 1) / stride);
+  for (auto& a : args) {
+    a.chunk_vecs = stride;
+    a.rounds = rounds;
+    a.ablate = cfg_.ablate;
+  }
+  LaunchCfg lc = launch_cfg(blocks_for(std::min(std::max(maxv, (size_t)1), stride), cfg_.max_blocks), cfg_.threads, stream);
+  if (uneven) lc.nblocks = std::max(1, std::min(cfg_.max_blocks, emulated_ ? std::max(1, 128 / world_) : cfg_.max_blocks) / 2);
+  cudaError_t e = launch_all_to_all(emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  if (e == cudaSuccess) ++launches_;
+  return e;
+}
+
+cudaError_t CudaComm::rooted(std::vector<CollArgs> args, cudaStream_t stream) {
+  CCL_CHECK_ARGS(args)
+  DeviceGuard g(device_);
+  const int mode = args[0].mode;
+  size_t stride = (mode == kGather) ? cfg_.half_bytes / (16 * (size_t)world_) : cfg_.half_bytes / 16;
+  stride = stride / 8 * 8;
+  const size_t maxv = ((size_t)args[0].count + 15) / 16;
+  const int rounds = (int)((maxv + stride - 1) / stride);
+  for (auto& a : args) {
+    a.chunk_vecs = stride;
+    a.rounds = rounds;
+    a.ablate = cfg_.ablate;
+  }
+  LaunchCfg lc = launch_cfg(blocks_for(std::min(maxv, stride), cfg_.max_blocks), cfg_.threads, stream);
+  cudaError_t e = launch_rooted(emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  if (e == cudaSuccess) ++launches_;
+  return e;
+}
+
+cudaError_t CudaComm::barrier(cudaStream_t stream) {
+  DeviceGuard g(device_);
+  std::vector<CollArgs> args(nctx());
+  for (auto& a : args) a.ablate = kAblateNone;
+  LaunchCfg lc = launch_cfg(1, 32, stream);
+  cudaError_t e = launch_barrier(emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  if (e == cudaSuccess) ++launches_;
+  return e;
+}
+
+cudaError_t CudaComm::barrier_single_rank(int i, cudaStream_t stream) {
+  DeviceGuard g(device_);
+  if (i < 0 || i >= nctx()) return cudaErrorInvalidValue;
+  CollArgs a;
+  LaunchCfg lc;
+  lc.nblocks = 1;
+  lc.nthreads = 32;
+  lc.nctx = 1;
+  lc.stream = stream;
+  return launch_barrier(&host_ctx_[i], &a, lc);
+}
+
+cudaError_t CudaComm::allreduce_residual_rmsnorm(int dtype, std::vector<FusedNormArgs> args, cudaStream_t stream) {
+  CCL_CHECK_ARGS(args)
+  DeviceGuard g(device_);
+  const FusedNormArgs& a0 = args[0];
+  if (a0.hidden % 8 != 0 || a0.rows <= 0) return cudaErrorInvalidValue;
+  int threads = std::min(1024, std::max(32, ((a0.hidden / 8 + 31) / 32) * 32));
+  if (a0.hidden / 8 > threads * 4) return cudaErrorInvalidValue;
+  if ((size_t)a0.rows * a0.hidden * 2 > fused_norm_capacity() && world_ > 1) return cudaErrorInvalidValue;
+  for (auto& a : args) a.ablate = cfg_.ablate;
+  LaunchCfg lc = launch_cfg(std::min(a0.rows, kMaxBlocks), threads, stream);
+  cudaError_t e = launch_allreduce_residual_rmsnorm(dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  if (e == cudaSuccess) ++launches_;
+  return e;
+}
+
+}  // namespace ccl

@@ -1,0 +1,118 @@
+// Host side of one CUDA communicator: the peer-mapped arena of every rank ("symmetric memory"),
+// the bootstrap that exchanges memory handles through a key-value store, algorithm selection
+// and the launch wrappers of every collective kernel.
+//
+// Counterpart of the reference's IPC bring-up (`exchange_peer_ipc_mem`,
+// src/gpu/allreduce.h:1208-1248, which all-gathers Level-Zero IPC handles over UNIX sockets and
+// needs MPI_Barrier) and of its per-op branches in src/gpu/dpcpp_ccl.cpp:731-1656. Here the
+// handles are cudaIpc handles published through the c10d Store; no MPI is involved.
+//
+// A CudaComm is either *real* (one process per GPU; nctx() == 1) or *emulated* (all ranks'
+// arenas on one GPU and one cooperative launch per collective; nctx() == world) — the latter
+// exists so that every kernel can be tested on a single GPU.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <functional>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "cuda/kernels/collectives.h"
+
+namespace ccl {
+
+struct KvStore {
+  std::function<void(const std::string&, const std::vector<uint8_t>&)> set;
+  std::function<std::vector<uint8_t>(const std::string&)> get;  // blocks until the key exists
+  std::function<int64_t(const std::string&, int64_t)> add;      // atomic counter
+};
+
+enum class Algo : int { kAuto = 0, kOneShot = 1, kTwoShot = 2, kNvls = 3 };
+
+struct CommConfig {
+  size_t half_bytes = 256ull << 20;   // one staging half per rank (arena = 2 halves + flags)
+  uint64_t spin_timeout_ms = 30000;   // device-side wait budget
+  size_t oneshot_max_bytes = 512 << 10;
+  size_t ag_push_max_bytes = 256 << 10;  // per-piece size below which all_gather pushes
+  int max_blocks = 64;                // CTAs for bandwidth-bound collectives
+  int threads = 512;
+  Algo algo = Algo::kAuto;
+  int ablate = kAblateNone;
+};
+
+struct AlgoChoice {
+  Algo algo;
+  int nblocks;
+  int nthreads;
+};
+
+class CudaComm {
+ public:
+  // Real communicator: collective over all `world` processes (blocks on the store).
+  CudaComm(int rank, int world, int device, const CommConfig& cfg, KvStore kv, const std::string& prefix);
+  // Emulated communicator on one device.
+  CudaComm(int world, int device, const CommConfig& cfg);
+  ~CudaComm();
+  CudaComm(const CudaComm&) = delete;
+  CudaComm& operator=(const CudaComm&) = delete;
+
+  int rank() const { return rank_; }
+  int world() const { return world_; }
+  int nctx() const { return emulated_ ? world_ : 1; }
+  int device() const { return device_; }
+  bool emulated() const { return emulated_; }
+  const CommConfig& config() const { return cfg_; }
+  CommConfig& mutable_config() { return cfg_; }
+  const RankCtx& ctx(int i = 0) const { return host_ctx_[i]; }
+
+  // Error record written by kernels whose bounded waits expired: {code, rank, peer, phase}.
+  // Returns code (0 = healthy).
+  int poll_status(int* rank = nullptr, int* peer = nullptr, int* phase = nullptr) const;
+  void clear_status();
+  // Own arena staging pointer (for zero-copy consumers) and its size.
+  char* local_data(int i = 0) const { return host_ctx_[i].data[host_ctx_[i].rank]; }
+
+  // ---- collectives. `args` has nctx() entries (one per emulated rank, or exactly one). ----
+  // The wrappers fill chunk_vecs / rounds / mode, choose algorithm and grid, and launch on `stream`.
+  cudaError_t allreduce(int dtype, std::vector<CollArgs> args, cudaStream_t stream, AlgoChoice* chosen = nullptr);
+  cudaError_t reduce(int dtype, std::vector<CollArgs> args, cudaStream_t stream);  // args.root set
+  cudaError_t reduce_scatter(int in_dtype, int out_dtype, std::vector<CollArgs> args, cudaStream_t stream);
+  cudaError_t all_gather(std::vector<CollArgs> args, cudaStream_t stream);
+  cudaError_t all_to_all(std::vector<CollArgs> args, bool uneven, cudaStream_t stream);
+  cudaError_t rooted(std::vector<CollArgs> args, cudaStream_t stream);  // mode + root + count set
+  cudaError_t barrier(cudaStream_t stream);
+  // Failure-detection probe: plays ONLY rank `i` of the barrier, so its wait for the other
+  // ranks' flags (which nothing sets) runs into the bounded-wait budget and reports a timeout.
+  cudaError_t barrier_single_rank(int i, cudaStream_t stream);
+  cudaError_t allreduce_residual_rmsnorm(int dtype, std::vector<FusedNormArgs> args, cudaStream_t stream);
+
+  // Capacity (bytes per rank) of the one-shot fused norm path.
+  size_t fused_norm_capacity() const { return cfg_.half_bytes / world_; }
+
+  uint64_t launches() const { return launches_; }
+
+ private:
+  void init_tables();
+  template <typename ArgsT>
+  const ArgsT* upload(const std::vector<ArgsT>& args, cudaStream_t stream);
+  LaunchCfg launch_cfg(int nblocks, int nthreads, cudaStream_t stream) const;
+  int blocks_for(size_t vecs, int cap) const;
+
+  int rank_ = 0, world_ = 1, device_ = 0;
+  bool emulated_ = false;
+  CommConfig cfg_;
+  KvStore kv_;
+  std::string prefix_;
+  size_t arena_bytes_ = 0;
+  std::vector<void*> local_arenas_;   // 1 (real) or world (emulated)
+  std::vector<void*> peer_arenas_;    // real: mapped peer bases (own at [rank])
+  std::vector<RankCtx> host_ctx_;     // nctx entries
+  RankCtx* dev_ctx_table_ = nullptr;  // emulation only
+  void* dev_args_table_ = nullptr;    // emulation only
+  int* status_host_ = nullptr;        // pinned + mapped
+  int* status_dev_ = nullptr;
+  uint64_t launches_ = 0;
+};
+
+}  // namespace ccl

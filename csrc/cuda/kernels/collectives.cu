@@ -1,0 +1,738 @@
+// Peer-memory collective kernels for sm_100a (NVLink 5 / NVSwitch): one-shot and two-shot
+// all_reduce, reduce(-to-root), reduce_scatter (with fused scale and bf16->fp32 cast),
+// all_gather (pull and push), all_to_all(v) with on-device round agreement, rooted
+// broadcast / gather / scatter, barrier, and the fused all_reduce + residual-add + RMSNorm used
+// by tensor-parallel decode.
+//
+// These replace the two SYCL-ESIMD all-reduce families of intel/torch-ccl
+// (src/gpu/allreduce_small.h:140-381 one-shot; src/gpu/allreduce.h:305-533 hierarchical
+// two-shot, 9 kernels per chunk) and every oneCCL call site of src/gpu/dpcpp_ccl.cpp. NVSwitch
+// is uniform, so the reference's card/tile hierarchy collapses into flat shards, its single-
+// thread sync kernels become in-kernel epoch flags, and accumulation is fp32 instead of fp16.
+//
+// Data movement: user buffers are not peer-mapped, so data crosses NVLink through the arenas
+// (see comm.cuh). Pushes are plain 16-byte stores into the peer's arena followed by a
+// release flag; pulls are system-coherent 16-byte loads from the peer's arena after an acquire.
+#include "collectives.h"
+#include "comm.cuh"
+
+#include <cstdio>
+
+namespace ccl {
+namespace {
+
+template <bool EMU>
+struct Launch {
+  RankCtx ctx;
+  CollArgs args;
+  const RankCtx* ctx_table;
+  const CollArgs* args_table;
+};
+
+struct Range { size_t j0, j1; };
+__device__ __forceinline__ Range sub_slice(size_t len) {
+  const size_t per = ceil_div(len, (size_t)gridDim.x);
+  size_t j0 = (size_t)blockIdx.x * per;
+  if (j0 > len) j0 = len;
+  size_t j1 = j0 + per;
+  if (j1 > len) j1 = len;
+  return {j0, j1};
+}
+__device__ __forceinline__ size_t clamp_len(size_t total, size_t begin, size_t cap) {
+  if (begin >= total) return 0;
+  const size_t r = total - begin;
+  return r < cap ? r : cap;
+}
+__device__ __forceinline__ bool is_aligned16(const void* p) {
+  return (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+}
+
+// user memory (piece of `count` elements, vector index base `vbase`) -> staging
+template <typename T>
+__device__ __forceinline__ void copy_user_to_stage(const T* src, size_t count, size_t vbase,
+                                                   char* stage, Range r) {
+  const bool al = is_aligned16(src);
+  const size_t nt = blockDim.x;
+  size_t j = r.j0 + threadIdx.x;
+  for (; j + 3 * nt < r.j1; j += 4 * nt) {
+    Vec<T> a = load_vec(src, vbase + j, count, al);
+    Vec<T> b = load_vec(src, vbase + j + nt, count, al);
+    Vec<T> c = load_vec(src, vbase + j + 2 * nt, count, al);
+    Vec<T> d = load_vec(src, vbase + j + 3 * nt, count, al);
+    store_stage(stage + j * 16, a);
+    store_stage(stage + (j + nt) * 16, b);
+    store_stage(stage + (j + 2 * nt) * 16, c);
+    store_stage(stage + (j + 3 * nt) * 16, d);
+  }
+  for (; j < r.j1; j += nt) store_stage(stage + j * 16, load_vec(src, vbase + j, count, al));
+}
+// staging -> user memory
+template <typename T>
+__device__ __forceinline__ void copy_stage_to_user(const char* stage, T* dst, size_t count,
+                                                   size_t vbase, Range r) {
+  const bool al = is_aligned16(dst);
+  const size_t nt = blockDim.x;
+  size_t j = r.j0 + threadIdx.x;
+  for (; j + 3 * nt < r.j1; j += 4 * nt) {
+    Vec<T> a = load_stage<T>(stage + j * 16);
+    Vec<T> b = load_stage<T>(stage + (j + nt) * 16);
+    Vec<T> c = load_stage<T>(stage + (j + 2 * nt) * 16);
+    Vec<T> d = load_stage<T>(stage + (j + 3 * nt) * 16);
+    store_vec(dst, vbase + j, count, al, a);
+    store_vec(dst, vbase + j + nt, count, al, b);
+    store_vec(dst, vbase + j + 2 * nt, count, al, c);
+    store_vec(dst, vbase + j + 3 * nt, count, al, d);
+  }
+  for (; j < r.j1; j += nt) store_vec(dst, vbase + j, count, al, load_stage<T>(stage + j * 16));
+}
+// user -> user
+template <typename T>
+__device__ __forceinline__ void copy_user_to_user(const T* src, T* dst, size_t count, size_t vbase,
+                                                  Range r) {
+  if (src == dst) return;
+  const bool als = is_aligned16(src), ald = is_aligned16(dst);
+  for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x)
+    store_vec(dst, vbase + j, count, ald, load_vec(src, vbase + j, count, als));
+}
+
+template <typename T>
+__device__ __forceinline__ Vec<T> finish_vec(const typename Acc<T>::type (&acc)[Vec<T>::kN],
+                                             const CollArgs& a) {
+  using A = typename Acc<T>::type;
+  Vec<T> r;
+#pragma unroll
+  for (int t = 0; t < Vec<T>::kN; ++t) {
+    A v = acc[t];
+    if (a.has_scale == 1) v = static_cast<A>(v * static_cast<A>(a.scale));        // floating types
+    else if (a.has_scale == 2) v = static_cast<A>(v / static_cast<A>(a.scale));   // integer average
+    r.v[t] = from_acc<T, A>(v);
+  }
+  return r;
+}
+
+#define CCL_GET_CTX                                                        \
+  const RankCtx& ctx = EMU ? L.ctx_table[blockIdx.y] : L.ctx;              \
+  const CollArgs& a = EMU ? L.args_table[blockIdx.y] : L.args;             \
+  __shared__ int s_failed;                                                 \
+  Sync sy(ctx, &s_failed, a.ablate != kAblateWorkOnly);                    \
+  const bool do_work = a.ablate != kAblateSyncOnly;                        \
+  (void)do_work;
+
+// ---------------------------------------------------------------------------------------------
+// all_reduce, one-shot: push the whole message to every peer, then everyone reduces everything.
+// Latency-optimal: one NVLink traversal plus one flag.
+// ---------------------------------------------------------------------------------------------
+template <typename T, bool EMU>
+__global__ void __launch_bounds__(1024) allreduce_oneshot_kernel(const __grid_constant__ Launch<EMU> L) {
+  CCL_GET_CTX
+  using A = typename Acc<T>::type;
+  constexpr int N = Vec<T>::kN;
+  const T* in = reinterpret_cast<const T*>(a.in);
+  T* out = reinterpret_cast<T*>(a.out);
+  const size_t count = a.count;
+  const size_t nvec = ceil_div(count, (size_t)N);
+  const size_t slot = round_up(nvec * 16, 128);
+  const Range r = sub_slice(nvec);
+  const bool al_in = is_aligned16(in), al_out = is_aligned16(out);
+  const int W = ctx.world, me = ctx.rank;
+
+  if (do_work) {
+    for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
+      const Vec<T> x = load_vec(in, j, count, al_in);
+#pragma unroll
+      for (int p = 0; p < kMaxRanks; ++p) {
+        if (p < W && p != me) store_stage(sy.half(p, 0) + (size_t)me * slot + j * 16, x);
+      }
+    }
+  }
+  sy.signal_all(0, 0);
+  const bool ok = sy.wait_all(0, 0);
+  if (do_work && ok) {
+    const char* mine = sy.half(me, 0);
+    for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
+      Vec<T> v[kMaxRanks];
+#pragma unroll
+      for (int p = 0; p < kMaxRanks; ++p) {
+        if (p < W) v[p] = (p == me) ? load_vec(in, j, count, al_in) : load_stage<T>(mine + (size_t)p * slot + j * 16);
+      }
+      A acc[N];
+#pragma unroll
+      for (int t = 0; t < N; ++t) acc[t] = to_acc(v[0].v[t]);
+#pragma unroll
+      for (int p = 1; p < kMaxRanks; ++p) {
+        if (p < W) {
+#pragma unroll
+          for (int t = 0; t < N; ++t) acc[t] = Combine<A>::apply(a.op, acc[t], to_acc(v[p].v[t]));
+        }
+      }
+      store_vec(out, j, count, al_out, finish_vec<T>(acc, a));
+    }
+  }
+  sy.finish(1);
+}
+
+// ---------------------------------------------------------------------------------------------
+// all_reduce, two-shot (also reduce-to-root when args.root >= 0): push shard p of the input to
+// rank p (reduce-scatter phase), reduce the own shard, then pull the other reduced shards from
+// the peers (all-gather phase). Bandwidth-optimal: each byte crosses NVLink 2(W-1)/W times.
+// Large messages run as several rounds through the double-buffered arena inside ONE launch.
+// ---------------------------------------------------------------------------------------------
+template <typename T, bool EMU>
+__global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const __grid_constant__ Launch<EMU> L) {
+  CCL_GET_CTX
+  using A = typename Acc<T>::type;
+  constexpr int N = Vec<T>::kN;
+  const T* in = reinterpret_cast<const T*>(a.in);
+  T* out = reinterpret_cast<T*>(a.out);
+  const size_t count = a.count;
+  const size_t nvec = ceil_div(count, (size_t)N);
+  const int W = ctx.world, me = ctx.rank;
+  const size_t stride_v = a.chunk_vecs;          // vectors per shard slot
+  const size_t cv = stride_v * W;                // vectors per round
+  const int rounds = (int)ceil_div(nvec, cv);
+  const bool al_in = is_aligned16(in), al_out = is_aligned16(out);
+  const bool gather_here = (a.root < 0) || (a.root == me);
+
+  bool ok = true;
+  for (int rd = 0; rd < rounds && ok; ++rd) {
+    const size_t base = (size_t)rd * cv;
+    const size_t n = clamp_len(nvec, base, cv);
+    const size_t spr = ceil_div(n, (size_t)W);
+    // phase 0: scatter my contribution to each shard's owner
+    if (do_work) {
+      for (int q = 1; q < W; ++q) {
+        const int p = (me + q) % W;
+        const size_t len = clamp_len(n, (size_t)p * spr, spr);
+        copy_user_to_stage(in, count, base + (size_t)p * spr,
+                           sy.half(p, rd) + (size_t)me * stride_v * 16, sub_slice(len));
+      }
+    }
+    sy.signal_all(0, rd);
+    ok = sy.wait_all(0, rd);
+    if (!ok) break;
+    // reduce my shard
+    const size_t mylen = clamp_len(n, (size_t)me * spr, spr);
+    char* regionA = sy.half(me, rd);
+    char* regionB = regionA + (size_t)W * stride_v * 16;
+    if (do_work) {
+      const Range r = sub_slice(mylen);
+      const size_t vb = base + (size_t)me * spr;
+      for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
+        Vec<T> v[kMaxRanks];
+#pragma unroll
+        for (int p = 0; p < kMaxRanks; ++p) {
+          if (p < W) v[p] = (p == me) ? load_vec(in, vb + j, count, al_in) : load_stage<T>(regionA + ((size_t)p * stride_v + j) * 16);
+        }
+        A acc[N];
+#pragma unroll
+        for (int t = 0; t < N; ++t) acc[t] = to_acc(v[0].v[t]);
+#pragma unroll
+        for (int p = 1; p < kMaxRanks; ++p) {
+          if (p < W) {
+#pragma unroll
+            for (int t = 0; t < N; ++t) acc[t] = Combine<A>::apply(a.op, acc[t], to_acc(v[p].v[t]));
+          }
+        }
+        const Vec<T> res = finish_vec<T>(acc, a);
+        store_stage(regionB + j * 16, res);
+        if (gather_here) store_vec(out, vb + j, count, al_out, res);
+      }
+    }
+    // phase 1: publish the reduced shard; gatherers pull the others
+    sy.signal_all(1, rd);
+    if (gather_here) {
+      ok = sy.wait_all(1, rd);
+      if (!ok) break;
+      if (do_work) {
+        for (int q = 1; q < W; ++q) {
+          const int p = (me + q) % W;
+          const size_t len = clamp_len(n, (size_t)p * spr, spr);
+          copy_stage_to_user(sy.half(p, rd) + (size_t)W * stride_v * 16, out, count,
+                             base + (size_t)p * spr, sub_slice(len));
+        }
+      }
+    }
+  }
+  sy.finish(rounds);
+}
+
+// ---------------------------------------------------------------------------------------------
+// reduce_scatter: rank p receives piece p of every rank and reduces. Pieces may have different
+// sizes; TOut may be wider than TIn (bf16 gradients reduced and stored as fp32) and the scale
+// (gradient average) is applied in the same pass.
+// ---------------------------------------------------------------------------------------------
+template <typename TIn, typename TOut, bool EMU>
+__global__ void __launch_bounds__(1024) reduce_scatter_kernel(const __grid_constant__ Launch<EMU> L) {
+  CCL_GET_CTX
+  using A = typename Acc<TIn>::type;
+  constexpr int N = Vec<TIn>::kN;
+  const int W = ctx.world, me = ctx.rank;
+  const size_t stride_v = a.chunk_vecs;
+  const int rounds = a.rounds;
+  TOut* out = reinterpret_cast<TOut*>(a.out);
+  const size_t mycount = a.in_cnt[me];
+  const TIn* mypiece = reinterpret_cast<const TIn*>(a.in_piece[me]);
+  const bool al_mine = is_aligned16(mypiece);
+  const bool al_out = is_aligned16(out);
+
+  bool ok = true;
+  for (int rd = 0; rd < rounds && ok; ++rd) {
+    const size_t vb = (size_t)rd * stride_v;
+    if (do_work) {
+      for (int q = 1; q < W; ++q) {
+        const int p = (me + q) % W;
+        const size_t nv = ceil_div((size_t)a.in_cnt[p], (size_t)N);
+        const size_t len = clamp_len(nv, vb, stride_v);
+        copy_user_to_stage(reinterpret_cast<const TIn*>(a.in_piece[p]), (size_t)a.in_cnt[p], vb,
+                           sy.half(p, rd) + (size_t)me * stride_v * 16, sub_slice(len));
+      }
+    }
+    sy.signal_all(0, rd);
+    ok = sy.wait_all(0, rd);
+    if (!ok) break;
+    if (do_work) {
+      const size_t nv = ceil_div(mycount, (size_t)N);
+      const Range r = sub_slice(clamp_len(nv, vb, stride_v));
+      const char* regionA = sy.half(me, rd);
+      for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
+        Vec<TIn> v[kMaxRanks];
+#pragma unroll
+        for (int p = 0; p < kMaxRanks; ++p) {
+          if (p < W) v[p] = (p == me) ? load_vec(mypiece, vb + j, mycount, al_mine) : load_stage<TIn>(regionA + ((size_t)p * stride_v + j) * 16);
+        }
+        A acc[N];
+#pragma unroll
+        for (int t = 0; t < N; ++t) acc[t] = to_acc(v[0].v[t]);
+#pragma unroll
+        for (int p = 1; p < kMaxRanks; ++p) {
+          if (p < W) {
+#pragma unroll
+            for (int t = 0; t < N; ++t) acc[t] = Combine<A>::apply(a.op, acc[t], to_acc(v[p].v[t]));
+          }
+        }
+        const size_t e0 = (vb + j) * N;
+        if constexpr (sizeof(TOut) == sizeof(TIn)) {
+          store_vec(reinterpret_cast<TIn*>(out), vb + j, mycount, al_out, finish_vec<TIn>(acc, a));
+        } else {
+          // widened output (float): N elements = N*4 bytes
+          if (al_out && e0 + N <= mycount) {
+#pragma unroll
+            for (int t = 0; t < N; t += 4) {
+              float4 o;
+              o.x = acc[t] * (a.has_scale ? a.scale : 1.f);
+              o.y = acc[t + 1] * (a.has_scale ? a.scale : 1.f);
+              o.z = acc[t + 2] * (a.has_scale ? a.scale : 1.f);
+              o.w = acc[t + 3] * (a.has_scale ? a.scale : 1.f);
+              *reinterpret_cast<float4*>(out + e0 + t) = o;
+            }
+          } else {
+#pragma unroll
+            for (int t = 0; t < N; ++t)
+              if (e0 + t < mycount) out[e0 + t] = static_cast<TOut>(acc[t] * (a.has_scale ? a.scale : 1.f));
+          }
+        }
+      }
+    }
+  }
+  sy.finish(rounds);
+}
+
+// ---------------------------------------------------------------------------------------------
+// all_gather (bytes). mode 0 (pull): stage the own piece locally, peers read it over NVLink
+// straight into their outputs. mode 1 (push): write the own piece into every peer's arena, each
+// rank then copies locally (lower latency for small pieces). Pieces may differ in size.
+// ---------------------------------------------------------------------------------------------
+template <bool EMU>
+__global__ void __launch_bounds__(1024) all_gather_kernel(const __grid_constant__ Launch<EMU> L) {
+  CCL_GET_CTX
+  using T = uint8_t;
+  const int W = ctx.world, me = ctx.rank;
+  const size_t stride_v = a.chunk_vecs;
+  const int rounds = a.rounds;
+  const T* in = reinterpret_cast<const T*>(a.in);
+  const size_t mybytes = a.out_cnt[me];
+  bool ok = true;
+  for (int rd = 0; rd < rounds && ok; ++rd) {
+    const size_t vb = (size_t)rd * stride_v;
+    const size_t mylen = clamp_len(ceil_div(mybytes, (size_t)16), vb, stride_v);
+    if (do_work) {
+      const Range r = sub_slice(mylen);
+      if (a.mode == 0) {
+        copy_user_to_stage(in, mybytes, vb, sy.half(me, rd), r);
+      } else {
+        for (int q = 1; q < W; ++q) {
+          const int p = (me + q) % W;
+          copy_user_to_stage(in, mybytes, vb, sy.half(p, rd) + (size_t)me * stride_v * 16, r);
+        }
+      }
+      copy_user_to_user(in, reinterpret_cast<T*>(a.out_piece[me]), mybytes, vb, r);
+    }
+    sy.signal_all(0, rd);
+    ok = sy.wait_all(0, rd);
+    if (!ok) break;
+    if (do_work) {
+      for (int q = 1; q < W; ++q) {
+        const int p = (me + q) % W;
+        const size_t pb = a.out_cnt[p];
+        const size_t len = clamp_len(ceil_div(pb, (size_t)16), vb, stride_v);
+        const char* src = (a.mode == 0) ? sy.half(p, rd) : sy.half(me, rd) + (size_t)p * stride_v * 16;
+        copy_stage_to_user(src, reinterpret_cast<T*>(a.out_piece[p]), pb, vb, sub_slice(len));
+      }
+    }
+  }
+  sy.finish(rounds);
+}
+
+// ---------------------------------------------------------------------------------------------
+// all_to_all(v) (bytes): piece p of the input goes to rank p. With uneven pieces no rank knows
+// the largest pair-wise piece, so round 0 exchanges each rank's largest send size through the
+// peers' state words and every CTA derives the same number of data rounds from the maximum.
+// ---------------------------------------------------------------------------------------------
+template <bool EMU>
+__global__ void __launch_bounds__(1024) all_to_all_kernel(const __grid_constant__ Launch<EMU> L) {
+  CCL_GET_CTX
+  using T = uint8_t;
+  const int W = ctx.world, me = ctx.rank;
+  const size_t stride_v = a.chunk_vecs;
+  int rounds = a.rounds;
+  int first = 0;
+  bool ok = true;
+  if (rounds == 0) {
+    // scratch words: state[16 + parity*8 + src] = src's largest piece in 16-byte vectors
+    size_t mx = 0;
+    for (int p = 0; p < W; ++p) {
+      const size_t v = ceil_div((size_t)a.in_cnt[p], (size_t)16);
+      mx = v > mx ? v : mx;
+    }
+    const int par = sy.parity(0);
+    if (threadIdx.x < W) {
+      // every CTA writes the same value; the peer's CTA b reads after CTA b's flag
+      uint32_t* peer_state = reinterpret_cast<uint32_t*>(ctx.flags[threadIdx.x]) + kFlagBytes / 4;
+      ptx::st_relaxed_sys(peer_state + 16 + par * kMaxRanks + me, (uint32_t)mx);
+    }
+    sy.signal_all(3, 0);
+    ok = sy.wait_all(3, 0);
+    size_t gmx = 0;
+    for (int p = 0; p < W; ++p) {
+      const size_t v = ptx::ld_relaxed_sys(ctx.state + 16 + par * kMaxRanks + p);
+      gmx = v > gmx ? v : gmx;
+    }
+    rounds = (int)ceil_div(gmx, stride_v);
+    first = 1;
+  }
+  for (int i = 0; i < rounds && ok; ++i) {
+    const int rd = first + i;
+    const size_t vb = (size_t)i * stride_v;
+    if (do_work) {
+      for (int q = 1; q < W; ++q) {
+        const int p = (me + q) % W;
+        const size_t pb = a.in_cnt[p];
+        const size_t len = clamp_len(ceil_div(pb, (size_t)16), vb, stride_v);
+        copy_user_to_stage(reinterpret_cast<const T*>(a.in_piece[p]), pb, vb,
+                           sy.half(p, rd) + (size_t)me * stride_v * 16, sub_slice(len));
+      }
+      const size_t sb = a.in_cnt[me];
+      copy_user_to_user(reinterpret_cast<const T*>(a.in_piece[me]), reinterpret_cast<T*>(a.out_piece[me]),
+                        sb, vb, sub_slice(clamp_len(ceil_div(sb, (size_t)16), vb, stride_v)));
+    }
+    sy.signal_all(0, rd);
+    ok = sy.wait_all(0, rd);
+    if (!ok) break;
+    if (do_work) {
+      for (int q = 1; q < W; ++q) {
+        const int p = (me + q) % W;
+        const size_t pb = a.out_cnt[p];
+        const size_t len = clamp_len(ceil_div(pb, (size_t)16), vb, stride_v);
+        copy_stage_to_user(sy.half(me, rd) + (size_t)p * stride_v * 16,
+                           reinterpret_cast<T*>(a.out_piece[p]), pb, vb, sub_slice(len));
+      }
+    }
+  }
+  sy.finish(first + rounds);
+}
+
+// ---------------------------------------------------------------------------------------------
+// rooted ops (bytes): broadcast, gather, scatter. The root and the other ranks acknowledge each
+// round so that nobody can run more than one round ahead of a rank that still reads staging.
+// ---------------------------------------------------------------------------------------------
+template <bool EMU>
+__global__ void __launch_bounds__(1024) rooted_kernel(const __grid_constant__ Launch<EMU> L) {
+  CCL_GET_CTX
+  using T = uint8_t;
+  const int W = ctx.world, me = ctx.rank, root = a.root;
+  const size_t stride_v = a.chunk_vecs;
+  const int rounds = a.rounds;
+  const size_t bytes = a.count;  // per piece
+  bool ok = true;
+  for (int rd = 0; rd < rounds && ok; ++rd) {
+    const size_t vb = (size_t)rd * stride_v;
+    const size_t len = clamp_len(ceil_div(bytes, (size_t)16), vb, stride_v);
+    const Range r = sub_slice(len);
+    if (a.mode == kBroadcast) {
+      T* buf = reinterpret_cast<T*>(a.out);
+      if (me == root) {
+        if (do_work)
+          for (int q = 1; q < W; ++q) copy_user_to_stage(buf, bytes, vb, sy.half((me + q) % W, rd), r);
+        sy.signal_all(0, rd);
+        ok = sy.wait_all(1, rd);
+      } else {
+        ok = sy.wait_one(root, 0, rd);
+        if (ok && do_work) copy_stage_to_user(sy.half(me, rd), buf, bytes, vb, r);
+        sy.signal_one(root, 1, rd);
+      }
+    } else if (a.mode == kGather) {
+      const T* in = reinterpret_cast<const T*>(a.in);
+      if (me == root) {
+        if (do_work) copy_user_to_user(in, reinterpret_cast<T*>(a.out_piece[me]), bytes, vb, r);
+        ok = sy.wait_all(0, rd);
+        if (ok && do_work)
+          for (int q = 1; q < W; ++q) {
+            const int p = (me + q) % W;
+            copy_stage_to_user(sy.half(me, rd) + (size_t)p * stride_v * 16,
+                               reinterpret_cast<T*>(a.out_piece[p]), bytes, vb, r);
+          }
+        sy.signal_all(1, rd);
+      } else {
+        if (do_work) copy_user_to_stage(in, bytes, vb, sy.half(root, rd) + (size_t)me * stride_v * 16, r);
+        sy.signal_one(root, 0, rd);
+        ok = sy.wait_one(root, 1, rd);
+      }
+    } else {  // scatter
+      T* out = reinterpret_cast<T*>(a.out);
+      if (me == root) {
+        if (do_work) {
+          for (int q = 1; q < W; ++q) {
+            const int p = (me + q) % W;
+            copy_user_to_stage(reinterpret_cast<const T*>(a.in_piece[p]), bytes, vb, sy.half(p, rd), r);
+          }
+          copy_user_to_user(reinterpret_cast<const T*>(a.in_piece[me]), out, bytes, vb, r);
+        }
+        sy.signal_all(0, rd);
+        ok = sy.wait_all(1, rd);
+      } else {
+        ok = sy.wait_one(root, 0, rd);
+        if (ok && do_work) copy_stage_to_user(sy.half(me, rd), out, bytes, vb, r);
+        sy.signal_one(root, 1, rd);
+      }
+    }
+  }
+  sy.finish(rounds);
+}
+
+template <bool EMU>
+__global__ void __launch_bounds__(64) barrier_kernel(const __grid_constant__ Launch<EMU> L) {
+  CCL_GET_CTX
+  sy.signal_all(0, 0);
+  sy.wait_all(0, 0);
+  sy.finish(1);
+}
+
+// ---------------------------------------------------------------------------------------------
+// fused all_reduce + residual add + RMSNorm (tensor-parallel decode). One CTA owns whole rows:
+// it pushes its rows of the partial sums to every peer, waits for the peers' rows, then adds
+// the partials in rank order (fp32), adds the residual, writes the new residual and the
+// normalised output. Rounding points match the unfused sequence all_reduce -> add -> rmsnorm.
+// ---------------------------------------------------------------------------------------------
+template <bool EMU>
+struct LaunchNorm {
+  RankCtx ctx;
+  FusedNormArgs args;
+  const RankCtx* ctx_table;
+  const FusedNormArgs* args_table;
+};
+
+template <typename T> __device__ __forceinline__ T round_to(float v);
+template <> __device__ __forceinline__ __nv_bfloat16 round_to<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+template <> __device__ __forceinline__ __half round_to<__half>(float v) { return __float2half(v); }
+
+constexpr int kNormMaxVecPerThread = 4;
+
+template <typename T, bool EMU>
+__global__ void __launch_bounds__(1024) allreduce_residual_rmsnorm_kernel(const __grid_constant__ LaunchNorm<EMU> L) {
+  const RankCtx& ctx = EMU ? L.ctx_table[blockIdx.y] : L.ctx;
+  const FusedNormArgs& a = EMU ? L.args_table[blockIdx.y] : L.args;
+  __shared__ int s_failed;
+  __shared__ float s_red[33];
+  Sync sy(ctx, &s_failed, a.ablate != kAblateWorkOnly);
+  constexpr int N = 8;
+  const int W = ctx.world, me = ctx.rank;
+  const int hv = a.hidden / N;  // vectors per row
+  const T* x = reinterpret_cast<const T*>(a.x);
+  T* res = reinterpret_cast<T*>(a.residual);
+  const T* wgt = reinterpret_cast<const T*>(a.weight);
+  T* out = reinterpret_cast<T*>(a.out);
+  const size_t slot = round_up((size_t)a.rows * a.hidden * sizeof(T), 128);
+
+  if (W > 1 && a.ablate != kAblateSyncOnly) {
+    for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
+      for (int i = threadIdx.x; i < hv; i += blockDim.x) {
+        const size_t off = ((size_t)row * hv + i) * 16;
+        const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + off);
+#pragma unroll
+        for (int p = 0; p < kMaxRanks; ++p)
+          if (p < W && p != me) ptx::st_v4(sy.half(p, 0) + (size_t)me * slot + off, v);
+      }
+    }
+  }
+  bool ok = true;
+  if (W > 1) {
+    sy.signal_all(0, 0);
+    ok = sy.wait_all(0, 0);
+  }
+  if (ok && a.ablate != kAblateSyncOnly) {
+    const char* mine = sy.half(me, 0);
+    for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
+      float h[kNormMaxVecPerThread][N];
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < kNormMaxVecPerThread; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < hv) {
+          const size_t off = ((size_t)row * hv + i) * 16;
+          float acc[N];
+#pragma unroll
+          for (int p = 0; p < kMaxRanks; ++p) {
+            if (p < W) {
+              Vec<T> v;
+              if (p == me) *reinterpret_cast<uint4*>(&v) = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + off);
+              else v = load_stage<T>(mine + (size_t)p * slot + off);
+#pragma unroll
+              for (int t = 0; t < N; ++t) acc[t] = (p == 0) ? to_acc(v.v[t]) : acc[t] + to_acc(v.v[t]);
+            }
+          }
+          Vec<T> r;
+          *reinterpret_cast<uint4*>(&r) = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(res) + off);
+          Vec<T> hn;
+#pragma unroll
+          for (int t = 0; t < N; ++t) {
+            const float s = to_acc(round_to<T>(acc[t]));        // all_reduce output, rounded
+            const T hr = round_to<T>(s + to_acc(r.v[t]));       // residual add, rounded
+            hn.v[t] = hr;
+            h[k][t] = to_acc(hr);
+            ss += h[k][t] * h[k][t];
+          }
+          *reinterpret_cast<uint4*>(reinterpret_cast<char*>(res) + off) = *reinterpret_cast<const uint4*>(&hn);
+        }
+      }
+      // block reduction of the sum of squares
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      __syncthreads();
+      if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      if (threadIdx.x < 32) {
+        float t = (threadIdx.x < (blockDim.x + 31) / 32) ? s_red[threadIdx.x] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (threadIdx.x == 0) s_red[32] = t;
+      }
+      __syncthreads();
+      const float rstd = rsqrtf(s_red[32] / (float)a.hidden + a.eps);
+#pragma unroll
+      for (int k = 0; k < kNormMaxVecPerThread; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < hv) {
+          Vec<T> w;
+          *reinterpret_cast<uint4*>(&w) = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(wgt) + (size_t)i * 16);
+          Vec<T> o;
+#pragma unroll
+          for (int t = 0; t < N; ++t) o.v[t] = round_to<T>(to_acc(round_to<T>(h[k][t] * rstd)) * to_acc(w.v[t]));
+          *reinterpret_cast<uint4*>(reinterpret_cast<char*>(out) + ((size_t)row * hv + i) * 16) = *reinterpret_cast<const uint4*>(&o);
+        }
+      }
+    }
+  }
+  if (W > 1) sy.finish(1);
+}
+
+// ---------------------------------------------------------------------------------------------
+// launch plumbing
+// ---------------------------------------------------------------------------------------------
+template <typename ArgsT, template <bool> class LT, typename KR, typename KE>
+cudaError_t launch_pair(KR kreal, KE kemu, const RankCtx* ctx, const ArgsT* args, const LaunchCfg& cfg) {
+  dim3 block(cfg.nthreads);
+  if (cfg.nctx <= 1) {
+    LT<false> L;
+    L.ctx = *ctx;
+    L.args = *args;
+    L.ctx_table = nullptr;
+    L.args_table = nullptr;
+    dim3 grid(cfg.nblocks, 1, 1);
+    kreal<<<grid, block, 0, cfg.stream>>>(L);
+    return cudaGetLastError();
+  }
+  LT<true> L;
+  L.ctx = RankCtx{};
+  L.args = ArgsT{};
+  L.ctx_table = ctx;
+  L.args_table = args;
+  dim3 grid(cfg.nblocks, cfg.nctx, 1);
+  void* params[] = {&L};
+  return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kemu), grid, block, params, 0, cfg.stream);
+}
+
+#define CCL_DISPATCH_REDUCE_DTYPE(DT, KERNEL)                                                          \
+  switch (DT) {                                                                                        \
+    case kU8: return launch_pair<CollArgs, Launch>(KERNEL<uint8_t, false>, KERNEL<uint8_t, true>, ctx, args, cfg);       \
+    case kI8: return launch_pair<CollArgs, Launch>(KERNEL<int8_t, false>, KERNEL<int8_t, true>, ctx, args, cfg);         \
+    case kI16: return launch_pair<CollArgs, Launch>(KERNEL<int16_t, false>, KERNEL<int16_t, true>, ctx, args, cfg);      \
+    case kI32: return launch_pair<CollArgs, Launch>(KERNEL<int32_t, false>, KERNEL<int32_t, true>, ctx, args, cfg);      \
+    case kI64: return launch_pair<CollArgs, Launch>(KERNEL<int64_t, false>, KERNEL<int64_t, true>, ctx, args, cfg);      \
+    case kF16: return launch_pair<CollArgs, Launch>(KERNEL<__half, false>, KERNEL<__half, true>, ctx, args, cfg);        \
+    case kBF16: return launch_pair<CollArgs, Launch>(KERNEL<__nv_bfloat16, false>, KERNEL<__nv_bfloat16, true>, ctx, args, cfg); \
+    case kF32: return launch_pair<CollArgs, Launch>(KERNEL<float, false>, KERNEL<float, true>, ctx, args, cfg);          \
+    case kF64: return launch_pair<CollArgs, Launch>(KERNEL<double, false>, KERNEL<double, true>, ctx, args, cfg);        \
+    default: return cudaErrorInvalidValue;                                                             \
+  }
+
+}  // namespace
+
+cudaError_t launch_allreduce_oneshot(int dtype, const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg) {
+  CCL_DISPATCH_REDUCE_DTYPE(dtype, allreduce_oneshot_kernel)
+}
+cudaError_t launch_allreduce_twoshot(int dtype, const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg) {
+  CCL_DISPATCH_REDUCE_DTYPE(dtype, allreduce_twoshot_kernel)
+}
+
+cudaError_t launch_reduce_scatter(int in_dtype, int out_dtype, const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg) {
+  if (in_dtype != out_dtype) {
+    if (out_dtype != kF32) return cudaErrorInvalidValue;
+    if (in_dtype == kBF16)
+      return launch_pair<CollArgs, Launch>(reduce_scatter_kernel<__nv_bfloat16, float, false>, reduce_scatter_kernel<__nv_bfloat16, float, true>, ctx, args, cfg);
+    if (in_dtype == kF16)
+      return launch_pair<CollArgs, Launch>(reduce_scatter_kernel<__half, float, false>, reduce_scatter_kernel<__half, float, true>, ctx, args, cfg);
+    return cudaErrorInvalidValue;
+  }
+  switch (in_dtype) {
+#define RS_CASE(E, T) case E: return launch_pair<CollArgs, Launch>(reduce_scatter_kernel<T, T, false>, reduce_scatter_kernel<T, T, true>, ctx, args, cfg);
+    RS_CASE(kU8, uint8_t) RS_CASE(kI8, int8_t) RS_CASE(kI16, int16_t) RS_CASE(kI32, int32_t)
+    RS_CASE(kI64, int64_t) RS_CASE(kF16, __half) RS_CASE(kBF16, __nv_bfloat16) RS_CASE(kF32, float)
+    RS_CASE(kF64, double)
+#undef RS_CASE
+    default: return cudaErrorInvalidValue;
+  }
+}
+cudaError_t launch_all_gather(const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg) {
+  return launch_pair<CollArgs, Launch>(all_gather_kernel<false>, all_gather_kernel<true>, ctx, args, cfg);
+}
+cudaError_t launch_all_to_all(const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg) {
+  return launch_pair<CollArgs, Launch>(all_to_all_kernel<false>, all_to_all_kernel<true>, ctx, args, cfg);
+}
+cudaError_t launch_rooted(const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg) {
+  return launch_pair<CollArgs, Launch>(rooted_kernel<false>, rooted_kernel<true>, ctx, args, cfg);
+}
+cudaError_t launch_barrier(const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg) {
+  LaunchCfg c = cfg;
+  c.nblocks = 1;
+  c.nthreads = 32;
+  return launch_pair<CollArgs, Launch>(barrier_kernel<false>, barrier_kernel<true>, ctx, args, c);
+}
+cudaError_t launch_allreduce_residual_rmsnorm(int dtype, const RankCtx* ctx, const FusedNormArgs* args, const LaunchCfg& cfg) {
+  if (dtype == kBF16)
+    return launch_pair<FusedNormArgs, LaunchNorm>(allreduce_residual_rmsnorm_kernel<__nv_bfloat16, false>, allreduce_residual_rmsnorm_kernel<__nv_bfloat16, true>, ctx, args, cfg);
+  if (dtype == kF16)
+    return launch_pair<FusedNormArgs, LaunchNorm>(allreduce_residual_rmsnorm_kernel<__half, false>, allreduce_residual_rmsnorm_kernel<__half, true>, ctx, args, cfg);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace ccl

@@ -1,0 +1,209 @@
+// Device-side communicator view and the signalling protocol shared by every collective kernel.
+//
+// Each rank owns one *arena* (peer-mapped on every other rank of the communicator):
+//
+//     [ data half 0 | data half 1 | flags | state ]
+//
+// * data halves: staging space, used alternately ("parity") by consecutive rounds so that a fast
+//   rank can start round k+1 while a slow rank still reads round k. A rank can never be two
+//   rounds ahead because every round makes each rank wait for every other rank at least once.
+// * flags: uint32 words indexed [phase][source rank][CTA]. They carry *monotonic epochs*: a word
+//   is only ever written with increasing values and never reset, so there is no reset race and
+//   a kernel can be replayed from a CUDA graph. CTA b of one rank only ever synchronises with
+//   CTA b of the other ranks, so no grid-wide co-residency is needed.
+// * state: the rank's epoch counter (read by every CTA at kernel start, advanced by the last
+//   CTA to finish) and the completion ticket.
+//
+// The intel/torch-ccl prototype kernels signal with atomic counters that are reset one slot
+// ahead inside a triple buffer (src/gpu/allreduce_small.h:193-285); the epoch scheme replaces
+// that. Every wait is bounded by `spin_ns`; on expiry the kernel writes an error record to
+// `status` (host-visible), stops synchronising and returns normally.
+//
+// Emulation: when launched with gridDim.y == world on ONE GPU, blockIdx.y selects the rank
+// context from a device table, so a single (cooperative) launch plays all ranks. That is how
+// the kernels are exercised on a single GPU.
+#pragma once
+#include "comm_types.h"
+#include "ptx.cuh"
+
+namespace ccl {
+
+__device__ __forceinline__ uint32_t* flag_ptr(uint32_t* base, int phase, int src, int blk) {
+  return base + ((size_t)phase * kMaxRanks + src) * kMaxBlocks + blk;
+}
+
+// Per-CTA protocol helper.
+struct Sync {
+  const RankCtx& ctx;
+  uint32_t epoch;   // epoch at kernel entry; round i signals with value epoch + i + 1
+  int blk;
+  bool sync_enabled;
+  int* failed;      // shared-memory flag
+
+  __device__ Sync(const RankCtx& c, int* failed_smem, bool enabled)
+      : ctx(c), blk(blockIdx.x), sync_enabled(enabled), failed(failed_smem) {
+    if (threadIdx.x == 0) *failed = 0;
+    epoch = ctx.state ? *reinterpret_cast<volatile uint32_t*>(ctx.state) : 0u;
+    __syncthreads();
+  }
+
+  __device__ __forceinline__ int parity(int round) const { return (epoch + round) & 1; }
+  __device__ __forceinline__ char* half(int peer, int round) const {
+    return ctx.data[peer] + (size_t)parity(round) * ctx.half_bytes;
+  }
+
+  // All of this CTA's prior writes (by any thread) become visible to `peer` CTAs that acquire
+  // the flag. Must be called by all threads of the CTA.
+  __device__ __forceinline__ void signal_all(int phase, int round) {
+    __syncthreads();
+    if (sync_enabled && *failed == 0 && threadIdx.x < ctx.world && (int)threadIdx.x != ctx.rank) {
+      ptx::st_release_sys(flag_ptr(ctx.flags[threadIdx.x], phase, ctx.rank, blk), epoch + round + 1);
+    }
+  }
+  __device__ __forceinline__ void signal_one(int peer, int phase, int round) {
+    __syncthreads();
+    if (sync_enabled && *failed == 0 && threadIdx.x == 0 && peer != ctx.rank) {
+      ptx::st_release_sys(flag_ptr(ctx.flags[peer], phase, ctx.rank, blk), epoch + round + 1);
+    }
+  }
+  // Wait until every peer's CTA `blk` has signalled (phase, round). All threads must call it.
+  // Returns false if the communicator is in a failed state.
+  __device__ __forceinline__ bool wait_all(int phase, int round) {
+    if (sync_enabled && threadIdx.x < ctx.world && (int)threadIdx.x != ctx.rank && *failed == 0) {
+      const uint32_t* f = flag_ptr(ctx.flags[ctx.rank], phase, threadIdx.x, blk);
+      if (!ptx::spin_until_epoch(f, epoch + round + 1, ctx.spin_ns)) report(threadIdx.x, phase);
+    }
+    __syncthreads();
+    return *failed == 0;
+  }
+  __device__ __forceinline__ bool wait_one(int peer, int phase, int round) {
+    if (sync_enabled && threadIdx.x == 0 && peer != ctx.rank && *failed == 0) {
+      const uint32_t* f = flag_ptr(ctx.flags[ctx.rank], phase, peer, blk);
+      if (!ptx::spin_until_epoch(f, epoch + round + 1, ctx.spin_ns)) report(peer, phase);
+    }
+    __syncthreads();
+    return *failed == 0;
+  }
+  __device__ void report(int peer, int phase) {
+    *failed = 1;
+    if (ctx.status && atomicCAS(ctx.status, kStatusOk, kStatusTimeout) == kStatusOk) {
+      ctx.status[1] = ctx.rank;
+      ctx.status[2] = peer;
+      ctx.status[3] = phase;
+      __threadfence_system();
+    }
+  }
+  // Advance the rank's epoch by `rounds` once all CTAs of the kernel have finished.
+  __device__ __forceinline__ void finish(int rounds) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const uint32_t t = atomicAdd(ctx.state + 1, 1u);
+      if (t == gridDim.x - 1) {
+        ctx.state[1] = 0;
+        ctx.state[0] = epoch + rounds;
+        __threadfence();
+      }
+    }
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// element helpers: everything is reduced in a wider accumulator type and rounded once
+// ---------------------------------------------------------------------------------------------
+template <typename T> struct Acc { using type = T; };
+template <> struct Acc<__nv_bfloat16> { using type = float; };
+template <> struct Acc<__half> { using type = float; };
+
+template <typename T> __device__ __forceinline__ typename Acc<T>::type to_acc(T v) { return v; }
+template <> __device__ __forceinline__ float to_acc<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_acc<__half>(__half v) { return __half2float(v); }
+
+template <typename T, typename A> __device__ __forceinline__ T from_acc(A v) { return static_cast<T>(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_acc<__nv_bfloat16, float>(float v) { return __float2bfloat16(v); }
+template <> __device__ __forceinline__ __half from_acc<__half, float>(float v) { return __float2half(v); }
+
+template <typename A, bool kIsInt = (A(1) / A(2) == A(0))>
+struct Combine {
+  static __device__ __forceinline__ A apply(int op, A a, A b) {
+    switch (op) {
+      case kSum: return a + b;
+      case kProd: return a * b;
+      case kMin: return b < a ? b : a;
+      case kMax: return b > a ? b : a;
+      default: return a + b;
+    }
+  }
+};
+template <typename A>
+struct Combine<A, true> {
+  static __device__ __forceinline__ A apply(int op, A a, A b) {
+    switch (op) {
+      case kSum: return a + b;
+      case kProd: return a * b;
+      case kMin: return b < a ? b : a;
+      case kMax: return b > a ? b : a;
+      case kBand: return a & b;
+      case kBor: return a | b;
+      case kBxor: return a ^ b;
+      default: return a + b;
+    }
+  }
+};
+
+template <typename T>
+__device__ __forceinline__ T zero_of() {
+  T z;
+  unsigned char* b = reinterpret_cast<unsigned char*>(&z);
+#pragma unroll
+  for (int i = 0; i < (int)sizeof(T); ++i) b[i] = 0;
+  return z;
+}
+
+// A 16-byte vector of T.
+template <typename T>
+struct alignas(16) Vec {
+  static constexpr int kN = 16 / sizeof(T);
+  T v[kN];
+};
+
+// Load vector `i` (16-byte units) of a `count`-element array that may be unaligned or end in a
+// partial vector. `aligned` is true when base is 16-byte aligned.
+template <typename T>
+__device__ __forceinline__ Vec<T> load_vec(const T* base, size_t i, size_t count, bool aligned) {
+  constexpr int N = Vec<T>::kN;
+  Vec<T> r;
+  if (aligned && (i + 1) * N <= count) {
+    *reinterpret_cast<uint4*>(&r) = *reinterpret_cast<const uint4*>(base + i * N);
+  } else {
+#pragma unroll
+    for (int j = 0; j < N; ++j) r.v[j] = (i * N + j < count) ? base[i * N + j] : zero_of<T>();
+  }
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T* base, size_t i, size_t count, bool aligned, const Vec<T>& r) {
+  constexpr int N = Vec<T>::kN;
+  if (aligned && (i + 1) * N <= count) {
+    *reinterpret_cast<uint4*>(base + i * N) = *reinterpret_cast<const uint4*>(&r);
+  } else {
+#pragma unroll
+    for (int j = 0; j < N; ++j)
+      if (i * N + j < count) base[i * N + j] = r.v[j];
+  }
+}
+// Staging accesses are always whole, aligned vectors. Loads bypass L1 and are system-coherent
+// (the data was written by another GPU); stores are plain (released by the flag write).
+template <typename T>
+__device__ __forceinline__ Vec<T> load_stage(const void* p) {
+  Vec<T> r;
+  *reinterpret_cast<uint4*>(&r) = ptx::ld_relaxed_sys_v4(p);
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ void store_stage(void* p, const Vec<T>& r) {
+  ptx::st_v4(p, *reinterpret_cast<const uint4*>(&r));
+}
+
+
+}  // namespace ccl

@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "99a51b7a3789f8f8f200f74add169891669d210e"
+git_version = "b0f33e28de06574a267e1f8b84341327a247b03d"
