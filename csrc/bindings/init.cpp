@@ -55,6 +55,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("trans_out") = false, py::arg("dual_off") = 0, py::arg("splitk") = 0,
         py::arg("bn") = 0);
   ccl_py::bind_cuda_comm(m);
+  ccl_py::bind_process_group(m);
   m.def("launch_count", &ccl::launch_count);
   m.def("launch_count_reset", &ccl::launch_count_reset);
 }

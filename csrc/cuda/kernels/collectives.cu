@@ -651,7 +651,7 @@ __global__ void __launch_bounds__(1024) allreduce_residual_rmsnorm_kernel(const 
 template <typename ArgsT, template <bool> class LT, typename KR, typename KE>
 cudaError_t launch_pair(KR kreal, KE kemu, const RankCtx* ctx, const ArgsT* args, const LaunchCfg& cfg) {
   dim3 block(cfg.nthreads);
-  if (cfg.nctx <= 1) {
+  if (!cfg.cooperative) {
     LT<false> L;
     L.ctx = *ctx;
     L.args = *args;

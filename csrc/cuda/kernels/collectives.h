@@ -49,7 +49,8 @@ struct LaunchCfg {
   int nblocks = 1;
   int nthreads = 512;
   int nctx = 1;            // 1 = real, world = emulation
-  int cooperative = 0;     // emulation launches are cooperative so all CTAs are co-resident
+  int cooperative = 0;     // 1 = emulation: ctx/args are DEVICE tables of nctx entries and the
+                           // launch is cooperative so that all CTAs are co-resident
   cudaStream_t stream = nullptr;
 };
 

@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "b0f33e28de06574a267e1f8b84341327a247b03d"
+git_version = "b608ed1cbd4361b0cef7ef8057f5911ce91ffc21"

@@ -1,0 +1,199 @@
+"""The c10d surface on CUDA tensors with one process per GPU (needs >= 2 GPUs): every collective
+against plain torch math, Work semantics, DDP, sub-groups and NCCL-backed send/recv."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from mp_util import run_ranks
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+SIZES = [1, 7, 4096, 458752 + 1, (8 << 20) + 3]
+
+
+def _world():
+    return min(torch.cuda.device_count(), int(os.environ.get("CCL_TEST_WORLD", "8")))
+
+
+def _data(rank, n, dtype=torch.float32, salt=0):
+    g = torch.Generator().manual_seed(99 + 31 * rank + salt)
+    return torch.randn(n, generator=g, dtype=torch.float64).to(dtype)
+
+
+def _tol(dtype, world):
+    t = {torch.bfloat16: 2e-2, torch.float16: 4e-3, torch.float32: 1e-5}[dtype]
+    return dict(rtol=t, atol=t * world)
+
+
+def _allreduce(rank, world):
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        for n in SIZES:
+            xs = [_data(r, n, dtype) for r in range(world)]
+            ref = torch.stack([x.double() for x in xs]).sum(0)
+            t = xs[rank].cuda()
+            dist.all_reduce(t)
+            torch.testing.assert_close(t.cpu().double(), ref.to(dtype).double(), **_tol(dtype, world))
+            # all ranks hold bitwise the same result
+            gathered = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(gathered, t)
+            for g in gathered:
+                assert torch.equal(g, gathered[0])
+    x = _data(rank, 1000).cuda()
+    ref = torch.stack([_data(r, 1000) for r in range(world)])
+    for op, r in [(dist.ReduceOp.AVG, ref.mean(0)), (dist.ReduceOp.MAX, ref.max(0).values), (dist.ReduceOp.MIN, ref.min(0).values)]:
+        t = x.clone()
+        dist.all_reduce(t, op=op)
+        torch.testing.assert_close(t.cpu(), r, rtol=1e-5, atol=1e-5)
+    ti = torch.arange(100, device="cuda", dtype=torch.int64) + rank
+    dist.all_reduce(ti, op=dist.ReduceOp.BXOR)
+    r = torch.zeros(100, dtype=torch.int64)
+    for k in range(world):
+        r ^= torch.arange(100) + k
+    assert torch.equal(ti.cpu(), r)
+    # async op + wait, coalesced
+    ts = [torch.full((50,), float(rank + i), device="cuda") for i in range(3)]
+    work = dist.all_reduce_coalesced(ts, async_op=True) if hasattr(dist, "all_reduce_coalesced") else None
+    if work is not None:
+        work.wait()
+        for i, t in enumerate(ts):
+            assert torch.all(t == sum(range(world)) + world * i)
+
+
+def _rooted(rank, world):
+    n = 300001
+    xs = [_data(r, n) for r in range(world)]
+    for root in {0, world - 1}:
+        t = xs[rank].cuda()
+        dist.reduce(t, dst=root)
+        if rank == root:
+            torch.testing.assert_close(t.cpu(), torch.stack(xs).sum(0), rtol=1e-5, atol=1e-5)
+        t = xs[rank].cuda()
+        dist.broadcast(t, src=root)
+        assert torch.equal(t.cpu(), xs[root])
+        g = [torch.empty(n, device="cuda") for _ in range(world)] if rank == root else None
+        dist.gather(xs[rank].cuda(), g, dst=root)
+        if rank == root:
+            for r in range(world):
+                assert torch.equal(g[r].cpu(), xs[r])
+        out = torch.empty(n, device="cuda")
+        dist.scatter(out, [x.cuda() for x in xs] if rank == root else None, src=root)
+        assert torch.equal(out.cpu(), xs[rank])
+    with pytest.raises(ValueError, match="unexpected rank"):
+        dist.group.WORLD._get_backend(torch.device("cuda")).broadcast([torch.zeros(1, device="cuda")], _bad_opts(world))
+
+
+def _bad_opts(world):
+    o = dist.BroadcastOptions()
+    o.rootRank = world
+    return o
+
+
+def _gather_scatter_family(rank, world):
+    for n in (1, 4099, 1 << 20):
+        xs = [_data(r, n, torch.bfloat16) for r in range(world)]
+        outs = [torch.empty(n, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+        dist.all_gather(outs, xs[rank].cuda())
+        for r in range(world):
+            assert torch.equal(outs[r].cpu(), xs[r])
+        flat = torch.empty(world * n, dtype=torch.bfloat16, device="cuda")
+        dist.all_gather_into_tensor(flat, xs[rank].cuda())
+        assert torch.equal(flat.cpu(), torch.cat(xs))
+        full = [_data(r, n * world, salt=3) for r in range(world)]
+        out = torch.empty(n, device="cuda")
+        dist.reduce_scatter_tensor(out, full[rank].cuda())
+        ref = torch.stack(full).sum(0)[rank * n:(rank + 1) * n]
+        torch.testing.assert_close(out.cpu(), ref, rtol=1e-5, atol=1e-5)
+    # uneven reduce_scatter list
+    cnt = [3 + 100 * p for p in range(world)]
+    ins = [[_data(r, cnt[p], salt=p) for p in range(world)] for r in range(world)]
+    out = torch.empty(cnt[rank], device="cuda")
+    dist.reduce_scatter(out, [t.cuda() for t in ins[rank]])
+    torch.testing.assert_close(out.cpu(), sum(ins[r][rank] for r in range(world)), rtol=1e-5, atol=1e-5)
+    # all_to_all: equal, uneven single, list
+    x = _data(rank, world * 1000).cuda()
+    o = torch.empty_like(x)
+    dist.all_to_all_single(o, x)
+    ref = torch.cat([_data(r, world * 1000)[rank * 1000:(rank + 1) * 1000] for r in range(world)])
+    assert torch.equal(o.cpu(), ref)
+    send = [[1 + ((r * 7 + p * 3) % 5) * 1000 for p in range(world)] for r in range(world)]
+    xin = _data(rank, sum(send[rank]), salt=5).cuda()
+    recv = [send[p][rank] for p in range(world)]
+    o = torch.empty(sum(recv), device="cuda")
+    dist.all_to_all_single(o, xin, output_split_sizes=recv, input_split_sizes=send[rank])
+    pieces = []
+    for p in range(world):
+        off = sum(send[p][:rank])
+        pieces.append(_data(p, sum(send[p]), salt=5)[off:off + send[p][rank]])
+    assert torch.equal(o.cpu(), torch.cat(pieces))
+    dist.barrier()
+
+
+def _work_semantics_and_ddp(rank, world):
+    t = torch.ones(1 << 20, device="cuda")
+    w = dist.all_reduce(t, async_op=True)
+    w.wait()
+    assert float(t[0]) == world
+    fut = dist.all_reduce(t, async_op=True).get_future()
+    fut.wait()
+    assert float(t[-1]) == world * world
+    # DDP over the backend: gradients are averaged across ranks
+    torch.manual_seed(0)
+    model = torch.nn.Linear(64, 32).cuda()
+    ddp = torch.nn.parallel.DistributedDataParallel(model, device_ids=[torch.cuda.current_device()])
+    x = _data(rank, 16 * 64).view(16, 64).cuda()
+    ddp(x).sum().backward()
+    g = model.weight.grad.clone()
+    ref = torch.stack([_data(r, 16 * 64).view(16, 64).sum(0) for r in range(world)]).mean(0)
+    torch.testing.assert_close(g[0].cpu(), ref, rtol=1e-4, atol=1e-4)
+    # sub-group of the even ranks
+    even = list(range(0, world, 2))
+    sub = dist.new_group(even)
+    if rank in even:
+        s = torch.full((1000,), float(rank), device="cuda")
+        dist.all_reduce(s, group=sub)
+        assert float(s[0]) == sum(even)
+    dist.barrier()
+
+
+def _p2p(rank, world):
+    if rank == 0:
+        dist.send(torch.arange(1000.0, device="cuda"), dst=1)
+    elif rank == 1:
+        t = torch.empty(1000, device="cuda")
+        dist.recv(t, src=0)
+        assert torch.equal(t.cpu(), torch.arange(1000.0))
+    # ring exchange with batched isend/irecv
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    s = torch.full((4096,), float(rank), device="cuda")
+    r = torch.empty(4096, device="cuda")
+    reqs = dist.batch_isend_irecv([dist.P2POp(dist.isend, s, nxt), dist.P2POp(dist.irecv, r, prv)])
+    for q in reqs:
+        q.wait()
+    torch.cuda.synchronize()
+    assert torch.all(r == float(prv))
+    dist.barrier()
+
+
+@pytest.mark.parametrize("fn", [_allreduce, _rooted, _gather_scatter_family, _work_semantics_and_ddp, _p2p],
+                         ids=lambda f: f.__name__.strip("_"))
+def test_cuda_ranks(fn):
+    run_ranks(fn, world=_world(), device="cuda", env={"NCCL_NVLS_ENABLE": "0", "CCL_ARENA_MB": "64"}, timeout=300)
+
+
+def _blocking_same_stream(rank, world):
+    t = torch.ones(100000, device="cuda")
+    for _ in range(10):
+        dist.all_reduce(t)
+        t /= world
+    torch.cuda.synchronize()
+    assert torch.allclose(t, torch.ones_like(t))
+
+
+@pytest.mark.parametrize("env", [{"CCL_BLOCKING_WAIT": "1"}, {"CCL_SAME_STREAM": "1"}, {"TORCH_LLM_ALLREDUCE": "1"}],
+                         ids=["blocking_wait", "same_stream", "llm_allreduce"])
+def test_cuda_modes(env):
+    e = {"NCCL_NVLS_ENABLE": "0", "CCL_ARENA_MB": "64"}
+    e.update(env)
+    run_ranks(_blocking_same_stream, world=_world(), device="cuda", env=e, timeout=300)

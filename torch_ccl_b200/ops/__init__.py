@@ -1,0 +1,47 @@
+"""Fused collective + compute ops. Each runs on the CURRENT CUDA stream of the tensor's device
+(so it can be captured in a CUDA graph) through the process group's peer-memory communicator."""
+import torch
+
+from .. import _C
+
+
+def _backend(group, tensor):
+    from .. import get_backend
+
+    return get_backend(group, "cuda")
+
+
+def allreduce_residual_rmsnorm(x, residual, weight, eps=1e-5, group=None, out=None):
+    """residual <- residual + all_reduce(x); returns rmsnorm(residual) * weight, in one kernel."""
+    out = torch.empty_like(x) if out is None else out
+    _backend(group, x).fused_allreduce_residual_rmsnorm(x, residual, weight, out, eps)
+    return out
+
+
+def all_reduce_scaled(tensor, scale=1.0, group=None):
+    """In-place SUM all_reduce with the result multiplied by `scale` in the same pass."""
+    _backend(group, tensor).fused_allreduce(tensor, scale)
+    return tensor
+
+
+def reduce_scatter_cast(inp, out, scale=1.0, group=None):
+    """out = scale * sum_ranks(piece of inp); `out` may be fp32 while `inp` is bf16/f16."""
+    _backend(group, inp).fused_reduce_scatter_cast(inp, out, scale)
+    return out
+
+
+def all_gather_copy_out(shard, outs, group=None):
+    """All-gather `shard` with rank p's piece written directly into outs[p]."""
+    _backend(group, shard).fused_all_gather_copy_out(shard, list(outs))
+    return outs
+
+
+def gemm_bf16_tn(a, b, out=None, trans_out=False, dual_off=0, splitk=0, bn=0, out_dtype=None):
+    """out = a @ b.T on tcgen05 tensor cores (bf16 operands, fp32 accumulation)."""
+    m = dual_off if dual_off > 0 else a.shape[0]
+    n = b.shape[0]
+    if out is None:
+        shape = (n, m) if trans_out else (m, n)
+        out = torch.empty(shape, device=a.device, dtype=out_dtype or torch.bfloat16)
+    _C.gemm_bf16_tn(a, b, out, trans_out, dual_off, splitk, bn)
+    return out
