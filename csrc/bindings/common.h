@@ -11,5 +11,6 @@ int to_ccl_dtype(at::ScalarType t);
 ccl::KvStore make_kv(const c10::intrusive_ptr<c10d::Store>& store);
 void bind_cuda_comm(py::module& m);
 void bind_process_group(py::module& m);
+void bind_model_ops(py::module& m);
 
 }  // namespace ccl_py

@@ -56,6 +56,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("bn") = 0);
   ccl_py::bind_cuda_comm(m);
   ccl_py::bind_process_group(m);
+  ccl_py::bind_model_ops(m);
   m.def("launch_count", &ccl::launch_count);
   m.def("launch_count_reset", &ccl::launch_count_reset);
 }

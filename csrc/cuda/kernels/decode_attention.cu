@@ -1,0 +1,228 @@
+// Single-token ("decode") attention for a Llama-style decoder, fused with rotary embedding and
+// the KV-cache append: one launch per layer reads q/k/v of the new token from the packed QKV
+// projection output, rotates q and k, writes k/v into the cache at the sequence's current
+// position, and attends over positions [0, pos]. Memory-bound on the KV cache, so the work is
+// split over the sequence (flash-decoding): each CTA handles one (sequence, head, KV range) and
+// writes an un-normalised partial (running max, sum, output) to a scratch buffer; the last CTA
+// to finish a (sequence, head) combines the partials. head_dim is fixed at 128.
+//
+// Thread mapping: 8 lanes share one cache position (16 dims = 32 bytes = one sector each), so a
+// warp covers 4 positions per step and a 4-warp CTA 16.
+#include "decode_attention.h"
+
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace ccl {
+namespace {
+
+constexpr int kHD = 128;
+constexpr int kThreads = 128;
+constexpr int kGroups = kThreads / 8;  // positions in flight per CTA step
+
+__device__ __forceinline__ void load16(const __nv_bfloat16* p, float (&f)[16]) {
+  const uint4 a = reinterpret_cast<const uint4*>(p)[0];
+  const uint4 b = reinterpret_cast<const uint4*>(p)[1];
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+    f[2 * i] = __low2float(h);
+    f[2 * i + 1] = __high2float(h);
+  }
+}
+__device__ __forceinline__ void store16(__nv_bfloat16* p, const float (&f)[16]) {
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  reinterpret_cast<uint4*>(p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  reinterpret_cast<uint4*>(p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+// Rotary embedding (rotate-half convention) of the 16 dims [16j, 16j+16) of one head vector.
+// `own` holds those dims, `partner` the dims 64 away; cos/sin rows have 64 entries.
+__device__ __forceinline__ void rope16(float (&own)[16], const float (&partner)[16], const float* cosr,
+                                       const float* sinr, int j) {
+  const int base = (j & 3) * 16;  // frequency index of own dim i is (16j + i) mod 64
+  const float sign = (j < 4) ? -1.f : 1.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float c = cosr[base + i], s = sinr[base + i];
+    own[i] = own[i] * c + sign * partner[i] * s;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) decode_attention_kernel(const DecodeAttnParams p) {
+  const int split = blockIdx.x;
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int nsplit = gridDim.x;
+  const int tid = threadIdx.x;
+  const int g = tid >> 3;  // position group within the CTA
+  const int j = tid & 7;   // dim slice within the head
+  const int kvh = h / (p.n_heads / p.n_kv_heads);
+  const int pos = p.positions[b];  // the new token's position; attends over [0, pos]
+  const int total = pos + 1;
+  const int per = (total + nsplit - 1) / nsplit;
+  const int t0 = split * per;
+  const int t1 = min(total, t0 + per);
+
+  const __nv_bfloat16* qkv = p.qkv + (size_t)b * p.qkv_stride;
+  const float* cosr = p.cos + (size_t)pos * (kHD / 2);
+  const float* sinr = p.sin + (size_t)pos * (kHD / 2);
+  const int pj = j ^ 4;
+
+  // q: rotate and pre-scale
+  float q[16];
+  {
+    float partner[16];
+    load16(qkv + (size_t)h * kHD + j * 16, q);
+    load16(qkv + (size_t)h * kHD + pj * 16, partner);
+    rope16(q, partner, cosr, sinr, j);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) q[i] *= p.scale;
+  }
+
+  __nv_bfloat16* kc = p.k_cache + (((size_t)b * p.n_kv_heads + kvh) * p.max_seq) * kHD;
+  __nv_bfloat16* vc = p.v_cache + (((size_t)b * p.n_kv_heads + kvh) * p.max_seq) * kHD;
+
+  // The CTA whose range contains `pos` handles the new token from the projection output: it
+  // rotates k, keeps k/v (rounded like the cache) in shared memory for its own use and, for the
+  // first head of a KV group, appends them to the cache. No other CTA reads that position.
+  const bool owns_new = (pos >= t0 && pos < t1);
+  __shared__ float s_new_k[kHD], s_new_v[kHD];
+  if (owns_new && g == 0) {
+    float k[16], partner[16], v[16];
+    const __nv_bfloat16* kn = qkv + (size_t)(p.n_heads + kvh) * kHD;
+    const __nv_bfloat16* vn = qkv + (size_t)(p.n_heads + p.n_kv_heads + kvh) * kHD;
+    load16(kn + j * 16, k);
+    load16(kn + pj * 16, partner);
+    load16(vn + j * 16, v);
+    rope16(k, partner, cosr, sinr, j);
+    if (h % (p.n_heads / p.n_kv_heads) == 0) {
+      store16(kc + (size_t)pos * kHD + j * 16, k);
+      store16(vc + (size_t)pos * kHD + j * 16, v);
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      s_new_k[j * 16 + i] = __bfloat162float(__float2bfloat16(k[i]));
+      s_new_v[j * 16 + i] = __bfloat162float(__float2bfloat16(v[i]));
+    }
+  }
+  __syncthreads();
+
+  float m = -INFINITY, l = 0.f, o[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) o[i] = 0.f;
+
+  for (int t = t0 + g; t < t1; t += kGroups) {
+    float k[16], v[16];
+    if (t == pos) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        k[i] = s_new_k[j * 16 + i];
+        v[i] = s_new_v[j * 16 + i];
+      }
+    } else {
+      load16(kc + (size_t)t * kHD + j * 16, k);
+      load16(vc + (size_t)t * kHD + j * 16, v);
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) s += q[i] * k[i];
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    const float mn = fmaxf(m, s);
+    const float corr = __expf(m - mn);
+    const float pr = __expf(s - mn);
+    l = l * corr + pr;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) o[i] = o[i] * corr + pr * v[i];
+    m = mn;
+  }
+
+  // combine the kGroups position groups of this CTA
+  __shared__ float s_m[kGroups], s_l[kGroups], s_o[kGroups][kHD];
+  if (j == 0) {
+    s_m[g] = m;
+    s_l[g] = l;
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s_o[g][j * 16 + i] = o[i];
+  __syncthreads();
+  float M = -INFINITY;
+  for (int i = 0; i < kGroups; ++i) M = fmaxf(M, s_m[i]);
+  float L = 0.f, acc = 0.f;  // thread `tid` owns output dim tid
+  for (int i = 0; i < kGroups; ++i) {
+    const float w = (s_m[i] == -INFINITY) ? 0.f : __expf(s_m[i] - M);
+    L += s_l[i] * w;
+    acc += s_o[i][tid] * w;
+  }
+
+  __nv_bfloat16* out = p.out + (size_t)b * p.out_stride + (size_t)h * kHD;
+  if (nsplit == 1) {
+    out[tid] = __float2bfloat16(acc / L);
+    return;
+  }
+  // partial of this split: [b][h][split] -> {M, L, o[128]}
+  float* part = p.scratch + (((size_t)b * p.n_heads + h) * nsplit + split) * (kHD + 2);
+  part[2 + tid] = acc;
+  if (tid == 0) {
+    part[0] = M;
+    part[1] = L;
+  }
+  __threadfence();
+  __shared__ int s_last;
+  __syncthreads();
+  if (tid == 0) {
+    unsigned int* counter = p.counters + (size_t)b * p.n_heads + h;
+    const unsigned int prev = atomicAdd(counter, 1u);
+    s_last = (prev == (unsigned int)nsplit - 1);
+    if (s_last) *counter = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float* base = p.scratch + ((size_t)b * p.n_heads + h) * nsplit * (kHD + 2);
+  float GM = -INFINITY;
+  for (int i = 0; i < nsplit; ++i) GM = fmaxf(GM, __ldcg(base + (size_t)i * (kHD + 2)));
+  float GL = 0.f, gacc = 0.f;
+  for (int i = 0; i < nsplit; ++i) {
+    const float* pi = base + (size_t)i * (kHD + 2);
+    const float mi = __ldcg(pi);
+    const float w = (mi == -INFINITY) ? 0.f : __expf(mi - GM);
+    GL += __ldcg(pi + 1) * w;
+    gacc += __ldcg(pi + 2 + tid) * w;
+  }
+  out[tid] = __float2bfloat16(gacc / GL);
+}
+
+}  // namespace
+
+size_t decode_attention_scratch_bytes(int batch, int n_heads, int nsplit) {
+  return (size_t)batch * n_heads * nsplit * (kHD + 2) * sizeof(float);
+}
+
+int decode_attention_default_splits(int batch, int n_heads, int max_context) {
+  const int pairs = batch * n_heads;
+  int s = (2 * 148 + pairs - 1) / pairs;  // aim at >= 2 CTAs per SM
+  const int cap = (max_context + 255) / 256;  // at least 256 positions per split
+  if (s > cap) s = cap;
+  if (s < 1) s = 1;
+  if (s > 32) s = 32;
+  return s;
+}
+
+cudaError_t decode_attention(const DecodeAttnParams& p, int batch, int nsplit, cudaStream_t stream) {
+  if (p.head_dim != kHD) return cudaErrorInvalidValue;
+  if (nsplit > 1 && (!p.scratch || !p.counters)) return cudaErrorInvalidValue;
+  dim3 grid(nsplit, p.n_heads, batch);
+  decode_attention_kernel<<<grid, kThreads, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace ccl

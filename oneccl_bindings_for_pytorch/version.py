@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "b608ed1cbd4361b0cef7ef8057f5911ce91ffc21"
+git_version = "d3068b93523a41f4ef44d895d1be8cf8ff01cda8"
