@@ -181,14 +181,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: returns false when the budget (in try_wait attempts, each of which already
-// suspends for a hardware-defined interval) is exhausted.
+// Bounded wait: returns false when `budget_ns` of wall time (globaltimer) has passed. try_wait
+// itself suspends the thread for a hardware-defined interval, so the clock is read rarely.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          uint32_t max_tries = (1u << 22)) {
-  for (uint32_t i = 0; i < max_tries; ++i) {
+                                          uint64_t budget_ns = 2000000000ull) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t it = 0;
+  while (true) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((++it & 15u) == 0 && globaltimer_ns() - t0 > budget_ns) return false;
   }
-  return false;
 }
 
 // ---------------------------------------------------------------------------------------------

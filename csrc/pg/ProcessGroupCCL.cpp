@@ -457,6 +457,7 @@ c10::intrusive_ptr<Work> ProcessGroupCCL::allreduce_coalesced(std::vector<at::Te
       [&](std::function<void(ccl::cpu::ShmComm&)> fn, std::vector<at::Tensor> outs) {
         return enqueueCpu(OpType::ALLREDUCE_COALESCED, "oneccl_bindings_for_pytorch::cpu::allreduce_coalesced", std::move(fn), std::move(outs), {}, false, seq, flight__);
       });
+  CCL_TRACK_COALESCED(w);
   return w;
 }
 
@@ -603,11 +604,13 @@ c10::intrusive_ptr<Work> ProcessGroupCCL::allgather_into_tensor_coalesced(std::v
   std::vector<std::vector<at::Tensor>> outs;
   for (auto& o : outputs) outs.push_back(split_flat(o, size_));
   auto flat = outputs;
-  return allgather_pieces(*this, OpType::COALESCED, "oneccl_bindings_for_pytorch::cuda::allgather_into_tensor_coalesced", "",
+  auto w = allgather_pieces(*this, OpType::COALESCED, "oneccl_bindings_for_pytorch::cuda::allgather_into_tensor_coalesced", "",
       inputs, outs, false, flat, opTimeout(opts.timeout), on_cuda, seq, flight__, bytes__,
       [&](std::function<void(ccl::cpu::ShmComm&)> fn) {
         return enqueueCpu(OpType::COALESCED, "oneccl_bindings_for_pytorch::cpu::allgather_into_tensor_coalesced", std::move(fn), flat, {}, false, seq, flight__);
       });
+  CCL_TRACK_COALESCED(w);
+  return w;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -813,11 +816,13 @@ c10::intrusive_ptr<Work> ProcessGroupCCL::reduce_scatter_tensor_coalesced(std::v
   RECORD_FUNCTION("oneccl_bindings_for_pytorch::reduce_scatter_tensor_coalesced", to_ivalues(inputs));
   CCL_OP_PROLOGUE("reduce_scatter_tensor_coalesced", inputs[0], "", tensors_str(inputs), nbytes(inputs))
   auto outs = outputs;
-  return reduce_scatter_pieces(*this, OpType::COALESCED, "oneccl_bindings_for_pytorch::cuda::reduce_scatter_tensor_coalesced", ins, outs, opts.reduceOp,
+  auto w = reduce_scatter_pieces(*this, OpType::COALESCED, "oneccl_bindings_for_pytorch::cuda::reduce_scatter_tensor_coalesced", ins, outs, opts.reduceOp,
       opTimeout(opts.timeout), on_cuda, bytes__,
       [&](std::function<void(ccl::cpu::ShmComm&)> fn) {
         return enqueueCpu(OpType::COALESCED, "oneccl_bindings_for_pytorch::cpu::reduce_scatter_tensor_coalesced", std::move(fn), outs, {}, false, seq, flight__);
       });
+  CCL_TRACK_COALESCED(w);
+  return w;
 }
 
 // ------------------------------------------------------------------------------------------

@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "d3068b93523a41f4ef44d895d1be8cf8ff01cda8"
+git_version = "550a022a39385d31b7ca693999e752df1d5706b2"

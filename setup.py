@@ -72,7 +72,9 @@ ext = CUDAExtension(
     sources=sources,
     include_dirs=[os.path.join(ROOT, "csrc")] + nccl_inc,
     extra_compile_args={"cxx": cxx_flags, "nvcc": nvcc_flags},
-    extra_link_args=["-lrt", "-lpthread", "-ldl"],
+    # the image's g++ wrapper finds only the static libstdc++; a private copy inside the extension has
+    # uninitialised locale state (stringstream crashes), so link the shared one explicitly
+    extra_link_args=["-lrt", "-lpthread", "-ldl", "-l:libstdc++.so.6"],
 )
 
 setup(

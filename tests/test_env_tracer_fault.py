@@ -1,0 +1,122 @@
+"""Environment knobs, the verbose tracer's line format, statistics / flight recorder, and
+host-side failure detection (a rank that never joins a collective; a rank that leaves between
+steps). No GPU is faulted or hung anywhere: failures are made on the host, on CPU ranks."""
+import os
+import re
+import subprocess
+import sys
+import time
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from mp_util import ROOT, run_ranks
+
+
+def _run_py(code, env=None):
+    e = dict(os.environ)
+    e.update(env or {})
+    e["PYTHONPATH"] = ROOT + os.pathsep + e.get("PYTHONPATH", "")
+    return subprocess.run([sys.executable, "-c", code], env=e, capture_output=True, text=True, timeout=120)
+
+
+def test_env_flag_parsing_rules():
+    code = "import oneccl_bindings_for_pytorch as c, torch_ccl_b200._C as C; print(C.env())"
+    r = _run_py(code, {"CCL_BLOCKING_WAIT": "1", "CCL_SAME_STREAM": "0", "TORCH_LLM_ALLREDUCE": "1", "CCL_ARENA_MB": "32",
+                       "LOCAL_RANK": "3", "LOCAL_WORLD_SIZE": "8"})
+    assert r.returncode == 0, r.stderr
+    env = eval(r.stdout.strip().splitlines()[-1])
+    assert env["blocking_wait"] is True
+    assert env["same_stream"] is True  # implied by TORCH_LLM_ALLREDUCE
+    assert env["arena_mb"] == 32 and env["local_rank"] == 3 and env["local_world_size"] == 8
+    # "2" is an integer but not 1 -> false; a non-integer is an error naming the variable
+    r = _run_py(code, {"CCL_BLOCKING_WAIT": "2"})
+    assert eval(r.stdout.strip().splitlines()[-1])["blocking_wait"] is False
+    r = _run_py(code, {"CCL_BLOCKING_WAIT": "yes"})
+    assert r.returncode != 0 and "Invalid value for environment variable: CCL_BLOCKING_WAIT" in r.stderr
+    r = _run_py(code, {"PMI_RANK": "0", "MPI_LOCALRANKID": "1", "MPI_LOCALNRANKS": "2"})
+    env = eval(r.stdout.strip().splitlines()[-1])
+    assert env["with_mpirun"] is True and env["local_rank"] == 1 and env["local_world_size"] == 2
+
+
+def _traced(rank, world):
+    t = torch.zeros(3, 1000)
+    dist.all_reduce(t)
+    dist.broadcast(t, src=1)
+    dist.reduce(t, dst=0)
+    dist.barrier()
+
+
+def test_verbose_tracer_line_format(capfd):
+    run_ranks(_traced, world=2, env={"ONECCL_BINDINGS_FOR_PYTORCH_ENV_VERBOSE": "1"})
+    out = capfd.readouterr().out
+    # header line, then the same line with the elapsed time appended (reference: dispatch_stub.cpp:61-119)
+    assert re.search(r"oneccl_bindings_for_pytorch::cpu::allreduce: \[0/2#\d+\] \[\(cpu, \[3, 1000\]\)\]\n", out)
+    assert re.search(r"oneccl_bindings_for_pytorch::cpu::allreduce: \[1/2#\d+\] \[\(cpu, \[3, 1000\]\)\] Time elapsed \(ms\): [\d.e+-]+", out)
+    assert re.search(r"oneccl_bindings_for_pytorch::cpu::broadcast: \[0/2#\d+\] \[1->0\] ", out)
+    assert re.search(r"oneccl_bindings_for_pytorch::cpu::reduce: \[1/2#\d+\] \[1->0\] ", out)
+
+
+def _stats(rank, world):
+    import torch_ccl_b200 as ccl
+
+    ccl._C.reset_stats()
+    for _ in range(5):
+        dist.all_reduce(torch.ones(256))
+    dist.barrier()
+    st = ccl.stats()
+    assert st["cpu::allreduce"]["count"] == 5 and st["cpu::allreduce"]["bytes"] == 5 * 1024
+    assert sum(st["cpu::allreduce"]["host_us_hist"]) == 5
+    fr = ccl.flight_recorder()
+    assert "cpu::allreduce bytes=1024" in fr and "NOT COMPLETED" not in fr.split("barrier")[0]
+
+
+def test_stats_and_flight_recorder():
+    run_ranks(_stats, world=2)
+
+
+def _missing_rank(rank, world):
+    dist.barrier()
+    t = torch.ones(4)
+    if rank == 1:
+        time.sleep(4.0)  # never joins the collective in time
+        return
+    t0 = time.time()
+    with pytest.raises(dist.DistBackendError, match="Caught collective operation timeout"):
+        dist.all_reduce(t)
+    assert time.time() - t0 < 3.5, "the wait must be bounded by the group timeout"
+    pg = dist.group.WORLD._get_backend(torch.device("cpu"))
+    assert pg.error_state() != 0
+    assert "allreduce" in __import__("torch_ccl_b200").flight_recorder()
+
+
+def test_rank_that_never_joins_times_out_on_peers():
+    run_ranks(_missing_rank, world=2, env={"CCL_TEST_TIMEOUT_S": "1.5", "CCL_TEST_NO_DESTROY": "1"})
+
+
+def _leaves_between_steps(rank, world):
+    """Elastic pattern: a rank leaves between steps; the survivors learn of it on the host (store
+    heartbeat) before their next collective, drop the group and build a smaller one."""
+    store = dist.distributed_c10d._get_default_store()
+    for step in range(3):
+        t = torch.ones(8)
+        dist.all_reduce(t)
+        assert torch.all(t == world)
+    if rank == world - 1:
+        store.set("left", str(rank))
+        return
+    store.wait(["left"])
+    gone = int(store.get("left"))
+    survivors = [r for r in range(world) if r != gone]
+    import oneccl_bindings_for_pytorch  # noqa: F401
+
+    sub = dist.ProcessGroupCCL(dist.PrefixStore("regroup", store), survivors.index(rank), len(survivors))
+    t = torch.ones(8)
+    sub.allreduce([t]).wait()
+    assert torch.all(t == len(survivors))
+    sub.shutdown()
+
+
+def test_regroup_after_a_rank_leaves():
+    run_ranks(_leaves_between_steps, world=3, env={"CCL_TEST_NO_DESTROY": "1"})
