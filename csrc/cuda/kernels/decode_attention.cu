@@ -114,6 +114,7 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const Decode
   }
   __syncthreads();
 
+  const unsigned gmask = 0xffu << (8 * ((tid & 31) >> 3));
   float m = -INFINITY, l = 0.f, o[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) o[i] = 0.f;
@@ -133,9 +134,10 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const Decode
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) s += q[i] * k[i];
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    // the 4 position groups of a warp run different trip counts: synchronise per 8-lane group
+    s += __shfl_xor_sync(gmask, s, 1);
+    s += __shfl_xor_sync(gmask, s, 2);
+    s += __shfl_xor_sync(gmask, s, 4);
     const float mn = fmaxf(m, s);
     const float corr = __expf(m - mn);
     const float pr = __expf(s - mn);

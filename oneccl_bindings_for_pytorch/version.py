@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "550a022a39385d31b7ca693999e752df1d5706b2"
+git_version = "0062a956ceaa999763f2d60fc13430ca494edd86"

@@ -197,12 +197,14 @@ class TPLlamaDecoder:
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream(self.device))
         saved_pos = self.positions.clone()
+        saved_tok = self.tokens.clone()  # the step feeds its sampled ids back into self.tokens
         with torch.cuda.stream(s):
             for _ in range(2):  # warm-up outside capture (lazy inits, tensor-map cache)
                 self._decode_body(B)
         torch.cuda.current_stream(self.device).wait_stream(s)
         torch.cuda.synchronize(self.device)
         self.positions.copy_(saved_pos)
+        self.tokens.copy_(saved_tok)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=s):
             self._decode_body(B)
