@@ -228,3 +228,95 @@ cudaError_t decode_attention(const DecodeAttnParams& p, int batch, int nsplit, c
 }
 
 }  // namespace ccl
+
+// ------------------------------------------------------------------------------------------
+// Entry point that allocates nothing (see decode_attention_noalloc.h for who needs it and the
+// rules of use). It lives in this file because the scratch array below has file scope and the
+// host can only turn the array's name into a device address from the file that defines it.
+// ------------------------------------------------------------------------------------------
+#include <mutex>
+#include <string>
+
+#include "decode_attention_noalloc.h"
+
+namespace {
+
+// Split-KV partials followed by the arrival counters. In host code `g_noalloc_scratch` is only
+// a stand-in for the symbol, not a device address: the address comes from
+// cudaGetSymbolAddress, once per device.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[CCL_NOALLOC_SCRATCH_BYTES];
+
+constexpr size_t kNoallocPartialBytes = (size_t)CCL_NOALLOC_MAX_PARTIALS * 130 * 4;
+constexpr int kNoallocMaxDevices = 64;
+std::mutex g_noalloc_mu;
+void* g_noalloc_ptr[kNoallocMaxDevices] = {};
+thread_local std::string g_noalloc_error;
+
+int noalloc_fail(int code, const std::string& msg) {
+  g_noalloc_error = msg;
+  return code;
+}
+
+}  // namespace
+
+extern "C" __attribute__((visibility("default"))) const char* ccl_noalloc_last_error(void) {
+  return g_noalloc_error.c_str();
+}
+
+extern "C" __attribute__((visibility("default"))) int ccl_decode_attention_noalloc(
+    const void* qkv, long long qkv_stride, void* k_cache, void* v_cache, const int* positions, const float* cos,
+    const float* sin, void* out, long long out_stride, int batch, int n_heads, int n_kv_heads, int head_dim,
+    int max_seq, int nsplit, void* stream) {
+  g_noalloc_error.clear();
+  if (!qkv || !k_cache || !v_cache || !positions || !cos || !sin || !out)
+    return noalloc_fail(2, "ccl_decode_attention_noalloc: null pointer argument");
+  if (batch <= 0 || n_heads <= 0 || n_kv_heads <= 0 || nsplit <= 0 || max_seq <= 0 || n_heads % n_kv_heads != 0)
+    return noalloc_fail(2, "ccl_decode_attention_noalloc: batch, heads, max_seq and nsplit must be positive and n_heads a multiple of n_kv_heads");
+  if (head_dim != 128) return noalloc_fail(2, "ccl_decode_attention_noalloc: head_dim must be 128");
+  const long long partials = (long long)batch * n_heads * nsplit;
+  if (partials > CCL_NOALLOC_MAX_PARTIALS)
+    return noalloc_fail(1, "ccl_decode_attention_noalloc: batch * n_heads * nsplit = " + std::to_string(partials) +
+                               " exceeds the built-in scratch of " + std::to_string(CCL_NOALLOC_MAX_PARTIALS) +
+                               " partial results; lower nsplit or use the entry point that takes a caller-provided scratch buffer");
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return noalloc_fail(3, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
+  if (dev < 0 || dev >= kNoallocMaxDevices) return noalloc_fail(2, "ccl_decode_attention_noalloc: device index out of range");
+  void* base = nullptr;
+  {
+    // first call on this device: resolve the device address of the built-in array
+    std::lock_guard<std::mutex> g(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (e != cudaSuccess || !p) return noalloc_fail(3, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+      g_noalloc_ptr[dev] = p;
+    }
+    base = g_noalloc_ptr[dev];
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  unsigned int* counters = reinterpret_cast<unsigned int*>(static_cast<unsigned char*>(base) + kNoallocPartialBytes);
+  // the array keeps the previous call's contents: the counters must start at zero
+  e = cudaMemsetAsync(counters, 0, (size_t)batch * n_heads * sizeof(unsigned int), s);
+  if (e != cudaSuccess) return noalloc_fail(3, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
+  ccl::DecodeAttnParams p;
+  p.qkv = static_cast<const __nv_bfloat16*>(qkv);
+  p.qkv_stride = qkv_stride;
+  p.k_cache = static_cast<__nv_bfloat16*>(k_cache);
+  p.v_cache = static_cast<__nv_bfloat16*>(v_cache);
+  p.positions = positions;
+  p.cos = cos;
+  p.sin = sin;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.out_stride = out_stride;
+  p.scratch = static_cast<float*>(base);
+  p.counters = counters;
+  p.n_heads = n_heads;
+  p.n_kv_heads = n_kv_heads;
+  p.head_dim = head_dim;
+  p.max_seq = max_seq;
+  p.scale = 1.0f / sqrtf((float)head_dim);
+  e = ccl::decode_attention(p, batch, nsplit, s);
+  if (e != cudaSuccess) return noalloc_fail(3, std::string("decode_attention launch: ") + cudaGetErrorString(e));
+  return 0;
+}

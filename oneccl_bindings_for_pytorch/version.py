@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "0062a956ceaa999763f2d60fc13430ca494edd86"
+git_version = "a0b43a4f12145a3ce0a13b6cbe602832f2c5e41b"
