@@ -31,15 +31,17 @@ cudaError_t launch(const GemmDesc& d, int splitk, cudaStream_t stream) {
   const int n_tiles = (int)((d.N + BN - 1) / BN);
   const int k_iters = (int)((d.K + kBK - 1) / kBK);
 
-  constexpr size_t kSmemBudget = 200 * 1024;
-  // split-K: bounded by the cluster limit, the reduce buffer and the amount of K work
-  const int max_split = DUAL ? 4 : 8;
-  if (splitk > max_split) splitk = max_split;
-  while (splitk > 1 && (smem_bytes<BN, DUAL>(3, splitk) > kSmemBudget || k_iters / splitk < 2))
-    --splitk;
+  constexpr size_t kSmemMax = 200 * 1024;
+  // split-K: bounded by the portable cluster size and by the amount of K work per CTA
+  if (splitk > 8) splitk = 8;
+  while (splitk > 1 && k_iters / splitk < 2) --splitk;
   if (splitk < 1) splitk = 1;
+  // Narrow (decode) tiles are memory-bound: when one CTA per SM does not cover the grid, shrink
+  // the pipeline so that two CTAs fit on an SM and the whole grid is resident as one wave.
+  size_t budget = kSmemMax;
+  if (BN <= 32 && (int64_t)m_tiles * n_tiles * splitk > 148) budget = 104 * 1024;
   int stages = kMaxStages;
-  while (stages > 2 && smem_bytes<BN, DUAL>(stages, splitk) > kSmemBudget) --stages;
+  while (stages > 2 && smem_bytes<BN, DUAL>(stages, splitk) > budget) --stages;
   const int per = (k_iters + splitk - 1) / splitk;
   if (stages > per && per >= 2) stages = per;
   const size_t smem = smem_bytes<BN, DUAL>(stages, splitk);
@@ -66,9 +68,9 @@ cudaError_t launch(const GemmDesc& d, int splitk, cudaStream_t stream) {
   auto kern = gemm_kernel<BN, DUAL, OutT>;
   static thread_local size_t configured = 0;
   if (configured < smem) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget + 2048);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax + 2048);
     if (e != cudaSuccess) return e;
-    configured = kSmemBudget + 2048;
+    configured = kSmemMax + 2048;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(m_tiles, n_tiles, splitk);
@@ -119,12 +121,18 @@ cudaError_t gemm_bf16_tn(const GemmDesc& d, cudaStream_t stream) {
   int splitk = d.splitk;
   if (splitk == 0) {
     const int64_t tiles = ((d.M + 127) / 128) * ((d.N + bn - 1) / bn);
-    int sm = 148;
+    const int64_t k_iters = (d.K + 63) / 64;
     splitk = 1;
-    if (tiles < sm) {
-      splitk = (int)((sm + tiles - 1) / tiles);
+    if (bn <= 32) {
+      // memory-bound: fill two CTA slots per SM (296 in all), keeping >= 4 K-steps per CTA
+      splitk = (int)(296 / tiles);
       if (splitk > 8) splitk = 8;
-      if (bn > 64) splitk = 1;  // the DSMEM reduce buffer only pays off for narrow tiles
+      while (splitk > 1 && k_iters / splitk < 4) --splitk;
+      if (splitk < 1) splitk = 1;
+    } else if (bn <= 64 && tiles < 148) {
+      splitk = (int)(148 / tiles);
+      if (splitk > 4) splitk = 4;
+      if (splitk < 1) splitk = 1;
     }
   }
   switch (bn) {

@@ -12,9 +12,10 @@
 //     warps 2..5  epilogue; warp w owns TMEM lanes 32*(w%4) .. 32*(w%4)+31
 //
 // Optional features, all used by the tensor-parallel decode / training paths:
-//   * split-K across a thread-block cluster (cluster dim z): non-leader CTAs push their fp32
-//     partial tiles into the leader's shared memory over DSMEM, the leader sums in a fixed
-//     order (deterministic) and runs the epilogue once;
+//   * split-K across a thread-block cluster (cluster dim z) with a reduce-scatter over DSMEM:
+//     CTA r of the cluster owns rows [r*rpc, (r+1)*rpc) of the tile, every CTA pushes its fp32
+//     partial of those rows into the owner's shared memory, and each owner sums in a fixed
+//     order (deterministic) and runs the epilogue for its rows, so the epilogue is parallel too;
 //   * "dual A": a second A tile `dual_off` rows further down shares the same B tile and gets
 //     its own TMEM columns; the epilogue then emits silu(acc0) * acc1 (SwiGLU with the gate and
 //     up projections stacked in one weight matrix);
@@ -117,11 +118,15 @@ __host__ __device__ constexpr int tmem_cols() {
   while (a < c) a <<= 1;
   return a;
 }
-// Dynamic shared memory: [<=1023 B alignment slack][stages][split-K reduce buffer][barriers]
+// Rows of the 128-row tile that each CTA of a split-K cluster finalises.
+__host__ __device__ constexpr int rows_per_owner(int splitk) { return (kBM + splitk - 1) / splitk; }
+// Dynamic shared memory: [<=1023 B alignment slack][stages][split-K reduce buffer][barriers].
+// The reduce buffer holds, for the rows this CTA owns, one partial row from every other CTA.
 template <int BN, bool DUAL>
 __host__ __device__ constexpr size_t smem_bytes(int stages, int splitk) {
   return 1024 + (size_t)stages * stage_bytes<BN, DUAL>() +
-         (size_t)(splitk > 1 ? (splitk - 1) : 0) * kBM * acc_cols<BN, DUAL>() * 4 + sizeof(Barriers);
+         (size_t)(splitk > 1 ? (splitk - 1) : 0) * rows_per_owner(splitk) * acc_cols<BN, DUAL>() * 4 +
+         sizeof(Barriers);
 }
 
 template <int BN, bool DUAL, typename EpiFn>
@@ -139,8 +144,9 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const C
   const int stages = p.stages;
   float* red = reinterpret_cast<float*>(smem + (size_t)stages * kStage);
   const int nred = p.splitk > 1 ? p.splitk - 1 : 0;
+  const int rpc = rows_per_owner(p.splitk);
   Barriers* bars = reinterpret_cast<Barriers*>(reinterpret_cast<uint8_t*>(red) +
-                                               (size_t)nred * kBM * kAcc * 4);
+                                               (size_t)nred * rpc * kAcc * 4);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -233,9 +239,13 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const C
       if (p.status) atomicExch(p.status, 103);
     }
     ptx::tc_fence_after();
-    if (p.splitk > 1 && crank != 0) {
-      // push the partial tile into the leader's reduce buffer: [crank-1][col/4][row] float4
-      const uint32_t base = ptx::mapa(ptx::smem_u32(red), 0) + (crank - 1) * (kBM * kAcc * 4);
+    if (p.splitk > 1) {
+      // reduce-scatter: send this row's partial to the CTA that owns the row
+      // (buffer layout at the owner: [source slot][column group of 4][local row] float4)
+      const int owner = row / rpc;
+      const int rl = row - owner * rpc;
+      const uint32_t slot = crank < (uint32_t)owner ? crank : crank - 1;
+      const uint32_t base = ptx::mapa(ptx::smem_u32(red), (uint32_t)owner) + slot * (uint32_t)(rpc * kAcc * 4);
       for (int c = 0; c < kAcc; c += 16) {
         uint32_t r[16];
         if (n_iters > 0 && ok) {
@@ -245,11 +255,13 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const C
 #pragma unroll
           for (int j = 0; j < 16; ++j) r[j] = 0;
         }
+        if ((uint32_t)owner != crank) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float4 v = make_float4(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
-                                 __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
-          ptx::st_cluster_v4(base + (((c >> 2) + g) * kBM + row) * 16, v);
+          for (int g = 0; g < 4; ++g) {
+            float4 v = make_float4(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
+                                   __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
+            ptx::st_cluster_v4(base + (uint32_t)((((c >> 2) + g) * rpc + rl) * 16), v);
+          }
         }
       }
     }
@@ -263,10 +275,12 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const C
     ptx::tc_fence_after();
   }
 
-  if (warp >= 2 && crank == 0) {
+  if (warp >= 2) {
     const int q = warp & 3;
     const int row = q * 32 + lane;
     const bool ok = (bars->failed == 0);
+    const bool mine = (p.splitk == 1) || ((uint32_t)(row / rpc) == crank);
+    const int rl = row - (int)crank * rpc;
     for (int c = 0; c < BN; c += 16) {
       float v[16], u[16];
       {
@@ -289,26 +303,29 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const C
           for (int j = 0; j < 16; ++j) u[j] = __uint_as_float(r[j]);
         }
       }
-      for (int s = 0; s < nred; ++s) {
-        const float4* pr = reinterpret_cast<const float4*>(red + (size_t)s * kBM * kAcc);
+      if (mine) {
+        // own partial first, then the other CTAs in rank order: a fixed summation order
+        for (int s = 0; s < nred; ++s) {
+          const float4* pr = reinterpret_cast<const float4*>(red + (size_t)s * rpc * kAcc);
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float4 t = pr[((c >> 2) + g) * kBM + row];
-          v[4 * g] += t.x; v[4 * g + 1] += t.y; v[4 * g + 2] += t.z; v[4 * g + 3] += t.w;
+          for (int g = 0; g < 4; ++g) {
+            float4 t = pr[((c >> 2) + g) * rpc + rl];
+            v[4 * g] += t.x; v[4 * g + 1] += t.y; v[4 * g + 2] += t.z; v[4 * g + 3] += t.w;
+          }
+          if (DUAL) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float4 t = pr[(((BN + c) >> 2) + g) * rpc + rl];
+              u[4 * g] += t.x; u[4 * g + 1] += t.y; u[4 * g + 2] += t.z; u[4 * g + 3] += t.w;
+            }
+          }
         }
         if (DUAL) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            float4 t = pr[(((BN + c) >> 2) + g) * kBM + row];
-            u[4 * g] += t.x; u[4 * g + 1] += t.y; u[4 * g + 2] += t.z; u[4 * g + 3] += t.w;
-          }
+          for (int j = 0; j < 16; ++j) v[j] = silu(v[j]) * u[j];
         }
+        if (ok) epi(p, m0 + row, n0 + c, v);
       }
-      if (DUAL) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = silu(v[j]) * u[j];
-      }
-      if (ok) epi(p, m0 + row, n0 + c, v);
     }
   }
 
