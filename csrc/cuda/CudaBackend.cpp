@@ -18,6 +18,41 @@ using c10d::ProcessGroupCCL;
 using AsyncWork = ProcessGroupCCL::AsyncWorkCCL;
 
 namespace {
+struct EventPool {
+  std::mutex mu;
+  std::vector<cudaEvent_t> free_plain[16], free_timing[16];
+};
+EventPool& event_pool() {
+  static EventPool* p = new EventPool();  // leaked: events may be returned during static destruction
+  return *p;
+}
+}  // namespace
+
+PooledEvent::~PooledEvent() {
+  if (!ev) return;
+  EventPool& p = event_pool();
+  std::lock_guard<std::mutex> g(p.mu);
+  (timing ? p.free_timing : p.free_plain)[device & 15].push_back(ev);
+}
+
+std::shared_ptr<PooledEvent> acquire_event(int device, bool timing) {
+  auto e = std::make_shared<PooledEvent>();
+  e->timing = timing;
+  e->device = device;
+  {
+    EventPool& p = event_pool();
+    std::lock_guard<std::mutex> g(p.mu);
+    auto& v = (timing ? p.free_timing : p.free_plain)[device & 15];
+    if (!v.empty()) {
+      e->ev = v.back();
+      v.pop_back();
+    }
+  }
+  if (!e->ev) C10_CUDA_CHECK(cudaEventCreateWithFlags(&e->ev, timing ? cudaEventDefault : cudaEventDisableTiming));
+  return e;
+}
+
+namespace {
 
 [[noreturn]] void throw_dist_error(const std::string& msg) {
   throw c10::DistBackendError(c10::SourceLocation{"ccl", __FILE__, __LINE__}, msg);
@@ -61,7 +96,7 @@ class CudaWork : public AsyncWork {
         if (!m.empty()) throw_dist_error(m);
       }
     } else if (!same_stream_) {
-      end_->block(c10::cuda::getCurrentCUDAStream(device_.index()));
+      C10_CUDA_CHECK(cudaStreamWaitEvent(c10::cuda::getCurrentCUDAStream(device_.index()).stream(), end_->ev, 0));
     }
     std::exception_ptr e;
     {
@@ -73,22 +108,30 @@ class CudaWork : public AsyncWork {
   }
 
   void synchronize() override {
-    if (!same_stream_ && end_) end_->block(c10::cuda::getCurrentCUDAStream(device_.index()));
+    if (!same_stream_ && end_) C10_CUDA_CHECK(cudaStreamWaitEvent(c10::cuda::getCurrentCUDAStream(device_.index()).stream(), end_->ev, 0));
   }
 
   float getDuration() const override {
     if (!start_ || !end_ || !timed_) return -1.f;
     if (!end_->query()) return -1.f;
-    return start_->elapsed_time(*end_);
+    float ms = -1.f;
+    if (cudaEventElapsedTime(&ms, start_->ev, end_->ev) != cudaSuccess) return -1.f;
+    return ms;
   }
 
-  void completeFutureOnStream(c10::cuda::CUDAStream stream) {
-    c10::cuda::CUDAStreamGuard g(stream);
-    if (nested_) future_->markCompleted(c10::IValue(nested_outputs_));
-    else future_->markCompleted(c10::IValue(outputs_));
+  // The future of CUDA work is completed in stream order: consumers of the future synchronise
+  // with the stream the collective ran on.
+  void completeFutureNow() override {
+    if (stream_) {
+      c10::cuda::CUDAStreamGuard g(*stream_);
+      AsyncWork::completeFutureNow();
+    } else {
+      AsyncWork::completeFutureNow();
+    }
   }
 
-  std::shared_ptr<at::cuda::CUDAEvent> start_, end_;
+  std::shared_ptr<PooledEvent> start_, end_;
+  std::optional<c10::cuda::CUDAStream> stream_;
   std::shared_ptr<CudaComm> comm_;
   bool blocking_ = false, same_stream_ = false, host_blocking_ = false, timed_ = false;
   std::chrono::milliseconds timeout_{10000};
@@ -140,7 +183,8 @@ void Watchdog::loop() {
     l.unlock();
     try {
       // works complete in stream order, so waiting on the oldest one first is enough
-      while (!it.end->query()) std::this_thread::sleep_for(std::chrono::microseconds(20));
+      // a coarse poll: waiters use the event directly, the watchdog only retires work
+      while (!it.end->query()) std::this_thread::sleep_for(std::chrono::microseconds(200));
       std::string m = it.comm ? status_message(*it.comm) : std::string();
       Telemetry::get().record_complete(it.work->flight_slot, it.seq);
       if (m.empty()) {
@@ -262,6 +306,7 @@ CudaComm& CudaBackendImpl::comm(const at::Device& device) {
                                                   : (uint64_t)std::max<int64_t>(1000, std::min<int64_t>(pg_ms, 30000));
     if (env.oneshot_max_bytes >= 0) cfg.oneshot_max_bytes = (size_t)env.oneshot_max_bytes;
     cfg.max_blocks = env.max_blocks;
+    cfg.threads = std::max(32, std::min(1024, env.threads / 32 * 32));
     if (env.algo == "oneshot") cfg.algo = Algo::kOneShot;
     else if (env.algo == "twoshot") cfg.algo = Algo::kTwoShot;
     if (env.work_only) cfg.ablate = kAblateWorkOnly;
@@ -304,24 +349,26 @@ c10::intrusive_ptr<c10d::Work> CudaBackendImpl::run(c10d::OpType type, const cha
 
   c10::cuda::CUDAStream cur = c10::cuda::getCurrentCUDAStream((c10::DeviceIndex)dev);
   c10::cuda::CUDAStream stream = same ? cur : comm_stream(device);
+  work->stream_ = stream;
   if (!same) {
-    at::cuda::CUDAEvent ready;
-    ready.record(cur);
-    ready.block(stream);
+    // fork: the communication stream waits for what the caller has enqueued so far. One event
+    // per backend is enough: a wait captures the record that precedes it.
+    if (!fork_event_) fork_event_ = acquire_event(dev, false);
+    C10_CUDA_CHECK(cudaEventRecord(fork_event_->ev, cur.stream()));
+    C10_CUDA_CHECK(cudaStreamWaitEvent(stream.stream(), fork_event_->ev, 0));
   }
   if (work->timed_) {
-    work->start_ = std::make_shared<at::cuda::CUDAEvent>(cudaEventDefault);
-    work->start_->record(stream);
+    work->start_ = acquire_event(dev, true);
+    C10_CUDA_CHECK(cudaEventRecord(work->start_->ev, stream.stream()));
   }
   std::string algo;
   {
     RECORD_FUNCTION(title, std::vector<c10::IValue>{});
     algo = fn(c, stream.stream());
   }
-  work->end_ = std::make_shared<at::cuda::CUDAEvent>(work->timed_ ? cudaEventDefault : cudaEventDisableTiming);
-  work->end_->record(stream);
-  work->completeFutureOnStream(stream);
-  work->flight_slot = Telemetry::get().record_start(seq, c10d::opTypeToString(type), "cuda", bytes, algo);
+  work->end_ = acquire_event(dev, work->timed_);
+  C10_CUDA_CHECK(cudaEventRecord(work->end_->ev, stream.stream()));
+  work->flight_slot = Telemetry::get().record_start(seq, title, "cuda", bytes, algo.c_str());
 
   Watchdog::Item item;
   item.work = work;
@@ -355,9 +402,9 @@ c10::intrusive_ptr<c10d::Work> CudaBackendImpl::p2p(bool is_send, at::Tensor& te
     ncclComm_t comm = nccl_->get("world", size_, rank_, dev);
     if (!p2p_in_group_) {
       if (!pg_->sameStream()) {
-        at::cuda::CUDAEvent ready;
-        ready.record(cur);
-        ready.block(stream);
+        if (!fork_event_) fork_event_ = acquire_event(dev, false);
+        C10_CUDA_CHECK(cudaEventRecord(fork_event_->ev, cur.stream()));
+        C10_CUDA_CHECK(cudaStreamWaitEvent(stream.stream(), fork_event_->ev, 0));
       }
       nccl_->group_start();
       p2p_in_group_ = true;
@@ -368,14 +415,16 @@ c10::intrusive_ptr<c10d::Work> CudaBackendImpl::p2p(bool is_send, at::Tensor& te
     ++p2p_batch_ops_;
     p2p_batch_tensors_.push_back(tensor);
     auto w = make_work(is_send ? c10d::OpType::SEND : c10d::OpType::RECV);
-    w->finishOk();  // the real completion is the Work returned by endCoalescing
+    w->end_ = acquire_event(dev, false);  // recorded before the group runs: completion is the Work of endCoalescing
+    C10_CUDA_CHECK(cudaEventRecord(w->end_->ev, cur.stream()));
+    w->finishOk();
     return w;
   }
   auto w = make_work(is_send ? c10d::OpType::SEND : c10d::OpType::RECV);
   if (!pg_->sameStream()) {
-    at::cuda::CUDAEvent ready;
-    ready.record(cur);
-    ready.block(stream);
+    if (!fork_event_) fork_event_ = acquire_event(dev, false);
+    C10_CUDA_CHECK(cudaEventRecord(fork_event_->ev, cur.stream()));
+    C10_CUDA_CHECK(cudaStreamWaitEvent(stream.stream(), fork_event_->ev, 0));
   }
   if (peer == rank_) {
     // self send/recv: a FIFO of pending sends matched by the next self-recv
@@ -395,9 +444,9 @@ c10::intrusive_ptr<c10d::Work> CudaBackendImpl::p2p(bool is_send, at::Tensor& te
     if (is_send) nccl_->send(tensor.data_ptr(), bytes, target, comm, stream.stream());
     else nccl_->recv(tensor.data_ptr(), bytes, target, comm, stream.stream());
   }
-  w->end_ = std::make_shared<at::cuda::CUDAEvent>(cudaEventDisableTiming);
-  w->end_->record(stream);
-  w->completeFutureOnStream(stream);
+  w->stream_ = stream;
+  w->end_ = acquire_event(dev, false);
+  C10_CUDA_CHECK(cudaEventRecord(w->end_->ev, stream.stream()));
   Watchdog::Item item;
   item.work = w;
   item.end = w->end_;
@@ -423,9 +472,9 @@ c10::intrusive_ptr<c10d::Work> CudaBackendImpl::p2p_group_end() {
   w->blocking_ = pg_->blockingWait();
   w->same_stream_ = pg_->sameStream();
   w->timeout_ = pg_->timeout();
-  w->end_ = std::make_shared<at::cuda::CUDAEvent>(cudaEventDisableTiming);
-  w->end_->record(stream);
-  w->completeFutureOnStream(stream);
+  w->stream_ = stream;
+  w->end_ = acquire_event(dev, false);
+  C10_CUDA_CHECK(cudaEventRecord(w->end_->ev, stream.stream()));
   Watchdog::Item item;
   item.work = w;
   item.end = w->end_;

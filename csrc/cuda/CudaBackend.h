@@ -19,6 +19,17 @@ namespace ccl {
 
 class NcclP2P;
 
+// CUDA events are recycled through a process-wide pool: creating and destroying two or three
+// events per collective costs more host time than launching the kernel.
+struct PooledEvent {
+  cudaEvent_t ev = nullptr;
+  bool timing = false;
+  int device = 0;
+  ~PooledEvent();
+  bool query() const { return cudaEventQuery(ev) == cudaSuccess; }
+};
+std::shared_ptr<PooledEvent> acquire_event(int device, bool timing);
+
 class CudaBackendImpl {
  public:
   CudaBackendImpl(c10d::ProcessGroupCCL* pg, c10::intrusive_ptr<c10d::Store> store, int rank, int size);
@@ -54,6 +65,7 @@ class CudaBackendImpl {
   std::mutex mu_;
   std::shared_ptr<CudaComm> comm_;
   std::unique_ptr<c10::cuda::CUDAStream> stream_;
+  std::shared_ptr<PooledEvent> fork_event_;
   std::unique_ptr<NcclP2P> nccl_;
   int p2p_batch_ops_ = 0;
   bool p2p_in_group_ = false;
@@ -68,7 +80,7 @@ class Watchdog {
   static Watchdog& get();
   struct Item {
     c10::intrusive_ptr<c10d::ProcessGroupCCL::AsyncWorkCCL> work;
-    std::shared_ptr<at::cuda::CUDAEvent> end;
+    std::shared_ptr<PooledEvent> end;
     std::shared_ptr<CudaComm> comm;
     std::vector<at::Tensor> keep;
     uint64_t seq;

@@ -110,6 +110,34 @@ __device__ __forceinline__ Vec<T> finish_vec(const typename Acc<T>::type (&acc)[
   return r;
 }
 
+// acc = v[0] (op) v[1] (op) ... in rank order. The SUM case, by far the most common, avoids the
+// per-element dispatch on the reduce kind.
+template <typename T>
+__device__ __forceinline__ void reduce_ranks(const Vec<T> (&v)[kMaxRanks], int W, int op,
+                                             typename Acc<T>::type (&acc)[Vec<T>::kN]) {
+  using A = typename Acc<T>::type;
+  constexpr int N = Vec<T>::kN;
+#pragma unroll
+  for (int t = 0; t < N; ++t) acc[t] = to_acc(v[0].v[t]);
+  if (op == kSum) {
+#pragma unroll
+    for (int p = 1; p < kMaxRanks; ++p) {
+      if (p < W) {
+#pragma unroll
+        for (int t = 0; t < N; ++t) acc[t] = acc[t] + to_acc(v[p].v[t]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int p = 1; p < kMaxRanks; ++p) {
+      if (p < W) {
+#pragma unroll
+        for (int t = 0; t < N; ++t) acc[t] = Combine<A>::apply(op, acc[t], to_acc(v[p].v[t]));
+      }
+    }
+  }
+}
+
 #define CCL_GET_CTX                                                        \
   const RankCtx& ctx = EMU ? L.ctx_table[blockIdx.y] : L.ctx;              \
   const CollArgs& a = EMU ? L.args_table[blockIdx.y] : L.args;             \
@@ -156,15 +184,7 @@ __global__ void __launch_bounds__(1024) allreduce_oneshot_kernel(const __grid_co
         if (p < W) v[p] = (p == me) ? load_vec(in, j, count, al_in) : load_stage<T>(mine + (size_t)p * slot + j * 16);
       }
       A acc[N];
-#pragma unroll
-      for (int t = 0; t < N; ++t) acc[t] = to_acc(v[0].v[t]);
-#pragma unroll
-      for (int p = 1; p < kMaxRanks; ++p) {
-        if (p < W) {
-#pragma unroll
-          for (int t = 0; t < N; ++t) acc[t] = Combine<A>::apply(a.op, acc[t], to_acc(v[p].v[t]));
-        }
-      }
+      reduce_ranks<T>(v, W, a.op, acc);
       store_vec(out, j, count, al_out, finish_vec<T>(acc, a));
     }
   }
@@ -224,15 +244,7 @@ __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const __grid_co
           if (p < W) v[p] = (p == me) ? load_vec(in, vb + j, count, al_in) : load_stage<T>(regionA + ((size_t)p * stride_v + j) * 16);
         }
         A acc[N];
-#pragma unroll
-        for (int t = 0; t < N; ++t) acc[t] = to_acc(v[0].v[t]);
-#pragma unroll
-        for (int p = 1; p < kMaxRanks; ++p) {
-          if (p < W) {
-#pragma unroll
-            for (int t = 0; t < N; ++t) acc[t] = Combine<A>::apply(a.op, acc[t], to_acc(v[p].v[t]));
-          }
-        }
+        reduce_ranks<T>(v, W, a.op, acc);
         const Vec<T> res = finish_vec<T>(acc, a);
         store_stage(regionB + j * 16, res);
         if (gather_here) store_vec(out, vb + j, count, al_out, res);
@@ -301,15 +313,7 @@ __global__ void __launch_bounds__(1024) reduce_scatter_kernel(const __grid_const
           if (p < W) v[p] = (p == me) ? load_vec(mypiece, vb + j, mycount, al_mine) : load_stage<TIn>(regionA + ((size_t)p * stride_v + j) * 16);
         }
         A acc[N];
-#pragma unroll
-        for (int t = 0; t < N; ++t) acc[t] = to_acc(v[0].v[t]);
-#pragma unroll
-        for (int p = 1; p < kMaxRanks; ++p) {
-          if (p < W) {
-#pragma unroll
-            for (int t = 0; t < N; ++t) acc[t] = Combine<A>::apply(a.op, acc[t], to_acc(v[p].v[t]));
-          }
-        }
+        reduce_ranks<TIn>(v, W, a.op, acc);
         const size_t e0 = (vb + j) * N;
         if constexpr (sizeof(TOut) == sizeof(TIn)) {
           store_vec(reinterpret_cast<TIn*>(out), vb + j, mycount, al_out, finish_vec<TIn>(acc, a));

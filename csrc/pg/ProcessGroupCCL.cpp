@@ -92,18 +92,30 @@ void ProcessGroupCCL::AsyncWorkCCL::makeFuture(bool nested, const std::vector<c1
 void ProcessGroupCCL::AsyncWorkCCL::setOutputs(std::vector<at::Tensor> outs) {
   outputs_ = std::move(outs);
   nested_ = false;
-  std::vector<c10::Device> devs;
-  if (!outputs_.empty() && outputs_[0].is_cuda()) devs.push_back(outputs_[0].device());
-  makeFuture(false, devs);
 }
 
 void ProcessGroupCCL::AsyncWorkCCL::setOutputs(std::vector<std::vector<at::Tensor>> outs) {
   nested_outputs_ = std::move(outs);
   nested_ = true;
-  std::vector<c10::Device> devs;
-  if (!nested_outputs_.empty() && !nested_outputs_[0].empty() && nested_outputs_[0][0].is_cuda())
-    devs.push_back(nested_outputs_[0][0].device());
-  makeFuture(true, devs);
+}
+
+void ProcessGroupCCL::AsyncWorkCCL::completeFutureNow() {
+  if (nested_) future_->markCompleted(c10::IValue(nested_outputs_));
+  else future_->markCompleted(c10::IValue(outputs_));
+}
+
+c10::intrusive_ptr<c10::ivalue::Future> ProcessGroupCCL::AsyncWorkCCL::getFuture() {
+  std::lock_guard<std::mutex> g(fut_mu_);
+  if (!future_) {
+    std::vector<c10::Device> devs;
+    if (!nested_ && !outputs_.empty() && outputs_[0].is_cuda()) devs.push_back(outputs_[0].device());
+    if (nested_ && !nested_outputs_.empty() && !nested_outputs_[0].empty() && nested_outputs_[0][0].is_cuda())
+      devs.push_back(nested_outputs_[0][0].device());
+    makeFuture(nested_, devs);
+    if (done_err_) future_->setError(done_err_);
+    else if (done_ok_ || !devs.empty()) completeFutureNow();  // CUDA work: stream-ordered completion
+  }
+  return future_;
 }
 
 std::vector<at::Tensor> ProcessGroupCCL::AsyncWorkCCL::result() {
@@ -115,15 +127,20 @@ std::vector<at::Tensor> ProcessGroupCCL::AsyncWorkCCL::result() {
 }
 
 void ProcessGroupCCL::AsyncWorkCCL::finishOk() {
-  if (future_ && !future_->completed()) {
-    if (nested_) future_->markCompleted(c10::IValue(nested_outputs_));
-    else future_->markCompleted(c10::IValue(outputs_));
+  {
+    std::lock_guard<std::mutex> g(fut_mu_);
+    done_ok_ = true;
+    if (future_ && !future_->completed()) completeFutureNow();
   }
   finish();
 }
 
 void ProcessGroupCCL::AsyncWorkCCL::finishError(std::exception_ptr e) {
-  if (future_ && !future_->completed()) future_->setError(e);
+  {
+    std::lock_guard<std::mutex> g(fut_mu_);
+    done_err_ = e;
+    if (future_ && !future_->completed()) future_->setError(e);
+  }
   finish(e);
 }
 
@@ -295,16 +312,17 @@ c10::intrusive_ptr<Work> ProcessGroupCCL::enqueueCpuP2P(OpType type, const char*
 #define CCL_OP_PROLOGUE(OPNAME, FIRST_TENSOR, FLOW, TENSORS_STR, BYTES)                                  \
   const uint64_t seq = nextSeq();                                                                        \
   const bool on_cuda = (FIRST_TENSOR).is_cuda();                                                         \
-  const std::string devname = on_cuda ? "cuda" : "cpu";                                                  \
-  ccl::OpTrace trace__(Env::get().verbose != 0, devname, OPNAME, rank_, size_, seq, FLOW,                \
-                       Env::get().verbose != 0 ? (TENSORS_STR) : std::string());                         \
-  const double t_host0__ = Telemetry::now_us();                                                          \
+  const char* devname = on_cuda ? "cuda" : "cpu";                                                        \
+  const bool verbose__ = Env::get().verbose != 0;                                                        \
+  ccl::OpTrace trace__(verbose__, devname, OPNAME, rank_, size_, seq, verbose__ ? std::string(FLOW) : std::string(), \
+                       verbose__ ? (TENSORS_STR) : std::string());                                       \
   const uint64_t bytes__ = (BYTES);                                                                      \
-  const size_t flight__ = Telemetry::get().record_start(seq, OPNAME, devname, bytes__, "");              \
+  /* CUDA ops are entered into the flight recorder by the launcher, with the algorithm chosen */         \
+  const size_t flight__ = on_cuda ? 0 : Telemetry::get().record_start(seq, OPNAME, devname, bytes__, ""); \
   struct HostTimer__ {                                                                                   \
-    const char* op; const std::string& dev; uint64_t bytes; double t0;                                   \
+    const char* op; const char* dev; uint64_t bytes; double t0;                                          \
     ~HostTimer__() { Telemetry::get().record_host_time(op, dev, bytes, "", Telemetry::now_us() - t0); }  \
-  } host_timer__{OPNAME, devname, bytes__, t_host0__};                                                   \
+  } host_timer__{OPNAME, devname, bytes__, Telemetry::now_us()};                                         \
   (void)flight__;
 
 static std::string flow_str(int from, int to) {

@@ -42,7 +42,9 @@ class ProcessGroupCCL : public Backend {
     AsyncWorkCCL(int rank, OpType op, const char* title, uint64_t seq);
     ~AsyncWorkCCL() override;
 
-    c10::intrusive_ptr<c10::ivalue::Future> getFuture() override { return future_; }
+    // The future is created on first request (most callers only wait()); for CUDA work it is
+    // completed in stream order, for CPU work when the operation has run.
+    c10::intrusive_ptr<c10::ivalue::Future> getFuture() override;
     std::vector<at::Tensor> result() override;
     uint64_t getSequencenumber() const override { return seq_; }
     float getDuration() const override { return duration_ms_; }
@@ -60,6 +62,10 @@ class ProcessGroupCCL : public Backend {
 
    protected:
     void makeFuture(bool nested, const std::vector<c10::Device>& devices);
+    virtual void completeFutureNow();  // marks future_ completed with the outputs
+    std::mutex fut_mu_;
+    bool done_ok_ = false;
+    std::exception_ptr done_err_;
     c10::intrusive_ptr<c10::ivalue::Future> future_;
     std::vector<at::Tensor> outputs_;
     std::vector<std::vector<at::Tensor>> nested_outputs_;

@@ -1,6 +1,7 @@
 #include "pg/Telemetry.h"
 
 #include <cmath>
+#include <cstdio>
 #include <iostream>
 
 namespace ccl {
@@ -25,7 +26,7 @@ void format_tensors(std::ostream& os, const std::vector<std::vector<at::Tensor>>
   os << "]";
 }
 
-OpTrace::OpTrace(bool enabled, const std::string& dev, const char* op, int rank, int size, uint64_t seq,
+OpTrace::OpTrace(bool enabled, const char* dev, const char* op, int rank, int size, uint64_t seq,
                  const std::string& flow, const std::string& tensors)
     : enabled_(enabled) {
   if (!enabled_) return;
@@ -54,8 +55,8 @@ double Telemetry::now_us() {
   return std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
 }
 
-size_t Telemetry::record_start(uint64_t seq, const std::string& op, const std::string& device, uint64_t bytes,
-                               const std::string& algo) {
+size_t Telemetry::record_start(uint64_t seq, const char* op, const char* device, uint64_t bytes,
+                               const char* algo) {
   std::lock_guard<std::mutex> g(mu_);
   const size_t slot = next_;
   FlightEntry& e = ring_[slot];
@@ -63,7 +64,7 @@ size_t Telemetry::record_start(uint64_t seq, const std::string& op, const std::s
   e.op = op;
   e.device = device;
   e.bytes = bytes;
-  e.algo = algo;
+  std::snprintf(e.algo, sizeof(e.algo), "%s", algo ? algo : "");
   e.t_enqueue_us = now_us();
   e.t_complete_us = -1;
   next_ = (next_ + 1) % kRing;
@@ -71,17 +72,17 @@ size_t Telemetry::record_start(uint64_t seq, const std::string& op, const std::s
   return slot;
 }
 
-void Telemetry::record_host_time(const std::string& op, const std::string& device, uint64_t bytes,
-                                 const std::string& algo, double host_us) {
+void Telemetry::record_host_time(const char* op, const char* device, uint64_t bytes, const char* algo,
+                                 double host_us) {
   std::lock_guard<std::mutex> g(mu_);
-  OpStat& s = stats_[device + "::" + op];
+  OpStat& s = stats_[std::make_pair(device, op)];
   s.count++;
   s.bytes += bytes;
   s.host_us_total += host_us;
   int b = host_us < 1 ? 0 : (int)std::floor(std::log2(host_us));
   if (b > 23) b = 23;
   s.host_us_hist[b]++;
-  if (!algo.empty()) s.algos[algo]++;
+  if (algo && algo[0]) s.algos[algo]++;
 }
 
 void Telemetry::record_complete(size_t slot, uint64_t seq) {
@@ -91,7 +92,16 @@ void Telemetry::record_complete(size_t slot, uint64_t seq) {
 
 std::map<std::string, OpStat> Telemetry::stats() const {
   std::lock_guard<std::mutex> g(mu_);
-  return stats_;
+  std::map<std::string, OpStat> out;
+  for (const auto& kv : stats_) {
+    OpStat& d = out[std::string(kv.first.first) + "::" + kv.first.second];
+    d.count += kv.second.count;
+    d.bytes += kv.second.bytes;
+    d.host_us_total += kv.second.host_us_total;
+    for (size_t i = 0; i < d.host_us_hist.size(); ++i) d.host_us_hist[i] += kv.second.host_us_hist[i];
+    for (const auto& a : kv.second.algos) d.algos[a.first] += a.second;
+  }
+  return out;
 }
 
 std::vector<FlightEntry> Telemetry::flight() const {
@@ -107,7 +117,7 @@ std::string Telemetry::dump_flight() const {
   os << "ccl flight recorder (oldest first):\n";
   for (const auto& e : flight()) {
     os << "  #" << e.seq << " " << e.device << "::" << e.op << " bytes=" << e.bytes;
-    if (!e.algo.empty()) os << " algo=" << e.algo;
+    if (e.algo[0]) os << " algo=" << e.algo;
     os << " enqueued@" << (uint64_t)e.t_enqueue_us << "us";
     if (e.t_complete_us >= 0) os << " completed@" << (uint64_t)e.t_complete_us << "us";
     else os << " NOT COMPLETED";

@@ -27,7 +27,7 @@ void format_tensors(std::ostream& os, const std::vector<std::vector<at::Tensor>>
 // when ONECCL_BINDINGS_FOR_PYTORCH_ENV_VERBOSE is non-zero.
 class OpTrace {
  public:
-  OpTrace(bool enabled, const std::string& dev, const char* op, int rank, int size, uint64_t seq,
+  OpTrace(bool enabled, const char* dev, const char* op, int rank, int size, uint64_t seq,
           const std::string& flow, const std::string& tensors);
   ~OpTrace();
 
@@ -47,10 +47,10 @@ struct OpStat {
 
 struct FlightEntry {
   uint64_t seq = 0;
-  std::string op;
-  std::string device;
+  const char* op = "";      // string literals: recording an op allocates nothing
+  const char* device = "";
   uint64_t bytes = 0;
-  std::string algo;
+  char algo[16] = {0};
   double t_enqueue_us = 0;   // since process start
   double t_complete_us = -1;  // -1: not completed yet
 };
@@ -59,10 +59,9 @@ class Telemetry {
  public:
   static Telemetry& get();
   // Returns the slot index of the flight-recorder entry.
-  size_t record_start(uint64_t seq, const std::string& op, const std::string& device, uint64_t bytes,
-                      const std::string& algo);
-  void record_host_time(const std::string& op, const std::string& device, uint64_t bytes,
-                        const std::string& algo, double host_us);
+  // `op` and `device` must be string literals (their addresses are kept).
+  size_t record_start(uint64_t seq, const char* op, const char* device, uint64_t bytes, const char* algo);
+  void record_host_time(const char* op, const char* device, uint64_t bytes, const char* algo, double host_us);
   void record_complete(size_t slot, uint64_t seq);
   std::map<std::string, OpStat> stats() const;
   std::vector<FlightEntry> flight() const;
@@ -73,7 +72,7 @@ class Telemetry {
  private:
   static constexpr size_t kRing = 256;
   mutable std::mutex mu_;
-  std::map<std::string, OpStat> stats_;
+  std::map<std::pair<const char*, const char*>, OpStat> stats_;  // keyed by literal addresses
   std::array<FlightEntry, kRing> ring_;
   size_t next_ = 0;
   size_t filled_ = 0;

@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "bf21273d28bdf987e048743f2dbd7f1f65ffdddb"
+git_version = "d32e83a6841375b2104aba14274413680d05943a"
