@@ -222,6 +222,8 @@ void bind_cuda_comm(py::module& m) {
             cfg.half_bytes = (size_t)half_bytes;
             cfg.spin_timeout_ms = (uint64_t)spin_ms;
             cfg.max_blocks = max_blocks;
+            cfg.threads = 512;
+            cfg.oneshot_max_bytes = 512 << 10;
             auto p = std::make_unique<PyComm>();
             p->comm = std::make_unique<CudaComm>(world, (int)c10::cuda::current_device(), cfg);
             return p;

@@ -27,6 +27,16 @@ struct DeviceGuard {
   }
 };
 
+}  // namespace
+
+size_t default_oneshot_max(int world) {
+  if (world <= 2) return 8u << 20;
+  if (world <= 4) return 1u << 20;
+  return 512u << 10;
+}
+
+namespace {
+
 size_t arena_size(size_t half) { return 2 * half + kFlagBytes + kStateBytes; }
 
 void fill_ctx(RankCtx& c, int rank, int world, const std::vector<void*>& bases, size_t half,
@@ -65,6 +75,7 @@ CudaComm::CudaComm(int rank, int world, int device, const CommConfig& cfg, KvSto
   if (world < 1 || world > kMaxRanks) throw std::runtime_error("ccl: CUDA communicators support 1..8 ranks");
   DeviceGuard g(device_);
   cfg_.half_bytes = round_up(cfg_.half_bytes, 1 << 20);
+  if (cfg_.oneshot_max_bytes == 0) cfg_.oneshot_max_bytes = default_oneshot_max(world_);
   arena_bytes_ = arena_size(cfg_.half_bytes);
   void* base = nullptr;
   check(cudaMalloc(&base, arena_bytes_), "cudaMalloc(arena)");
@@ -113,6 +124,7 @@ CudaComm::CudaComm(int world, int device, const CommConfig& cfg)
   if (world < 1 || world > kMaxRanks) throw std::runtime_error("ccl: CUDA communicators support 1..8 ranks");
   DeviceGuard g(device_);
   cfg_.half_bytes = round_up(cfg_.half_bytes, 1 << 20);
+  if (cfg_.oneshot_max_bytes == 0) cfg_.oneshot_max_bytes = default_oneshot_max(world_);
   arena_bytes_ = arena_size(cfg_.half_bytes);
   for (int r = 0; r < world_; ++r) {
     void* base = nullptr;
@@ -198,6 +210,15 @@ LaunchCfg CudaComm::launch_cfg(int nblocks, int nthreads, cudaStream_t stream) c
   return c;
 }
 
+// Small messages get small CTAs (cheaper to launch and to synchronise).
+static int threads_for(size_t vecs, int nblocks, int max_threads) {
+  size_t per = (vecs + (size_t)nblocks - 1) / (size_t)std::max(1, nblocks);
+  size_t t = (per + 31) / 32 * 32;
+  if (t < 128) t = 128;
+  if (t > (size_t)max_threads) t = max_threads;
+  return (int)t;
+}
+
 int CudaComm::blocks_for(size_t vecs, int cap) const {
   const size_t per_block = (size_t)cfg_.threads * 4;
   size_t b = (vecs + per_block - 1) / per_block;
@@ -229,13 +250,13 @@ cudaError_t CudaComm::allreduce(int dtype, std::vector<CollArgs> args, cudaStrea
   cudaError_t e;
   LaunchCfg lc;
   if (algo == Algo::kOneShot) {
-    lc = launch_cfg(blocks_for(nvec, 32), cfg_.threads, stream);
+    lc = launch_cfg(blocks_for(nvec, cfg_.max_blocks), threads_for(nvec, blocks_for(nvec, cfg_.max_blocks), cfg_.threads), stream);
     e = launch_allreduce_oneshot(dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
   } else {
     size_t stride = cfg_.half_bytes / (16 * (size_t)(world_ + 1));
     stride = stride / 8 * 8;
     for (auto& a : args) a.chunk_vecs = stride;
-    lc = launch_cfg(blocks_for((nvec + world_ - 1) / world_, cfg_.max_blocks), cfg_.threads, stream);
+    lc = launch_cfg(blocks_for((nvec + world_ - 1) / world_, cfg_.max_blocks), threads_for((nvec + world_ - 1) / world_, blocks_for((nvec + world_ - 1) / world_, cfg_.max_blocks), cfg_.threads), stream);
     e = launch_allreduce_twoshot(dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
   }
   if (chosen) *chosen = AlgoChoice{algo, lc.nblocks, lc.nthreads};
@@ -253,7 +274,7 @@ cudaError_t CudaComm::reduce(int dtype, std::vector<CollArgs> args, cudaStream_t
     a.chunk_vecs = stride;
     a.ablate = cfg_.ablate;
   }
-  LaunchCfg lc = launch_cfg(blocks_for((nvec + world_ - 1) / world_, cfg_.max_blocks), cfg_.threads, stream);
+  LaunchCfg lc = launch_cfg(blocks_for((nvec + world_ - 1) / world_, cfg_.max_blocks), threads_for((nvec + world_ - 1) / world_, blocks_for((nvec + world_ - 1) / world_, cfg_.max_blocks), cfg_.threads), stream);
   cudaError_t e = launch_allreduce_twoshot(dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
   if (e == cudaSuccess) ++launches_;
   return e;
@@ -275,7 +296,7 @@ cudaError_t CudaComm::reduce_scatter(int in_dtype, int out_dtype, std::vector<Co
     a.rounds = rounds;
     a.ablate = cfg_.ablate;
   }
-  LaunchCfg lc = launch_cfg(blocks_for(std::min(maxv, stride), cfg_.max_blocks), cfg_.threads, stream);
+  LaunchCfg lc = launch_cfg(blocks_for(std::min(maxv, stride), cfg_.max_blocks), threads_for(std::min(maxv, stride), blocks_for(std::min(maxv, stride), cfg_.max_blocks), cfg_.threads), stream);
   cudaError_t e = launch_reduce_scatter(in_dtype, out_dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
   if (e == cudaSuccess) ++launches_;
   return e;
@@ -298,7 +319,7 @@ cudaError_t CudaComm::all_gather(std::vector<CollArgs> args, cudaStream_t stream
     a.mode = mode;
     a.ablate = cfg_.ablate;
   }
-  LaunchCfg lc = launch_cfg(blocks_for(std::min(maxv, stride), cfg_.max_blocks), cfg_.threads, stream);
+  LaunchCfg lc = launch_cfg(blocks_for(std::min(maxv, stride), cfg_.max_blocks), threads_for(std::min(maxv, stride), blocks_for(std::min(maxv, stride), cfg_.max_blocks), cfg_.threads), stream);
   cudaError_t e = launch_all_gather(emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
   if (e == cudaSuccess) ++launches_;
   return e;
@@ -321,7 +342,7 @@ cudaError_t CudaComm::all_to_all(std::vector<CollArgs> args, bool uneven, cudaSt
     a.rounds = rounds;
     a.ablate = cfg_.ablate;
   }
-  LaunchCfg lc = launch_cfg(blocks_for(std::min(std::max(maxv, (size_t)1), stride), cfg_.max_blocks), cfg_.threads, stream);
+  LaunchCfg lc = launch_cfg(blocks_for(std::min(std::max(maxv, (size_t)1), stride), cfg_.max_blocks), threads_for(std::min(std::max(maxv, (size_t)1), stride), blocks_for(std::min(std::max(maxv, (size_t)1), stride), cfg_.max_blocks), cfg_.threads), stream);
   if (uneven) lc.nblocks = std::max(1, std::min(cfg_.max_blocks, emulated_ ? std::max(1, 128 / world_) : cfg_.max_blocks) / 2);
   cudaError_t e = launch_all_to_all(emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
   if (e == cudaSuccess) ++launches_;
@@ -341,7 +362,7 @@ cudaError_t CudaComm::rooted(std::vector<CollArgs> args, cudaStream_t stream) {
     a.rounds = rounds;
     a.ablate = cfg_.ablate;
   }
-  LaunchCfg lc = launch_cfg(blocks_for(std::min(maxv, stride), cfg_.max_blocks), cfg_.threads, stream);
+  LaunchCfg lc = launch_cfg(blocks_for(std::min(maxv, stride), cfg_.max_blocks), threads_for(std::min(maxv, stride), blocks_for(std::min(maxv, stride), cfg_.max_blocks), cfg_.threads), stream);
   cudaError_t e = launch_rooted(emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
   if (e == cudaSuccess) ++launches_;
   return e;

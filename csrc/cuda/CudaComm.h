@@ -33,13 +33,17 @@ enum class Algo : int { kAuto = 0, kOneShot = 1, kTwoShot = 2, kNvls = 3 };
 struct CommConfig {
   size_t half_bytes = 256ull << 20;   // one staging half per rank (arena = 2 halves + flags)
   uint64_t spin_timeout_ms = 30000;   // device-side wait budget
-  size_t oneshot_max_bytes = 512 << 10;
+  size_t oneshot_max_bytes = 0;        // 0: pick from the world size (see default_oneshot_max)
   size_t ag_push_max_bytes = 256 << 10;  // per-piece size below which all_gather pushes
-  int max_blocks = 64;                // CTAs for bandwidth-bound collectives
-  int threads = 512;
+  int max_blocks = 128;               // CTAs for bandwidth-bound collectives
+  int threads = 1024;
   Algo algo = Algo::kAuto;
   int ablate = kAblateNone;
 };
+
+// One-shot all_reduce moves (W-1)*S bytes into every GPU, two-shot 2*S*(W-1)/W: with two ranks
+// they move the same, with eight the crossover is a few hundred KB (measured on B200/NVSwitch).
+size_t default_oneshot_max(int world);
 
 struct AlgoChoice {
   Algo algo;

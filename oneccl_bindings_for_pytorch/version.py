@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "d32e83a6841375b2104aba14274413680d05943a"
+git_version = "4f8681f50a5ae32deca34fd05bcf5c8c5c7d04ba"
