@@ -201,6 +201,46 @@ struct PyComm {
        "allreduce_residual_rmsnorm");
   }
 
+  // a[r]: [M, K_r]; b[r]: [N, K_r]; out[r]: [M/W, N]
+  void gemm_rs(std::vector<at::Tensor> as, std::vector<at::Tensor> bs, std::vector<at::Tensor> outs) {
+    check_n(as.size());
+    std::vector<ccl::GemmRsArgs> args(as.size());
+    for (size_t i = 0; i < as.size(); ++i) {
+      TORCH_CHECK(as[i].scalar_type() == at::kBFloat16 && bs[i].scalar_type() == at::kBFloat16 && outs[i].scalar_type() == at::kBFloat16, "bf16 tensors required");
+      TORCH_CHECK(as[i].stride(1) == 1 && bs[i].stride(1) == 1 && outs[i].is_contiguous(), "K-contiguous operands, contiguous output");
+      args[i].a = as[i].data_ptr();
+      args[i].b = bs[i].data_ptr();
+      args[i].out = outs[i].data_ptr();
+      args[i].M = as[i].size(0);
+      args[i].K = as[i].size(1);
+      args[i].N = bs[i].size(0);
+      args[i].lda = as[i].stride(0);
+      args[i].ldb = bs[i].stride(0);
+      TORCH_CHECK(outs[i].size(0) * comm->world() == args[i].M && outs[i].size(1) == args[i].N, "out must be [M/world, N]");
+    }
+    cu(comm->gemm_rs(args, stream()), "gemm_rs");
+  }
+  // a_shard[r]: [M/W, K]; b[r]: [N_r, K]; out[r]: [M, N_r]
+  void ag_gemm(std::vector<at::Tensor> as, std::vector<at::Tensor> bs, std::vector<at::Tensor> outs) {
+    check_n(as.size());
+    std::vector<ccl::AgGemmArgs> args(as.size());
+    for (size_t i = 0; i < as.size(); ++i) {
+      TORCH_CHECK(as[i].scalar_type() == at::kBFloat16 && bs[i].scalar_type() == at::kBFloat16 && outs[i].scalar_type() == at::kBFloat16, "bf16 tensors required");
+      TORCH_CHECK(as[i].is_contiguous() && bs[i].stride(1) == 1 && outs[i].stride(1) == 1, "packed A shard, K-contiguous B");
+      args[i].a_shard = as[i].data_ptr();
+      args[i].b = bs[i].data_ptr();
+      args[i].out = outs[i].data_ptr();
+      args[i].M = as[i].size(0) * comm->world();
+      args[i].K = as[i].size(1);
+      args[i].N = bs[i].size(0);
+      args[i].lda = as[i].stride(0);
+      args[i].ldb = bs[i].stride(0);
+      args[i].ldo = outs[i].stride(0);
+      TORCH_CHECK(outs[i].size(0) == args[i].M && outs[i].size(1) == args[i].N, "out must be [M, N]");
+    }
+    cu(comm->ag_gemm(args, stream()), "ag_gemm");
+  }
+
   std::vector<int> status() {
     int r = 0, p = 0, ph = 0;
     int code = comm->poll_status(&r, &p, &ph);
@@ -265,6 +305,8 @@ void bind_cuda_comm(py::module& m) {
       .def("scatter", &PyComm::scatter)
       .def("barrier", &PyComm::barrier)
       .def("allreduce_residual_rmsnorm", &PyComm::allreduce_residual_rmsnorm)
+      .def("gemm_rs", &PyComm::gemm_rs)
+      .def("ag_gemm", &PyComm::ag_gemm)
       .def("status", &PyComm::status)
       .def("clear_status", [](PyComm& c) { c.comm->clear_status(); });
 }

@@ -167,6 +167,45 @@ void bind_process_group(py::module& m) {
              }
              C10_CUDA_CHECK(c.all_gather({a}, c10::cuda::getCurrentCUDAStream()));
            })
+      .def("fused_gemm_rs",
+           // out[M/W, N] = this rank's rows of sum over ranks of a[M, K_local] @ b[N, K_local]^T
+           [](ProcessGroupCCL& pg, const at::Tensor& a, const at::Tensor& b, at::Tensor& out) {
+             auto& c = cuda_comm_of(pg, a);
+             c10::cuda::CUDAGuard g(a.device());
+             TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16, "bf16 tensors required");
+             TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && out.is_contiguous(), "K-contiguous operands, contiguous output");
+             ccl::GemmRsArgs r;
+             r.a = a.data_ptr();
+             r.b = b.data_ptr();
+             r.out = out.data_ptr();
+             r.M = a.size(0);
+             r.K = a.size(1);
+             r.N = b.size(0);
+             r.lda = a.stride(0);
+             r.ldb = b.stride(0);
+             TORCH_CHECK(out.size(0) * c.world() == r.M && out.size(1) == r.N, "out must be [M/world, N]");
+             C10_CUDA_CHECK(c.gemm_rs({r}, c10::cuda::getCurrentCUDAStream()));
+           })
+      .def("fused_ag_gemm",
+           // out[M, N_local] = all_gather(a_shard)[M, K] @ b[N_local, K]^T
+           [](ProcessGroupCCL& pg, const at::Tensor& a_shard, const at::Tensor& b, at::Tensor& out) {
+             auto& c = cuda_comm_of(pg, a_shard);
+             c10::cuda::CUDAGuard g(a_shard.device());
+             TORCH_CHECK(a_shard.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16, "bf16 tensors required");
+             TORCH_CHECK(a_shard.is_contiguous() && b.stride(1) == 1 && out.stride(1) == 1, "packed A shard, K-contiguous B");
+             ccl::AgGemmArgs r;
+             r.a_shard = a_shard.data_ptr();
+             r.b = b.data_ptr();
+             r.out = out.data_ptr();
+             r.M = a_shard.size(0) * c.world();
+             r.K = a_shard.size(1);
+             r.N = b.size(0);
+             r.lda = a_shard.stride(0);
+             r.ldb = b.stride(0);
+             r.ldo = out.stride(0);
+             TORCH_CHECK(out.size(0) == r.M && out.size(1) == r.N, "out must be [M, N]");
+             C10_CUDA_CHECK(c.ag_gemm({r}, c10::cuda::getCurrentCUDAStream()));
+           })
       .def("cuda_comm_status", [](ProcessGroupCCL& pg, const at::Tensor& t) {
         auto& c = cuda_comm_of(pg, t);
         int r = 0, p = 0, ph = 0;

@@ -378,6 +378,44 @@ cudaError_t CudaComm::barrier(cudaStream_t stream) {
   return e;
 }
 
+cudaError_t CudaComm::gemm_rs(const std::vector<GemmRsArgs>& args, cudaStream_t stream) {
+  CCL_CHECK_ARGS(args)
+  DeviceGuard g(device_);
+  // every rank's GEMM only pushes and signals; the reduce kernels wait. Played one rank after
+  // the other in emulation, which is safe because the pushes never wait.
+  for (int i = 0; i < nctx(); ++i) {
+    cudaError_t e = launch_gemm_rs(host_ctx_[i], args[i], stream);
+    if (e != cudaSuccess) return e;
+    ++launches_;
+  }
+  for (int i = 0; i < nctx(); ++i) {
+    const size_t nvec = (size_t)(args[i].M / world_) * args[i].N * 2 / 16;
+    cudaError_t e = launch_gemm_rs_reduce(host_ctx_[i], args[i], blocks_for(nvec, 64), stream);
+    if (e != cudaSuccess) return e;
+    ++launches_;
+  }
+  return cudaSuccess;
+}
+
+cudaError_t CudaComm::ag_gemm(const std::vector<AgGemmArgs>& args, cudaStream_t stream) {
+  CCL_CHECK_ARGS(args)
+  DeviceGuard g(device_);
+  const int ncomm = 8;
+  if (!emulated_) {
+    cudaError_t e = launch_ag_gemm(host_ctx_[0], args[0], 0, ncomm, stream);
+    if (e == cudaSuccess) ++launches_;
+    return e;
+  }
+  for (int mode = 1; mode <= 2; ++mode) {
+    for (int i = 0; i < nctx(); ++i) {
+      cudaError_t e = launch_ag_gemm(host_ctx_[i], args[i], mode, ncomm, stream);
+      if (e != cudaSuccess) return e;
+      ++launches_;
+    }
+  }
+  return cudaSuccess;
+}
+
 cudaError_t CudaComm::barrier_single_rank(int i, cudaStream_t stream) {
   DeviceGuard g(device_);
   if (i < 0 || i >= nctx()) return cudaErrorInvalidValue;

@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "cuda/kernels/collectives.h"
+#include "cuda/kernels/gemm_collective.h"
 
 namespace ccl {
 
@@ -90,6 +91,10 @@ class CudaComm {
   // ranks' flags (which nothing sets) runs into the bounded-wait budget and reports a timeout.
   cudaError_t barrier_single_rank(int i, cudaStream_t stream);
   cudaError_t allreduce_residual_rmsnorm(int dtype, std::vector<FusedNormArgs> args, cudaStream_t stream);
+
+  // Fused tensor-parallel GEMMs (one entry per rank context, like the collectives).
+  cudaError_t gemm_rs(const std::vector<GemmRsArgs>& args, cudaStream_t stream);
+  cudaError_t ag_gemm(const std::vector<AgGemmArgs>& args, cudaStream_t stream);
 
   // Capacity (bytes per rank) of the one-shot fused norm path.
   size_t fused_norm_capacity() const { return cfg_.half_bytes / world_; }

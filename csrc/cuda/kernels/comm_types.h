@@ -9,7 +9,7 @@ namespace ccl {
 
 constexpr int kMaxRanks = 8;
 constexpr int kMaxBlocks = 256;   // CTAs per collective kernel (flag slots per source rank)
-constexpr int kNumPhases = 4;
+constexpr int kNumPhases = 5;     // phases 0-3: epoch flags of the collectives; 4: arrival counters of the fused GEMM ops
 constexpr size_t kFlagBytes = (size_t)kNumPhases * kMaxRanks * kMaxBlocks * sizeof(uint32_t);
 constexpr size_t kStateBytes = 4096;  // epoch, ticket, scratch tables (all-to-all counts, ...)
 

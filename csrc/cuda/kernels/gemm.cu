@@ -22,7 +22,8 @@ template <int BN, bool DUAL, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                 const Params p) {
-  gemm_tile_body<BN, DUAL>(&tma_a, &tma_b, p, StoreEpilogue<OutT>{});
+  const int m0 = blockIdx.x * kBM;
+  gemm_tile_body<BN, DUAL>(&tma_a, &tma_b, p, StoreEpilogue<OutT>{}, TileCoord{m0, m0, (int)blockIdx.y * BN});
 }
 
 template <int BN, bool DUAL, typename OutT>
@@ -64,6 +65,7 @@ cudaError_t launch(const GemmDesc& d, int splitk, cudaStream_t stream) {
   p.stages = stages;
   p.splitk = splitk;
   p.status = d.status;
+  p.acquire_a = 0;
 
   auto kern = gemm_kernel<BN, DUAL, OutT>;
   static thread_local size_t configured = 0;

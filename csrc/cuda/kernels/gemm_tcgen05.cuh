@@ -46,6 +46,16 @@ struct Params {
   int stages;           // pipeline depth
   int splitk;           // cluster size along z (1 = no split)
   int* status;          // device-visible error word (0 = ok)
+  int acquire_a;        // 1: A was written by another GPU and observed through a flag; order the
+                        //    TMA (async proxy) reads after that acquire with a proxy fence
+};
+
+// Where a CTA's tile lives: `a_row` is the TMA row coordinate of the A tile (it differs from the
+// logical output row `m0` when A is read from a gathered staging buffer), `n0` the B/N offset.
+struct TileCoord {
+  int a_row;
+  int m0;
+  int n0;
 };
 
 struct __align__(8) Barriers {
@@ -131,7 +141,7 @@ __host__ __device__ constexpr size_t smem_bytes(int stages, int splitk) {
 
 template <int BN, bool DUAL, typename EpiFn>
 __device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
-                                               const Params& p, const EpiFn& epi) {
+                                               const Params& p, const EpiFn& epi, const TileCoord tc) {
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA M=128 needs N % 16 == 0");
   static_assert(acc_cols<BN, DUAL>() <= 512, "TMEM has 512 columns");
   extern __shared__ uint8_t smem_raw[];
@@ -150,8 +160,8 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const C
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * kBM;
-  const int n0 = blockIdx.y * BN;
+  const int m0 = tc.m0;
+  const int n0 = tc.n0;
   const uint32_t crank = p.splitk > 1 ? ptx::cluster_ctarank() : 0;
 
   // K range of this split.
@@ -184,6 +194,7 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const C
     if (lane == 0) {
       ptx::prefetch_tmap(tma_a);
       ptx::prefetch_tmap(tma_b);
+      if (p.acquire_a) asm volatile("fence.proxy.async;" ::: "memory");
       for (int i = 0; i < n_iters; ++i) {
         const int s = i % stages;
         const uint32_t ph = (i / stages) & 1;
@@ -195,8 +206,8 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const C
         uint8_t* st = smem + (size_t)s * kStage;
         ptx::mbar_arrive_expect_tx(&bars->full[s], kStage);
         const int kx = (it_begin + i) * kBK;
-        ptx::tma_load_2d(st, tma_a, &bars->full[s], kx, m0);
-        if (DUAL) ptx::tma_load_2d(st + kABytes, tma_a, &bars->full[s], kx, m0 + p.dual_off);
+        ptx::tma_load_2d(st, tma_a, &bars->full[s], kx, tc.a_row);
+        if (DUAL) ptx::tma_load_2d(st + kABytes, tma_a, &bars->full[s], kx, tc.a_row + p.dual_off);
         ptx::tma_load_2d(st + kABytes * (DUAL ? 2 : 1), tma_b, &bars->full[s], kx, n0);
       }
     }

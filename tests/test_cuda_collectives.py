@@ -197,3 +197,32 @@ def test_cuda_modes(env):
     e = {"NCCL_NVLS_ENABLE": "0", "CCL_ARENA_MB": "64"}
     e.update(env)
     run_ranks(_blocking_same_stream, world=_world(), device="cuda", env=e, timeout=300)
+
+
+def _fused_gemm_ops(rank, world):
+    from torch_ccl_b200 import ops
+
+    torch.manual_seed(11)
+    M, N, Kl = world * 256, 512, 256
+    As = [torch.randn(M, Kl, generator=torch.Generator().manual_seed(r)).to(torch.bfloat16) for r in range(world)]
+    Bs = [(torch.randn(N, Kl, generator=torch.Generator().manual_seed(100 + r)) * 0.1).to(torch.bfloat16) for r in range(world)]
+    for _ in range(3):
+        out = ops.gemm_reduce_scatter(As[rank].cuda(), Bs[rank].cuda())
+    torch.cuda.synchronize()
+    ref = sum((As[r].float() @ Bs[r].float().t()).to(torch.bfloat16).float() for r in range(world))
+    rows = M // world
+    torch.testing.assert_close(out.cpu().float(), ref[rank * rows:(rank + 1) * rows], rtol=2e-2, atol=0.2)
+    shard = [torch.randn(128, 320, generator=torch.Generator().manual_seed(200 + r)).to(torch.bfloat16) for r in range(world)]
+    w = (torch.randn(256, 320, generator=torch.Generator().manual_seed(300 + rank)) * 0.1).to(torch.bfloat16)
+    for _ in range(3):
+        out2 = ops.all_gather_gemm(shard[rank].cuda(), w.cuda())
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out2.cpu().float(), torch.cat(shard).float() @ w.float().t(), rtol=2e-2, atol=0.2)
+    t = torch.ones(10, device="cuda")
+    dist.all_reduce(t)
+    assert float(t[0]) == world
+    dist.barrier()
+
+
+def test_cuda_fused_gemm_collectives():
+    run_ranks(_fused_gemm_ops, world=_world(), device="cuda", env={"NCCL_NVLS_ENABLE": "0", "CCL_ARENA_MB": "64"}, timeout=300)

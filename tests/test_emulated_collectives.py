@@ -341,3 +341,50 @@ def test_bounded_wait_reports_timeout_instead_of_hanging():
     assert st[2] == 1  # peer that never signalled
     x = torch.ones(8, device="cuda")
     assert float((x + 1).sum()) == 16.0  # context alive
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_gemm_reduce_scatter_fused(comms, world):
+    """Row-parallel linear + reduce-scatter in one pass: tcgen05 tiles pushed into the owners'
+    arenas from the epilogue, then summed. Oracle: fp32 matmul of the concatenated K shards."""
+    c = comms(world, 8 << 20)
+    torch.manual_seed(5)
+    M, N, Kl = world * 256, 384, 320
+    As = [torch.randn(M, Kl).to(torch.bfloat16) for _ in range(world)]
+    Bs = [(torch.randn(N, Kl) * 0.1).to(torch.bfloat16) for _ in range(world)]
+    outs = [torch.empty(M // world, N, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    da, db = [a.cuda() for a in As], [b.cuda() for b in Bs]
+    for _ in range(3):  # repeated calls: counters, epochs and parity keep in step
+        c.gemm_rs(da, db, outs)
+    torch.cuda.synchronize()
+    assert c.status()[0] == 0
+    parts = [As[r].float() @ Bs[r].float().t() for r in range(world)]
+    ref = sum(p.to(torch.bfloat16).float() for p in parts)  # partials travel as bf16
+    rows = M // world
+    for r in range(world):
+        torch.testing.assert_close(outs[r].cpu().float(), ref[r * rows:(r + 1) * rows], rtol=2e-2, atol=0.15)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_all_gather_gemm_fused(comms, world):
+    """All-gather + column-parallel linear: shards pushed into the peers' arenas, tiles of a
+    shard start as soon as its arrival counter is reached."""
+    c = comms(world, 8 << 20)
+    torch.manual_seed(6)
+    rows, K, Nl = 128, 448, 272
+    As = [torch.randn(rows, K).to(torch.bfloat16) for _ in range(world)]
+    Bs = [(torch.randn(Nl, K) * 0.1).to(torch.bfloat16) for _ in range(world)]
+    outs = [torch.empty(world * rows, Nl, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    da, db = [a.cuda() for a in As], [b.cuda() for b in Bs]
+    for _ in range(3):
+        c.ag_gemm(da, db, outs)
+    torch.cuda.synchronize()
+    assert c.status()[0] == 0
+    full = torch.cat(As).float()
+    for r in range(world):
+        torch.testing.assert_close(outs[r].cpu().float(), full @ Bs[r].float().t(), rtol=2e-2, atol=0.15)
+    # an op of the ordinary kind right after: the shared epoch must still line up
+    xs = [torch.full((1000,), float(r + 1), device="cuda") for r in range(world)]
+    c.allreduce(xs, xs, SUM, 1.0, 0, 1)
+    torch.cuda.synchronize()
+    assert float(xs[0][0]) == sum(range(1, world + 1))

@@ -36,6 +36,28 @@ def all_gather_copy_out(shard, outs, group=None):
     return outs
 
 
+def gemm_reduce_scatter(a, b, group=None, out=None):
+    """Row-parallel linear fused with its reduce-scatter: returns this rank's rows [M/W, N] of
+    sum_ranks(a_rank[M, K_local] @ b_rank[N, K_local].T); tiles cross NVLink from the GEMM epilogue."""
+    be = _backend(group, a)
+    world = torch.distributed.get_world_size(group)
+    if out is None:
+        out = torch.empty(a.shape[0] // world, b.shape[0], device=a.device, dtype=torch.bfloat16)
+    be.fused_gemm_rs(a, b, out)
+    return out
+
+
+def all_gather_gemm(a_shard, b, group=None, out=None):
+    """All-gather fused with a column-parallel linear: returns all_gather(a_shard)[M, K] @ b[N, K].T;
+    tiles of a shard start as soon as that shard has arrived."""
+    be = _backend(group, a_shard)
+    world = torch.distributed.get_world_size(group)
+    if out is None:
+        out = torch.empty(a_shard.shape[0] * world, b.shape[0], device=a_shard.device, dtype=torch.bfloat16)
+    be.fused_ag_gemm(a_shard, b, out)
+    return out
+
+
 def gemm_bf16_tn(a, b, out=None, trans_out=False, dual_off=0, splitk=0, bn=0, out_dtype=None):
     """out = a @ b.T on tcgen05 tensor cores (bf16 operands, fp32 accumulation)."""
     m = dual_off if dual_off > 0 else a.shape[0]
