@@ -14,6 +14,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import torch_ccl_b200._C as C  # noqa: E402
+from torch_ccl_b200.ops import pack_weight  # noqa: E402
 
 
 def peaks():
@@ -61,6 +62,16 @@ def main():
         t = timeit(lambda i: C.gemm_bf16_tn(ws[i % nbuf], x, out, True, n_out if dual else 0, splitk, 16), args.iters)
         gbs = wrows * K * 2 / t / 1e9
         row = {"shape": label, "us": round(t * 1e6, 2), "GBps": round(gbs, 1), f"frac_hbm_{src}": round(gbs / hbm, 3)}
+        # the same product with the weights pre-packed as contiguous 128x64 tiles
+        pad = (n_out + 127) // 128 * 128
+        if dual:
+            pk = [torch.cat([pack_weight(w[:n_out]), pack_weight(w[n_out:])]) for w in ws]
+        else:
+            pk = [pack_weight(w) for w in ws]
+        t2 = timeit(lambda i: C.gemm_bf16_tn(pk[i % nbuf], x, out, True, pad if dual else 0, splitk, 16, n_out), args.iters)
+        row["tiled_us"] = round(t2 * 1e6, 2)
+        row[f"tiled_frac_hbm_{src}"] = round(wrows * K * 2 / t2 / 1e9 / hbm, 3)
+        del pk
         if args.torch and not dual:
             tt = timeit(lambda i: torch.matmul(x, ws[i % nbuf].t(), out=out), args.iters)
             row["torch_us"] = round(tt * 1e6, 2)

@@ -1,0 +1,74 @@
+"""Small, fixed single-kernel workloads for profiling (one kernel family per case, a handful of
+launches, inputs larger than the 126 MB L2 but only a few hundred MB on the device).
+
+    python bench/kernel_cases.py {gemm_decode|gemm_swiglu|gemm_large|attention|addnorm} [--iters N]
+"""
+import argparse
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import torch_ccl_b200._C as C  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case")
+    ap.add_argument("--iters", type=int, default=6)
+    a = ap.parse_args()
+    dev = "cuda"
+    bf = dict(device=dev, dtype=torch.bfloat16)
+    if a.case == "gemm_decode":  # Llama-7B QKV projection at batch 16 (weights stream from HBM)
+        ws = [torch.randn(12288, 4096, **bf) * 0.02 for _ in range(3)]
+        x = torch.randn(16, 4096, **bf)
+        out = torch.empty(16, 12288, **bf)
+        fn = lambda i: C.gemm_bf16_tn(ws[i % 3], x, out, True, 0, 0, 16)
+    elif a.case == "gemm_swiglu":  # gate/up projection with the fused SwiGLU epilogue
+        ws = [torch.randn(22016, 4096, **bf) * 0.02 for _ in range(2)]
+        x = torch.randn(16, 4096, **bf)
+        out = torch.empty(16, 11008, **bf)
+        fn = lambda i: C.gemm_bf16_tn(ws[i % 2], x, out, True, 11008, 0, 16)
+    elif a.case == "gemm_large":  # compute-bound
+        A = torch.randn(8192, 4096, **bf)
+        B = torch.randn(8192, 4096, **bf)
+        out = torch.empty(8192, 8192, **bf)
+        fn = lambda i: C.gemm_bf16_tn(A, B, out, False, 0, 1, 0)
+    elif a.case == "attention":  # batch 16 x 32 heads over a 1024-token cache (268 MB of K/V)
+        B, nh, S = 16, 32, 1280
+        qkv = torch.randn(B, 3 * nh * 128, **bf)
+        kc = torch.randn(B, nh, S, 128, **bf)
+        vc = torch.randn(B, nh, S, 128, **bf)
+        pos = torch.full((B,), 1024, device=dev, dtype=torch.int32)
+        inv = 1.0 / (10000.0 ** (torch.arange(0, 128, 2, device=dev).float() / 128))
+        ang = torch.arange(S, device=dev).float()[:, None] * inv[None]
+        cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+        out = torch.empty(B, nh * 128, **bf)
+        ns = C.decode_attention_default_splits(B, nh, S)
+        scratch = torch.zeros(C.decode_attention_scratch_bytes(B, nh, ns) // 4 + 1, device=dev)
+        cnt = torch.zeros(B * nh, device=dev, dtype=torch.int32)
+        fn = lambda i: C.decode_attention(qkv, kc, vc, pos, cos, sin, out, scratch, cnt, nh, nh, ns)
+    elif a.case == "addnorm":
+        comm = C.CudaComm.create(None, 0, 1, 1 << 20, 1000, "ccl/case")
+        x = torch.randn(16, 4096, **bf)
+        res = torch.randn(16, 4096, **bf)
+        w = torch.ones(4096, **bf)
+        out = torch.empty(16, 4096, **bf)
+        fn = lambda i: comm.allreduce_residual_rmsnorm([x], [res], [w], [out], 1e-5)
+    else:
+        raise SystemExit("unknown case")
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize()
+    s.record()
+    for i in range(a.iters):
+        fn(i)
+    e.record()
+    torch.cuda.synchronize()
+    print(f"{a.case}: {s.elapsed_time(e) / a.iters * 1e3:.2f} us per launch")
+
+
+if __name__ == "__main__":
+    main()

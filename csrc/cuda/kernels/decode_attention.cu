@@ -119,8 +119,9 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const Decode
 #pragma unroll
   for (int i = 0; i < 16; ++i) o[i] = 0.f;
 
-  for (int t = t0 + g; t < t1; t += kGroups) {
-    float k[16], v[16];
+  // Two positions per step and lane group: the loads of the second are in flight while the first
+  // is being reduced (the kernel is bound by memory latency, not by arithmetic).
+  auto fetch = [&](int t, float (&k)[16], float (&v)[16]) {
     if (t == pos) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
@@ -131,6 +132,8 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const Decode
       load16(kc + (size_t)t * kHD + j * 16, k);
       load16(vc + (size_t)t * kHD + j * 16, v);
     }
+  };
+  auto step = [&](const float (&k)[16], const float (&v)[16]) {
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) s += q[i] * k[i];
@@ -145,6 +148,19 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const Decode
 #pragma unroll
     for (int i = 0; i < 16; ++i) o[i] = o[i] * corr + pr * v[i];
     m = mn;
+  };
+  int t = t0 + g;
+  for (; t + kGroups < t1; t += 2 * kGroups) {
+    float k0[16], v0[16], k1[16], v1[16];
+    fetch(t, k0, v0);
+    fetch(t + kGroups, k1, v1);
+    step(k0, v0);
+    step(k1, v1);
+  }
+  if (t < t1) {
+    float k0[16], v0[16];
+    fetch(t, k0, v0);
+    step(k0, v0);
   }
 
   // combine the kGroups position groups of this CTA
@@ -211,7 +227,7 @@ size_t decode_attention_scratch_bytes(int batch, int n_heads, int nsplit) {
 
 int decode_attention_default_splits(int batch, int n_heads, int max_context) {
   const int pairs = batch * n_heads;
-  int s = (2 * 148 + pairs - 1) / pairs;  // aim at >= 2 CTAs per SM
+  int s = (4 * 148) / pairs;  // four CTAs fit on an SM (registers): fill them, but stay within one wave
   const int cap = (max_context + 255) / 256;  // at least 256 positions per split
   if (s > cap) s = cap;
   if (s < 1) s = 1;

@@ -26,6 +26,50 @@ __global__ void __launch_bounds__(kThreads, 1)
   gemm_tile_body<BN, DUAL>(&tma_a, &tma_b, p, StoreEpilogue<OutT>{}, TileCoord{m0, m0, (int)blockIdx.y * BN});
 }
 
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                           const Params p) {
+  gemm_persistent_body<BN>(&tma_a, &tma_b, p, StoreEpilogue<OutT>{});
+}
+
+// Compute-bound shapes: persistent CTAs, double-buffered TMEM accumulators.
+template <int BN, typename OutT>
+cudaError_t launch_persistent(const GemmDesc& d, cudaStream_t stream) {
+  const int m_tiles = (int)((d.M + kBM - 1) / kBM);
+  const int n_tiles = (int)((d.N + BN - 1) / BN);
+  constexpr size_t kSmemMax = 200 * 1024;
+  int stages = kMaxStages;
+  while (stages > 2 && persistent_smem_bytes<BN>(stages) > kSmemMax) --stages;
+  const size_t smem = persistent_smem_bytes<BN>(stages);
+  CUtensorMap ta, tb;
+  if (!tma::make_2d_bf16(&ta, d.a, (uint64_t)d.M, (uint64_t)d.K, (uint64_t)d.lda, kBM, kBK)) return cudaErrorInvalidValue;
+  if (!tma::make_2d_bf16(&tb, d.b, (uint64_t)d.N, (uint64_t)d.K, (uint64_t)d.ldb, BN, kBK)) return cudaErrorInvalidValue;
+  Params p{};
+  p.M = (int)d.M;
+  p.N = (int)d.N;
+  p.K = (int)d.K;
+  p.out = d.out;
+  p.ldo = d.ldo;
+  p.stages = stages;
+  p.splitk = 1;
+  p.status = d.status;
+  auto kern = gemm_persistent_kernel<BN, OutT>;
+  static thread_local bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax + 2048);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  int sms = 148;
+  const int total = m_tiles * n_tiles;
+  const int grid = total < sms ? total : sms;
+  kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) g_launches.fetch_add(1);
+  return e;
+}
+
 template <int BN, bool DUAL, typename OutT>
 cudaError_t launch(const GemmDesc& d, int splitk, cudaStream_t stream) {
   const int m_tiles = (int)((d.M + kBM - 1) / kBM);
@@ -49,8 +93,13 @@ cudaError_t launch(const GemmDesc& d, int splitk, cudaStream_t stream) {
 
   CUtensorMap ta, tb;
   const int64_t a_rows = DUAL ? (d.dual_off + d.M) : d.M;
-  if (!tma::make_2d_bf16(&ta, d.a, (uint64_t)a_rows, (uint64_t)d.K, (uint64_t)d.lda, kBM, kBK))
+  if (d.a_tiled) {
+    if (d.dual_off % kBM != 0) return cudaErrorInvalidValue;
+    if (!tma::make_2d_bf16(&ta, d.a, (uint64_t)d.a_packed_rows, (uint64_t)kBK, (uint64_t)kBK, kBM, kBK))
+      return cudaErrorInvalidValue;
+  } else if (!tma::make_2d_bf16(&ta, d.a, (uint64_t)a_rows, (uint64_t)d.K, (uint64_t)d.lda, kBM, kBK)) {
     return cudaErrorInvalidValue;
+  }
   if (!tma::make_2d_bf16(&tb, d.b, (uint64_t)d.N, (uint64_t)d.K, (uint64_t)d.ldb, BN, kBK))
     return cudaErrorInvalidValue;
 
@@ -66,6 +115,8 @@ cudaError_t launch(const GemmDesc& d, int splitk, cudaStream_t stream) {
   p.splitk = splitk;
   p.status = d.status;
   p.acquire_a = 0;
+  p.a_tiled = d.a_tiled;
+  p.k_tiles = k_iters;
 
   auto kern = gemm_kernel<BN, DUAL, OutT>;
   static thread_local size_t configured = 0;
@@ -109,7 +160,7 @@ cudaError_t dispatch_bn(const GemmDesc& d, int splitk, cudaStream_t s) {
 
 cudaError_t gemm_bf16_tn(const GemmDesc& d, cudaStream_t stream) {
   if (!d.a || !d.b || !d.out || d.M <= 0 || d.N <= 0 || d.K <= 0) return cudaErrorInvalidValue;
-  if ((d.lda % 8) || (d.ldb % 8)) return cudaErrorInvalidValue;  // TMA strides: 16-byte multiples
+  if ((!d.a_tiled && (d.lda % 8)) || (d.ldb % 8)) return cudaErrorInvalidValue;  // TMA strides: 16-byte multiples
   if ((reinterpret_cast<uintptr_t>(d.a) & 15) || (reinterpret_cast<uintptr_t>(d.b) & 15))
     return cudaErrorInvalidValue;
   int bn = d.bn;
@@ -136,6 +187,13 @@ cudaError_t gemm_bf16_tn(const GemmDesc& d, cudaStream_t stream) {
       if (splitk > 4) splitk = 4;
       if (splitk < 1) splitk = 1;
     }
+  }
+  // large row-major problems without split-K: the persistent kernel
+  if (!d.a_tiled && !d.trans_out && d.dual_off == 0 && splitk == 1 && (bn == 128 || bn == 256) && !d.no_persistent &&
+      ((d.M + 127) / 128) * ((d.N + bn - 1) / bn) >= 148) {
+    if (bn == 256)
+      return d.out_fp32 ? gemm::launch_persistent<256, float>(d, stream) : gemm::launch_persistent<256, __nv_bfloat16>(d, stream);
+    return d.out_fp32 ? gemm::launch_persistent<128, float>(d, stream) : gemm::launch_persistent<128, __nv_bfloat16>(d, stream);
   }
   switch (bn) {
     case 16: return gemm::dispatch_bn<16>(d, splitk, stream);

@@ -18,6 +18,13 @@ struct GemmDesc {
   int64_t dual_off = 0;  // >0: SwiGLU mode, out = silu(A[m]·B) * (A[m+dual_off]·B); M counts gate rows
   int splitk = 0;      // 0 = choose automatically
   int bn = 0;          // 0 = choose automatically from N
+  // a_tiled: `a` holds the matrix pre-packed for streaming: rows padded to a multiple of 128, K to a
+  // multiple of 64, stored as [rows/128][K/64][128][64] (each 128x64 tile is 16 KB contiguous), so a
+  // TMA box reads one contiguous block instead of 128 strided 128-byte pieces. With dual_off > 0 the
+  // second operand starts dual_off (a multiple of 128) packed rows after the first.
+  int a_tiled = 0;
+  int64_t a_packed_rows = 0;  // total rows of the packed [*, 64] matrix
+  int no_persistent = 0;  // 1: force the one-tile-per-CTA kernel (testing)
   int* status = nullptr;  // optional device error word
 };
 

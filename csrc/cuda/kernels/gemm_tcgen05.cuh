@@ -46,6 +46,9 @@ struct Params {
   int stages;           // pipeline depth
   int splitk;           // cluster size along z (1 = no split)
   int* status;          // device-visible error word (0 = ok)
+  int a_tiled;          // 1: A is pre-packed as contiguous 128x64 tiles, tile (mt, kt) at packed
+                        //    row (mt * k_tiles + kt) * 128 of a [*, 64] matrix (see gemm.h)
+  int k_tiles;          // K / 64 of the packed A
   int acquire_a;        // 1: A was written by another GPU and observed through a flag; order the
                         //    TMA (async proxy) reads after that acquire with a proxy fence
 };
@@ -206,8 +209,17 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const C
         uint8_t* st = smem + (size_t)s * kStage;
         ptx::mbar_arrive_expect_tx(&bars->full[s], kStage);
         const int kx = (it_begin + i) * kBK;
-        ptx::tma_load_2d(st, tma_a, &bars->full[s], kx, tc.a_row);
-        if (DUAL) ptx::tma_load_2d(st + kABytes, tma_a, &bars->full[s], kx, tc.a_row + p.dual_off);
+        if (p.a_tiled) {
+          // one contiguous 16 KB tile per load: every DRAM page that is opened is fully used
+          const int kt = it_begin + i;
+          ptx::tma_load_2d(st, tma_a, &bars->full[s], 0, ((tc.a_row / kBM) * p.k_tiles + kt) * kBM);
+          if (DUAL)
+            ptx::tma_load_2d(st + kABytes, tma_a, &bars->full[s], 0,
+                             (((tc.a_row + p.dual_off) / kBM) * p.k_tiles + kt) * kBM);
+        } else {
+          ptx::tma_load_2d(st, tma_a, &bars->full[s], kx, tc.a_row);
+          if (DUAL) ptx::tma_load_2d(st + kABytes, tma_a, &bars->full[s], kx, tc.a_row + p.dual_off);
+        }
         ptx::tma_load_2d(st + kABytes * (DUAL ? 2 : 1), tma_b, &bars->full[s], kx, n0);
       }
     }
@@ -340,6 +352,172 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const C
     }
   }
 
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) ptx::tmem_dealloc(tmem_base, kTmemCols);
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Persistent variant for compute-bound problems: one CTA per SM walks a list of output tiles
+// (grouped so that the tiles in flight at any time share A and B panels in L2). The smem ring
+// keeps running across tiles, and the accumulator is double-buffered in TMEM (2 x BN columns):
+// while the epilogue warps drain tile i, the MMA warp already accumulates tile i+1.
+// ---------------------------------------------------------------------------------------------
+struct __align__(8) PersistentBarriers {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  uint32_t failed;
+};
+
+template <int BN>
+__host__ __device__ constexpr size_t persistent_smem_bytes(int stages) {
+  return 1024 + (size_t)stages * stage_bytes<BN, false>() + sizeof(PersistentBarriers);
+}
+
+__device__ __forceinline__ void tile_of(int t, int m_tiles, int n_tiles, int& mt, int& nt) {
+  constexpr int kGroupM = 16;
+  const int in_group = kGroupM * n_tiles;
+  const int gid = t / in_group;
+  const int first_m = gid * kGroupM;
+  const int gsm = (m_tiles - first_m) < kGroupM ? (m_tiles - first_m) : kGroupM;
+  const int r = t - gid * in_group;
+  mt = first_m + r % gsm;
+  nt = r / gsm;
+}
+
+template <int BN, typename EpiFn>
+__device__ __forceinline__ void gemm_persistent_body(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
+                                                     const Params& p, const EpiFn& epi) {
+  static_assert(BN == 128 || BN == 256, "persistent kernel: BN 128 or 256 (2*BN TMEM columns)");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  constexpr int kStage = stage_bytes<BN, false>();
+  constexpr int kABytes = kBM * kBK * 2;
+  constexpr uint32_t kTmemCols = 2 * BN;
+  const int stages = p.stages;
+  PersistentBarriers* bars = reinterpret_cast<PersistentBarriers*>(smem + (size_t)stages * kStage);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tiles = (p.M + kBM - 1) / kBM;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int total = m_tiles * n_tiles;
+  const int k_iters = (p.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(&bars->full[s], 1);
+      ptx::mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(&bars->tmem_full[b], 1);
+      ptx::mbar_init(&bars->tmem_empty[b], 128);  // every epilogue thread arrives
+    }
+    bars->failed = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&bars->tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      ptx::prefetch_tmap(tma_a);
+      ptx::prefetch_tmap(tma_b);
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < total; t += gridDim.x) {
+        int mt, nt;
+        tile_of(t, m_tiles, n_tiles, mt, nt);
+        for (int k = 0; k < k_iters; ++k, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1;
+          if (!ptx::mbar_wait(&bars->empty[s], ph ^ 1)) {
+            bars->failed = 1;
+            if (p.status) atomicExch(p.status, 111);
+            t = total;
+            break;
+          }
+          uint8_t* st = smem + (size_t)s * kStage;
+          ptx::mbar_arrive_expect_tx(&bars->full[s], kStage);
+          ptx::tma_load_2d(st, tma_a, &bars->full[s], k * kBK, mt * kBM);
+          ptx::tma_load_2d(st + kABytes, tma_b, &bars->full[s], k * kBK, nt * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::make_idesc_bf16(kBM, BN);
+      uint32_t it = 0;
+      int i = 0;
+      for (int t = blockIdx.x; t < total; t += gridDim.x, ++i) {
+        const int acc = i & 1;
+        if (!ptx::mbar_wait(&bars->tmem_empty[acc], (((uint32_t)i >> 1) & 1) ^ 1)) {
+          bars->failed = 1;
+          if (p.status) atomicExch(p.status, 112);
+          break;
+        }
+        ptx::tc_fence_after();
+        bool ok = true;
+        for (int k = 0; k < k_iters; ++k, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1;
+          if (!ptx::mbar_wait(&bars->full[s], ph)) {
+            bars->failed = 1;
+            if (p.status) atomicExch(p.status, 113);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t a_addr = ptx::smem_u32(smem + (size_t)s * kStage);
+          const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+          for (int kk = 0; kk < kBK / 16; ++kk) {
+            ptx::umma_bf16_ss(tmem_base + acc * BN, ptx::make_desc_sw128(a_addr + kk * 32),
+                              ptx::make_desc_sw128(b_addr + kk * 32), idesc, (k > 0 || kk > 0) ? 1u : 0u);
+          }
+          ptx::umma_commit(&bars->empty[s]);
+        }
+        if (!ok) break;
+        ptx::umma_commit(&bars->tmem_full[acc]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    int i = 0;
+    for (int t = blockIdx.x; t < total; t += gridDim.x, ++i) {
+      int mt, nt;
+      tile_of(t, m_tiles, n_tiles, mt, nt);
+      const int acc = i & 1;
+      if (!ptx::mbar_wait(&bars->tmem_full[acc], ((uint32_t)i >> 1) & 1)) {
+        bars->failed = 1;
+        if (p.status) atomicExch(p.status, 114);
+        break;
+      }
+      ptx::tc_fence_after();
+#pragma unroll 2
+      for (int c = 0; c < BN; c += 16) {
+        uint32_t r[16];
+        ptx::tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c, r);
+        ptx::tmem_ld_wait();
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+        epi(p, mt * kBM + row, nt * BN + c, v);
+      }
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(&bars->tmem_empty[acc]);
+    }
+  }
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 1) ptx::tmem_dealloc(tmem_base, kTmemCols);

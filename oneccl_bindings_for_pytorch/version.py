@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "4457f4c50cbfb85c00bc2c167ac5e4873bf5ebe2"
+git_version = "6d99678bac48ccd2325915631b494121a1415d29"

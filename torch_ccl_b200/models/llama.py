@@ -20,6 +20,7 @@ import torch
 import torch.distributed as dist
 
 from .. import _C
+from ..ops import pack_weight, unpack_weight
 
 
 @dataclass
@@ -110,16 +111,20 @@ class TPLlamaDecoder:
             wg = _rand((cfg.inter, H), s + 5, dev)[r * self.inter:(r + 1) * self.inter]
             wu = _rand((cfg.inter, H), s + 6, dev)[r * self.inter:(r + 1) * self.inter]
             wd = _rand((H, cfg.inter), s + 7, dev)[:, r * self.inter:(r + 1) * self.inter]
+            # weights are kept pre-tiled for streaming (see ops.pack_weight); gate and up are padded
+            # to whole 128-row tiles separately so that the SwiGLU pairs line up tile by tile
             self.layers.append(dict(
-                wqkv=torch.cat([wq, wk, wv]).contiguous(), wo=wo.contiguous(),
-                wgu=torch.cat([wg, wu]).contiguous(), wd=wd.contiguous(),
+                wqkv=pack_weight(torch.cat([wq, wk, wv])), wo=pack_weight(wo),
+                wgu=torch.cat([pack_weight(wg), pack_weight(wu)]), wd=pack_weight(wd),
                 attn_norm=torch.ones(H, device=dev, dtype=torch.bfloat16),
                 mlp_norm=torch.ones(H, device=dev, dtype=torch.bfloat16),
                 k=torch.zeros(max_batch, self.nkv, max_seq, hd, device=dev, dtype=torch.bfloat16),
                 v=torch.zeros(max_batch, self.nkv, max_seq, hd, device=dev, dtype=torch.bfloat16)))
             del wq, wk, wv, wo, wg, wu, wd
         self.embed = _rand((cfg.vocab, H), seed * 100003 + 900001, dev)[r * self.vshard:(r + 1) * self.vshard].contiguous()
-        self.lm_head = _rand((cfg.vocab, H), seed * 100003 + 900002, dev)[r * self.vshard:(r + 1) * self.vshard].contiguous()
+        self.lm_head = pack_weight(_rand((cfg.vocab, H), seed * 100003 + 900002, dev)[r * self.vshard:(r + 1) * self.vshard])
+        self.inter_pad = (self.inter + 127) // 128 * 128
+        self.qkv_rows = (self.nh + 2 * self.nkv) * hd
         self.final_norm = torch.ones(H, device=dev, dtype=torch.bfloat16)
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2, device=dev, dtype=torch.float32) / hd))
         ang = torch.arange(max_seq, device=dev, dtype=torch.float32)[:, None] * inv[None, :]
@@ -149,10 +154,19 @@ class TPLlamaDecoder:
         self._pin_out = None
 
     # ------------------------------------------------------------------------------------
-    def _gemm_t(self, w, x, out, dual=0):
-        """out[b, n] = x[b, :] @ w[n, :]^T with the weights on the UMMA M side."""
-        bn = 16 if x.shape[0] <= 16 else (32 if x.shape[0] <= 32 else 64)
-        _C.gemm_bf16_tn(w, x, out, True, dual, 0, bn)
+    def _gemm_t(self, w, x, out, rows, dual=0, splitk=0):
+        """out[b, n] = x[b, :] @ W[n, :]^T with the pre-tiled weights on the UMMA M side."""
+        b = x.shape[0]
+        bn = 16 if b <= 16 else (32 if b <= 32 else (64 if b <= 64 else 128))
+        _C.gemm_bf16_tn(w, x, out, True, dual, 1 if b > 64 else splitk, bn, rows)
+
+    def dense_weights(self, L):
+        """Row-major copies of a layer's weights (oracle / debugging only)."""
+        H, hd = self.cfg.hidden, self.cfg.head_dim
+        half = L["wgu"].shape[0] // 2
+        return dict(wqkv=unpack_weight(L["wqkv"], self.qkv_rows, H), wo=unpack_weight(L["wo"], H, self.nh * hd),
+                    wg=unpack_weight(L["wgu"][:half], self.inter, H), wu=unpack_weight(L["wgu"][half:], self.inter, H),
+                    wd=unpack_weight(L["wd"], H, self.inter))
 
     def _embed_partial(self, tokens, out):
         """Vocab-parallel embedding: rows outside this rank's shard contribute zeros."""
@@ -169,16 +183,16 @@ class TPLlamaDecoder:
         h.zero_()
         self.comm.ar_res_norm(x, h, self.layers[0]["attn_norm"], xn, cfg.eps)
         for li, L in enumerate(self.layers):
-            self._gemm_t(L["wqkv"], xn, qkv)
+            self._gemm_t(L["wqkv"], xn, qkv, self.qkv_rows)
             _C.decode_attention(qkv, L["k"], L["v"], self.positions[:B], self.cos, self.sin, attn, self.scratch,
                                 self.counters, self.nh, self.nkv, self.nsplit)
-            self._gemm_t(L["wo"], attn, x)
+            self._gemm_t(L["wo"], attn, x, cfg.hidden)
             self.comm.ar_res_norm(x, h, L["mlp_norm"], xn, cfg.eps)
-            self._gemm_t(L["wgu"], xn, act, dual=self.inter)
-            self._gemm_t(L["wd"], act, x)
+            self._gemm_t(L["wgu"], xn, act, self.inter, dual=self.inter_pad)
+            self._gemm_t(L["wd"], act, x, cfg.hidden)
             nw = self.layers[li + 1]["attn_norm"] if li + 1 < cfg.n_layers else self.final_norm
             self.comm.ar_res_norm(x, h, nw, xn, cfg.eps)
-        self._gemm_t(self.lm_head, xn, self.logits[:B])
+        self._gemm_t(self.lm_head, xn, self.logits[:B], self.vshard)
         val, idx = self.logits[:B].max(dim=-1)
         if self.world > 1:
             self.my_best[:B, 0] = val
@@ -266,7 +280,7 @@ class TPLlamaDecoder:
             norm_step(self.layers[0]["attn_norm"])
             for li, L in enumerate(self.layers):
                 qkv = torch.empty(S, (self.nh + 2 * self.nkv) * hd, **bf)
-                _C.gemm_bf16_tn(xn, L["wqkv"], qkv, False, 0, 1, 0)
+                self._gemm_t(L["wqkv"], xn, qkv, self.qkv_rows)
                 q = rope(qkv[:, : self.nh * hd].view(1, S, self.nh, hd))
                 k = rope(qkv[:, self.nh * hd:(self.nh + self.nkv) * hd].view(1, S, self.nkv, hd))
                 v = qkv[:, (self.nh + self.nkv) * hd:].view(1, S, self.nkv, hd)
@@ -276,16 +290,15 @@ class TPLlamaDecoder:
                     q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
                     enable_gqa=self.nh != self.nkv)
                 attn = o.transpose(1, 2).reshape(S, self.nh * hd).contiguous()
-                _C.gemm_bf16_tn(attn, L["wo"], x, False, 0, 1, 0)
+                self._gemm_t(L["wo"], attn, x, cfg.hidden)
                 norm_step(L["mlp_norm"])
                 act = torch.empty(S, self.inter, **bf)
-                # SwiGLU: weights on the M side with the dual-A epilogue, output transposed back
-                _C.gemm_bf16_tn(L["wgu"], xn, act, True, self.inter, 1, 128 if S >= 128 else 16)
-                _C.gemm_bf16_tn(act, L["wd"], x, False, 0, 1, 0)
+                self._gemm_t(L["wgu"], xn, act, self.inter, dual=self.inter_pad)
+                self._gemm_t(L["wd"], act, x, cfg.hidden)
                 nw = self.layers[li + 1]["attn_norm"] if li + 1 < cfg.n_layers else self.final_norm
                 norm_step(nw)
             logits = torch.empty(1, self.vshard, device=dev, dtype=torch.float32)
-            _C.gemm_bf16_tn(self.lm_head, xn[S - 1:S].contiguous(), logits, True, 0, 0, 16)
+            self._gemm_t(self.lm_head, xn[S - 1:S].contiguous(), logits, self.vshard)
             val, idx = logits.max(dim=-1)
             if self.world > 1:
                 mine = torch.stack([val, (idx + self.rank * self.vshard).float()], dim=-1)
@@ -329,7 +342,8 @@ class TPLlamaDecoder:
 
         xn = rms(h, self.layers[0]["attn_norm"])
         for li, L in enumerate(self.layers):
-            qkv = (xn.float() @ L["wqkv"].float().t()).to(torch.bfloat16).float()
+            D = self.dense_weights(L)
+            qkv = (xn.float() @ D["wqkv"].float().t()).to(torch.bfloat16).float()
             q = rope(qkv[:, : self.nh * hd].view(B, self.nh, hd))
             k = rope(qkv[:, self.nh * hd:(self.nh + self.nkv) * hd].view(B, self.nkv, hd)).to(torch.bfloat16).float()
             v = qkv[:, (self.nh + self.nkv) * hd:].view(B, self.nkv, hd)
@@ -344,13 +358,12 @@ class TPLlamaDecoder:
                 s = torch.einsum("hd,htd->ht", q[b], kk) / math.sqrt(hd)
                 outs.append(torch.einsum("ht,htd->hd", s.softmax(-1), vv).reshape(-1))
             attn = torch.stack(outs).to(torch.bfloat16)
-            o = allreduce((attn.float() @ L["wo"].float().t()).to(torch.bfloat16))
+            o = allreduce((attn.float() @ D["wo"].float().t()).to(torch.bfloat16))
             h = (o.float() + h.float()).to(torch.bfloat16)
             xn = rms(h, L["mlp_norm"])
-            gu = xn.float() @ L["wgu"].float().t()
-            act = (torch.nn.functional.silu(gu[:, : self.inter]) * gu[:, self.inter:]).to(torch.bfloat16)
-            d = allreduce((act.float() @ L["wd"].float().t()).to(torch.bfloat16))
+            act = (torch.nn.functional.silu(xn.float() @ D["wg"].float().t()) * (xn.float() @ D["wu"].float().t())).to(torch.bfloat16)
+            d = allreduce((act.float() @ D["wd"].float().t()).to(torch.bfloat16))
             h = (d.float() + h.float()).to(torch.bfloat16)
             nw = self.layers[li + 1]["attn_norm"] if li + 1 < cfg.n_layers else self.final_norm
             xn = rms(h, nw)
-        return xn.float() @ self.lm_head.float().t()
+        return xn.float() @ unpack_weight(self.lm_head, self.vshard, cfg.hidden).float().t()

@@ -58,12 +58,31 @@ def all_gather_gemm(a_shard, b, group=None, out=None):
     return out
 
 
-def gemm_bf16_tn(a, b, out=None, trans_out=False, dual_off=0, splitk=0, bn=0, out_dtype=None):
+def pack_weight(w):
+    """Re-lays a [rows, K] weight for streaming by the swap-AB GEMM: rows padded to a multiple of
+    128 and K to a multiple of 64, stored as [rows/128][K/64][128][64] so that every 128x64 tile is
+    one contiguous 16 KB block (a TMA box then reads whole DRAM pages instead of 128 strided
+    128-byte pieces). Returns a [*, 64] bf16 tensor for `gemm_bf16_tn(..., a_tiled_rows=rows)`."""
+    rows, k = w.shape
+    rp, kp = (rows + 127) // 128 * 128, (k + 63) // 64 * 64
+    if rp != rows or kp != k:
+        w = torch.nn.functional.pad(w, (0, kp - k, 0, rp - rows))
+    return w.view(rp // 128, 128, kp // 64, 64).permute(0, 2, 1, 3).contiguous().view(-1, 64)
+
+
+def unpack_weight(packed, rows, k):
+    """Inverse of pack_weight."""
+    rp, kp = (rows + 127) // 128 * 128, (k + 63) // 64 * 64
+    w = packed.view(rp // 128, kp // 64, 128, 64).permute(0, 2, 1, 3).reshape(rp, kp)
+    return w[:rows, :k]
+
+
+def gemm_bf16_tn(a, b, out=None, trans_out=False, dual_off=0, splitk=0, bn=0, out_dtype=None, a_tiled_rows=0):
     """out = a @ b.T on tcgen05 tensor cores (bf16 operands, fp32 accumulation)."""
-    m = dual_off if dual_off > 0 else a.shape[0]
+    m = a_tiled_rows if a_tiled_rows > 0 else (dual_off if dual_off > 0 else a.shape[0])
     n = b.shape[0]
     if out is None:
         shape = (n, m) if trans_out else (m, n)
         out = torch.empty(shape, device=a.device, dtype=out_dtype or torch.bfloat16)
-    _C.gemm_bf16_tn(a, b, out, trans_out, dual_off, splitk, bn)
+    _C.gemm_bf16_tn(a, b, out, trans_out, dual_off, splitk, bn, a_tiled_rows)
     return out
