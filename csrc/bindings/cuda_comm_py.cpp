@@ -37,6 +37,39 @@ ccl::KvStore make_kv(const c10::intrusive_ptr<c10d::Store>& store) {
   return kv;
 }
 
+void fill_moe_dispatch(ccl::MoeArgs& a, const at::Tensor& x, const at::Tensor& idx, at::Tensor& out_x, at::Tensor& meta,
+                       at::Tensor& count, int experts_per_rank) {
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.dim() == 2, "x: [tokens, hidden] bf16");
+  TORCH_CHECK(idx.scalar_type() == at::kInt && idx.is_contiguous() && idx.dim() == 2 && idx.size(0) == x.size(0), "expert_idx: [tokens, topk] int32");
+  TORCH_CHECK(out_x.scalar_type() == at::kBFloat16 && out_x.is_contiguous() && out_x.size(1) == x.size(1), "out_x: [rows, hidden] bf16");
+  TORCH_CHECK(meta.scalar_type() == at::kInt && meta.is_contiguous() && meta.size(0) >= out_x.size(0) && meta.size(1) == 3, "meta: [rows, 3] int32");
+  TORCH_CHECK(count.scalar_type() == at::kInt && count.numel() >= 9, "count: [9] int32");
+  a.x = x.data_ptr();
+  a.expert_idx = idx.data_ptr<int>();
+  a.out_x = out_x.data_ptr();
+  a.out_meta = meta.data_ptr<int>();
+  a.out_count = count.data_ptr<int>();
+  a.tokens = (int)x.size(0);
+  a.topk = (int)idx.size(1);
+  a.hidden = (int)x.size(1);
+  a.experts_per_rank = experts_per_rank;
+}
+
+void fill_moe_combine(ccl::MoeArgs& a, const at::Tensor& y, const at::Tensor& meta, const at::Tensor& count,
+                      const at::Tensor& gate, at::Tensor& out) {
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.is_contiguous() && y.dim() == 2, "y: [rows, hidden] bf16");
+  TORCH_CHECK(gate.scalar_type() == at::kFloat && gate.is_contiguous() && gate.dim() == 2, "gate: [tokens, topk] fp32");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.is_contiguous() && out.size(0) == gate.size(0) && out.size(1) == y.size(1), "out: [tokens, hidden] bf16");
+  a.x = y.data_ptr();
+  a.out_meta = const_cast<int*>(meta.data_ptr<int>());
+  a.in_rows = count.data_ptr<int>();
+  a.gate = gate.data_ptr<float>();
+  a.out_x = out.data_ptr();
+  a.tokens = (int)gate.size(0);
+  a.topk = (int)gate.size(1);
+  a.hidden = (int)y.size(1);
+}
+
 namespace {
 
 void cu(cudaError_t e, const char* what) {
@@ -241,6 +274,24 @@ struct PyComm {
     cu(comm->ag_gemm(args, stream()), "ag_gemm");
   }
 
+  // MoE dispatch: x[r] [T, H] bf16, idx[r] [T, K] int32 -> out_x[r] [cap_rows, H], meta[r] [cap_rows, 3] int32, count[r] [1+W] int32
+  void moe_dispatch(std::vector<at::Tensor> xs, std::vector<at::Tensor> idx, std::vector<at::Tensor> out_x,
+                    std::vector<at::Tensor> meta, std::vector<at::Tensor> count, int experts_per_rank) {
+    check_n(xs.size());
+    std::vector<ccl::MoeArgs> args(xs.size());
+    for (size_t i = 0; i < xs.size(); ++i) fill_moe_dispatch(args[i], xs[i], idx[i], out_x[i], meta[i], count[i], experts_per_rank);
+    cu(comm->moe_dispatch(args, stream()), "moe_dispatch");
+  }
+  // MoE combine: y[r] [rows, H] bf16 (expert outputs, dispatch order) -> out[r] [T, H]
+  void moe_combine(std::vector<at::Tensor> ys, std::vector<at::Tensor> meta, std::vector<at::Tensor> count,
+                   std::vector<at::Tensor> gate, std::vector<at::Tensor> outs) {
+    check_n(ys.size());
+    std::vector<ccl::MoeArgs> args(ys.size());
+    for (size_t i = 0; i < ys.size(); ++i) fill_moe_combine(args[i], ys[i], meta[i], count[i], gate[i], outs[i]);
+    cu(comm->moe_combine(args, stream()), "moe_combine");
+  }
+  int moe_capacity(int hidden) { return comm->moe_capacity(hidden); }
+
   std::vector<int> status() {
     int r = 0, p = 0, ph = 0;
     int code = comm->poll_status(&r, &p, &ph);
@@ -307,6 +358,9 @@ void bind_cuda_comm(py::module& m) {
       .def("allreduce_residual_rmsnorm", &PyComm::allreduce_residual_rmsnorm)
       .def("gemm_rs", &PyComm::gemm_rs)
       .def("ag_gemm", &PyComm::ag_gemm)
+      .def("moe_dispatch", &PyComm::moe_dispatch)
+      .def("moe_combine", &PyComm::moe_combine)
+      .def("moe_capacity", &PyComm::moe_capacity)
       .def("status", &PyComm::status)
       .def("clear_status", [](PyComm& c) { c.comm->clear_status(); });
 }

@@ -206,6 +206,25 @@ void bind_process_group(py::module& m) {
              TORCH_CHECK(out.size(0) == r.M && out.size(1) == r.N, "out must be [M, N]");
              C10_CUDA_CHECK(c.ag_gemm({r}, c10::cuda::getCurrentCUDAStream()));
            })
+      .def("fused_moe_dispatch",
+           [](ProcessGroupCCL& pg, const at::Tensor& x, const at::Tensor& idx, at::Tensor& out_x, at::Tensor& meta,
+              at::Tensor& count, int experts_per_rank) {
+             auto& c = cuda_comm_of(pg, x);
+             c10::cuda::CUDAGuard g(x.device());
+             ccl::MoeArgs a;
+             fill_moe_dispatch(a, x, idx, out_x, meta, count, experts_per_rank);
+             C10_CUDA_CHECK(c.moe_dispatch({a}, c10::cuda::getCurrentCUDAStream()));
+           })
+      .def("fused_moe_combine",
+           [](ProcessGroupCCL& pg, const at::Tensor& y, const at::Tensor& meta, const at::Tensor& count,
+              const at::Tensor& gate, at::Tensor& out) {
+             auto& c = cuda_comm_of(pg, y);
+             c10::cuda::CUDAGuard g(y.device());
+             ccl::MoeArgs a;
+             fill_moe_combine(a, y, meta, count, gate, out);
+             C10_CUDA_CHECK(c.moe_combine({a}, c10::cuda::getCurrentCUDAStream()));
+           })
+      .def("moe_capacity", [](ProcessGroupCCL& pg, const at::Tensor& like) { return cuda_comm_of(pg, like).moe_capacity((int)like.size(-1)); })
       .def("cuda_comm_status", [](ProcessGroupCCL& pg, const at::Tensor& t) {
         auto& c = cuda_comm_of(pg, t);
         int r = 0, p = 0, ph = 0;

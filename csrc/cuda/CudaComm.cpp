@@ -416,6 +416,42 @@ cudaError_t CudaComm::ag_gemm(const std::vector<AgGemmArgs>& args, cudaStream_t 
   return cudaSuccess;
 }
 
+int CudaComm::moe_capacity(int hidden) const {
+  const size_t per_src = cfg_.half_bytes / world_;
+  const size_t fixed = (size_t)kMaxBlocks * 4 + 256;
+  if (per_src <= fixed) return 0;
+  return (int)((per_src - fixed) / ((size_t)hidden * 2 + 8));
+}
+
+cudaError_t CudaComm::moe_dispatch(std::vector<MoeArgs> args, cudaStream_t stream) {
+  CCL_CHECK_ARGS(args)
+  DeviceGuard g(device_);
+  const int cap = moe_capacity(args[0].hidden);
+  if (cap <= 0 || args[0].hidden % 8 != 0) return cudaErrorInvalidValue;
+  for (auto& a : args) {
+    a.cap = cap;
+    a.slot_bytes = moe_dispatch_slot_bytes(cap, a.hidden);
+    if (a.slot_bytes * world_ > cfg_.half_bytes) {
+      a.cap = cap - 64;
+      a.slot_bytes = moe_dispatch_slot_bytes(a.cap, a.hidden);
+    }
+  }
+  LaunchCfg lc = launch_cfg(std::min(64, cfg_.max_blocks), 512, stream);
+  cudaError_t e = launch_moe_dispatch(emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  if (e == cudaSuccess) ++launches_;
+  return e;
+}
+
+cudaError_t CudaComm::moe_combine(std::vector<MoeArgs> args, cudaStream_t stream) {
+  CCL_CHECK_ARGS(args)
+  DeviceGuard g(device_);
+  if ((size_t)args[0].tokens * args[0].topk * args[0].hidden * 2 > cfg_.half_bytes) return cudaErrorInvalidValue;
+  LaunchCfg lc = launch_cfg(std::min(64, cfg_.max_blocks), 512, stream);
+  cudaError_t e = launch_moe_combine(emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  if (e == cudaSuccess) ++launches_;
+  return e;
+}
+
 cudaError_t CudaComm::barrier_single_rank(int i, cudaStream_t stream) {
   DeviceGuard g(device_);
   if (i < 0 || i >= nctx()) return cudaErrorInvalidValue;

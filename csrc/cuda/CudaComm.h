@@ -20,6 +20,7 @@
 
 #include "cuda/kernels/collectives.h"
 #include "cuda/kernels/gemm_collective.h"
+#include "cuda/kernels/moe_a2a.h"
 
 namespace ccl {
 
@@ -95,6 +96,12 @@ class CudaComm {
   // Fused tensor-parallel GEMMs (one entry per rank context, like the collectives).
   cudaError_t gemm_rs(const std::vector<GemmRsArgs>& args, cudaStream_t stream);
   cudaError_t ag_gemm(const std::vector<AgGemmArgs>& args, cudaStream_t stream);
+
+  // Expert-parallel MoE token exchange. `cap` rows per (source, destination) pair is derived
+  // from the arena size; moe_capacity() reports it.
+  int moe_capacity(int hidden) const;
+  cudaError_t moe_dispatch(std::vector<MoeArgs> args, cudaStream_t stream);
+  cudaError_t moe_combine(std::vector<MoeArgs> args, cudaStream_t stream);
 
   // Capacity (bytes per rank) of the one-shot fused norm path.
   size_t fused_norm_capacity() const { return cfg_.half_bytes / world_; }

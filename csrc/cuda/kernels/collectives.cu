@@ -15,6 +15,7 @@
 // release flag; pulls are system-coherent 16-byte loads from the peer's arena after an acquire.
 #include "collectives.h"
 #include "comm.cuh"
+#include "gemm.h"
 
 #include <cstdio>
 
@@ -661,9 +662,15 @@ cudaError_t launch_pair(KR kreal, KE kemu, const RankCtx* ctx, const ArgsT* args
     L.args = *args;
     L.ctx_table = nullptr;
     L.args_table = nullptr;
-    dim3 grid(cfg.nblocks, 1, 1);
-    kreal<<<grid, block, 0, cfg.stream>>>(L);
-    return cudaGetLastError();
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(cfg.nblocks, 1, 1);
+    lc.blockDim = block;
+    lc.dynamicSmemBytes = 0;
+    lc.stream = cfg.stream;
+    cudaLaunchAttribute attr[1];
+    lc.attrs = attr;
+    lc.numAttrs = pdl_launch_attr(&attr[0]);
+    return cudaLaunchKernelEx(&lc, kreal, L);
   }
   LT<true> L;
   L.ctx = RankCtx{};

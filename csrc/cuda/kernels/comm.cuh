@@ -42,6 +42,10 @@ struct Sync {
 
   __device__ Sync(const RankCtx& c, int* failed_smem, bool enabled)
       : ctx(c), blk(blockIdx.x), sync_enabled(enabled), failed(failed_smem) {
+    // programmatic dependent launch: let the next kernel start its prologue, then wait for the
+    // kernels before this one (they produced the input and advanced the epoch)
+    ptx::griddep_launch_dependents();
+    ptx::griddep_wait();
     if (threadIdx.x == 0) *failed = 0;
     epoch = ctx.state ? *reinterpret_cast<volatile uint32_t*>(ctx.state) : 0u;
     __syncthreads();

@@ -6,9 +6,16 @@
 // writes an un-normalised partial (running max, sum, output) to a scratch buffer; the last CTA
 // to finish a (sequence, head) combines the partials. head_dim is fixed at 128.
 //
-// Thread mapping: 8 lanes share one cache position (16 dims = 32 bytes = one sector each), so a
-// warp covers 4 positions per step and a 4-warp CTA 16.
+// The K and V rows of one (sequence, head) are contiguous in the cache, so one elected thread
+// streams them with untiled bulk copies (cp.async.bulk, completion on an mbarrier) into a 4-stage
+// shared-memory ring of 32-position chunks; with three CTAs per SM that keeps ~190 KB of loads in
+// flight per SM without spending registers on them. Thread mapping for the math: 8 lanes share
+// one cache position (16 dims = 32 bytes each), so a warp covers 4 positions per step and a
+// 4-warp CTA 16.
 #include "decode_attention.h"
+
+#include "gemm.h"
+#include "ptx.cuh"
 
 #include <cuda_bf16.h>
 #include <stdint.h>
@@ -18,9 +25,25 @@ namespace {
 
 constexpr int kHD = 128;
 constexpr int kThreads = 128;
-constexpr int kGroups = kThreads / 8;  // positions in flight per CTA step
+constexpr int kGroups = kThreads / 8;  // positions per CTA step
+constexpr int kChunk = 32;             // positions per pipeline stage
+constexpr int kStages = 3;             // 48 KB of ring: four CTAs fit on an SM
+constexpr int kRowBytes = kHD * 2;
+constexpr int kStageBytes = 2 * kChunk * kRowBytes;  // K chunk followed by V chunk
+constexpr size_t kDynSmem = (size_t)kStages * kStageBytes + 128;
 
 __device__ __forceinline__ void load16(const __nv_bfloat16* p, float (&f)[16]) {
+  const uint4 a = reinterpret_cast<const uint4*>(p)[0];
+  const uint4 b = reinterpret_cast<const uint4*>(p)[1];
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+    f[2 * i] = __low2float(h);
+    f[2 * i + 1] = __high2float(h);
+  }
+}
+__device__ __forceinline__ void load16_smem(const unsigned char* p, float (&f)[16]) {
   const uint4 a = reinterpret_cast<const uint4*>(p)[0];
   const uint4 b = reinterpret_cast<const uint4*>(p)[1];
   const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
@@ -56,6 +79,8 @@ __device__ __forceinline__ void rope16(float (&own)[16], const float (&partner)[
 }
 
 __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const DecodeAttnParams p) {
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();  // q/k/v of the new token come from the projection kernel just before
   const int split = blockIdx.x;
   const int h = blockIdx.y;
   const int b = blockIdx.z;
@@ -119,52 +144,80 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const Decode
 #pragma unroll
   for (int i = 0; i < 16; ++i) o[i] = 0.f;
 
-  // Two positions per step and lane group: the loads of the second are in flight while the first
-  // is being reduced (the kernel is bound by memory latency, not by arithmetic).
-  auto fetch = [&](int t, float (&k)[16], float (&v)[16]) {
-    if (t == pos) {
+  // ---- stream [t0, t1) through the shared-memory ring ---------------------------------------
+  extern __shared__ __align__(128) unsigned char dyn_smem[];
+  unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(dyn_smem) + 127) & ~uintptr_t(127));
+  __shared__ __align__(8) uint64_t s_full[kStages];
+  const int n_chunks = (t1 > t0) ? (t1 - t0 + kChunk - 1) / kChunk : 0;
+  if (tid == 0) {
+    for (int i = 0; i < kStages; ++i) ptx::mbar_init(&s_full[i], 1);
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+  auto issue = [&](int c) {  // thread 0 only
+    const int st = c % kStages;
+    const int start = t0 + c * kChunk;
+    const int n = min(kChunk, t1 - start);
+    const uint32_t bytes = (uint32_t)n * kRowBytes;
+    unsigned char* dst = ring + (size_t)st * kStageBytes;
+    ptx::mbar_arrive_expect_tx(&s_full[st], 2 * bytes);
+    ptx::bulk_load(dst, kc + (size_t)start * kHD, bytes, &s_full[st]);
+    ptx::bulk_load(dst + kChunk * kRowBytes, vc + (size_t)start * kHD, bytes, &s_full[st]);
+  };
+  if (tid == 0)
+    for (int c = 0; c < n_chunks && c < kStages; ++c) issue(c);
+  bool ok = true;
+  for (int c = 0; c < n_chunks; ++c) {
+    const int st = c % kStages;
+    if (!ptx::mbar_wait(&s_full[st], (c / kStages) & 1)) ok = false;  // bounded; result is then invalid
+    const unsigned char* ks = ring + (size_t)st * kStageBytes;
+    const unsigned char* vs = ks + kChunk * kRowBytes;
+    const int start = t0 + c * kChunk;
+    const int n = min(kChunk, t1 - start);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        k[i] = s_new_k[j * 16 + i];
-        v[i] = s_new_v[j * 16 + i];
+    for (int pass = 0; pass < kChunk / kGroups; ++pass) {
+      const int lt = pass * kGroups + g;
+      const int t = start + lt;
+      float k[16], v[16];
+      if (lt < n) {
+        if (t == pos) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            k[i] = s_new_k[j * 16 + i];
+            v[i] = s_new_v[j * 16 + i];
+          }
+        } else {
+          load16_smem(ks + (size_t)lt * kRowBytes + j * 32, k);
+          load16_smem(vs + (size_t)lt * kRowBytes + j * 32, v);
+        }
       }
-    } else {
-      load16(kc + (size_t)t * kHD + j * 16, k);
-      load16(vc + (size_t)t * kHD + j * 16, v);
+      // all 8 lanes of a group share `lt`, so the branch is uniform within the shuffle mask
+      if (lt < n) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) s += q[i] * k[i];
+        s += __shfl_xor_sync(gmask, s, 1);
+        s += __shfl_xor_sync(gmask, s, 2);
+        s += __shfl_xor_sync(gmask, s, 4);
+        const float mn = fmaxf(m, s);
+        const float corr = __expf(m - mn);
+        const float pr = __expf(s - mn);
+        l = l * corr + pr;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = o[i] * corr + pr * v[i];
+        m = mn;
+      }
     }
-  };
-  auto step = [&](const float (&k)[16], const float (&v)[16]) {
-    float s = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) s += q[i] * k[i];
-    // the 4 position groups of a warp run different trip counts: synchronise per 8-lane group
-    s += __shfl_xor_sync(gmask, s, 1);
-    s += __shfl_xor_sync(gmask, s, 2);
-    s += __shfl_xor_sync(gmask, s, 4);
-    const float mn = fmaxf(m, s);
-    const float corr = __expf(m - mn);
-    const float pr = __expf(s - mn);
-    l = l * corr + pr;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) o[i] = o[i] * corr + pr * v[i];
-    m = mn;
-  };
-  int t = t0 + g;
-  for (; t + kGroups < t1; t += 2 * kGroups) {
-    float k0[16], v0[16], k1[16], v1[16];
-    fetch(t, k0, v0);
-    fetch(t + kGroups, k1, v1);
-    step(k0, v0);
-    step(k1, v1);
+    __syncthreads();  // everyone is done with this stage: refill it
+    if (tid == 0 && c + kStages < n_chunks) issue(c + kStages);
   }
-  if (t < t1) {
-    float k0[16], v0[16];
-    fetch(t, k0, v0);
-    step(k0, v0);
-  }
+  if (!ok && p.status && tid == 0) atomicExch(p.status, 201);
 
   // combine the kGroups position groups of this CTA
-  __shared__ float s_m[kGroups], s_l[kGroups], s_o[kGroups][kHD];
+  // (the ring is free now — every chunk was consumed before the last barrier — and is reused
+  // for the partial outputs)
+  __shared__ float s_m[kGroups], s_l[kGroups];
+  float (*s_o)[kHD] = reinterpret_cast<float (*)[kHD]>(ring);
   if (j == 0) {
     s_m[g] = m;
     s_l[g] = l;
@@ -227,7 +280,7 @@ size_t decode_attention_scratch_bytes(int batch, int n_heads, int nsplit) {
 
 int decode_attention_default_splits(int batch, int n_heads, int max_context) {
   const int pairs = batch * n_heads;
-  int s = (4 * 148) / pairs;  // four CTAs fit on an SM (registers): fill them, but stay within one wave
+  int s = (4 * 148) / pairs;  // four CTAs fit on an SM (shared-memory ring): fill them, but stay within one wave
   const int cap = (max_context + 255) / 256;  // at least 256 positions per split
   if (s > cap) s = cap;
   if (s < 1) s = 1;
@@ -238,9 +291,21 @@ int decode_attention_default_splits(int batch, int n_heads, int max_context) {
 cudaError_t decode_attention(const DecodeAttnParams& p, int batch, int nsplit, cudaStream_t stream) {
   if (p.head_dim != kHD) return cudaErrorInvalidValue;
   if (nsplit > 1 && (!p.scratch || !p.counters)) return cudaErrorInvalidValue;
-  dim3 grid(nsplit, p.n_heads, batch);
-  decode_attention_kernel<<<grid, kThreads, 0, stream>>>(p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nsplit, p.n_heads, batch);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDynSmem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  cfg.dynamicSmemBytes = kDynSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_launch_attr(&attr[0]);
+  return cudaLaunchKernelEx(&cfg, decode_attention_kernel, p);
 }
 
 }  // namespace ccl

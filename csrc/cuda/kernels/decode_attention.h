@@ -20,6 +20,7 @@ struct DecodeAttnParams {
   unsigned int* counters;    // [batch * n_heads], zero-initialised once; the kernel re-zeroes them
   int n_heads, n_kv_heads, head_dim, max_seq;
   float scale;               // 1/sqrt(head_dim)
+  int* status = nullptr;     // optional device error word (set if a bounded wait expires)
 };
 
 size_t decode_attention_scratch_bytes(int batch, int n_heads, int nsplit);

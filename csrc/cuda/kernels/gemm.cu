@@ -6,12 +6,27 @@
 
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 
 namespace ccl {
 
 namespace {
 std::atomic<uint64_t> g_launches{0};
 }
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("CCL_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+int pdl_launch_attr(cudaLaunchAttribute* attr) {
+  if (!pdl_enabled()) return 0;
+  attr->id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr->val.programmaticStreamSerializationAllowed = 1;
+  return 1;
+}
+
 uint64_t launch_count() { return g_launches.load(); }
 void launch_count_add(uint64_t n) { g_launches.fetch_add(n); }
 void launch_count_reset() { g_launches.store(0); }
@@ -116,6 +131,7 @@ cudaError_t launch(const GemmDesc& d, int splitk, cudaStream_t stream) {
   p.status = d.status;
   p.acquire_a = 0;
   p.a_tiled = d.a_tiled;
+  p.a_static = d.a_tiled;  // packed operands are weights: nothing on the stream produces them
   p.k_tiles = k_iters;
 
   auto kern = gemm_kernel<BN, DUAL, OutT>;
@@ -130,13 +146,13 @@ cudaError_t launch(const GemmDesc& d, int splitk, cudaStream_t stream) {
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = splitk;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 1 + pdl_launch_attr(&attr[1]);
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
   if (e == cudaSuccess) g_launches.fetch_add(1);
   return e;
@@ -177,8 +193,9 @@ cudaError_t gemm_bf16_tn(const GemmDesc& d, cudaStream_t stream) {
     const int64_t k_iters = (d.K + 63) / 64;
     splitk = 1;
     if (bn <= 32) {
-      // memory-bound: fill two CTA slots per SM (296 in all), keeping >= 4 K-steps per CTA
-      splitk = (int)(296 / tiles);
+      // memory-bound: measured best on B200 with roughly 200 CTAs in flight (between one and
+      // two per SM), keeping >= 4 K-steps per CTA
+      splitk = (int)((200 + tiles / 2) / tiles);
       if (splitk > 8) splitk = 8;
       while (splitk > 1 && k_iters / splitk < 4) --splitk;
       if (splitk < 1) splitk = 1;

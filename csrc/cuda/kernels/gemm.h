@@ -31,6 +31,13 @@ struct GemmDesc {
 // Launches on `stream`; returns cudaSuccess or the launch / argument error.
 cudaError_t gemm_bf16_tn(const GemmDesc& d, cudaStream_t stream);
 
+// Programmatic dependent launch for the kernels of this library (env CCL_PDL, default on): each
+// kernel is launched with the programmatic-serialization attribute, triggers its successor early
+// and waits for its predecessor only where it first touches data that an earlier kernel produced.
+bool pdl_enabled();
+// Fills `attr` for cudaLaunchKernelEx; returns the number of attributes written (0 or 1).
+int pdl_launch_attr(cudaLaunchAttribute* attr);
+
 // Number of kernels of this library launched since the last call to reset (per process).
 uint64_t launch_count();
 void launch_count_add(uint64_t n);

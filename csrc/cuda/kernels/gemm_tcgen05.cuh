@@ -49,6 +49,8 @@ struct Params {
   int a_tiled;          // 1: A is pre-packed as contiguous 128x64 tiles, tile (mt, kt) at packed
                         //    row (mt * k_tiles + kt) * 128 of a [*, 64] matrix (see gemm.h)
   int k_tiles;          // K / 64 of the packed A
+  int a_static;         // 1: A is constant data (weights): it may be fetched before the
+                        //    predecessor kernel on the stream has finished (programmatic dependent launch)
   int acquire_a;        // 1: A was written by another GPU and observed through a flag; order the
                         //    TMA (async proxy) reads after that acquire with a proxy fence
 };
@@ -192,25 +194,20 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const C
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  ptx::griddep_launch_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
       ptx::prefetch_tmap(tma_a);
       ptx::prefetch_tmap(tma_b);
       if (p.acquire_a) asm volatile("fence.proxy.async;" ::: "memory");
-      for (int i = 0; i < n_iters; ++i) {
+      auto load_a = [&](int i) {
         const int s = i % stages;
-        const uint32_t ph = (i / stages) & 1;
-        if (!ptx::mbar_wait(&bars->empty[s], ph ^ 1)) {
-          bars->failed = 1;
-          if (p.status) atomicExch(p.status, 101);
-          break;
-        }
         uint8_t* st = smem + (size_t)s * kStage;
-        ptx::mbar_arrive_expect_tx(&bars->full[s], kStage);
         const int kx = (it_begin + i) * kBK;
+        ptx::mbar_arrive_expect_tx(&bars->full[s], kStage);
         if (p.a_tiled) {
-          // one contiguous 16 KB tile per load: every DRAM page that is opened is fully used
+          // one contiguous 16 KB tile per load
           const int kt = it_begin + i;
           ptx::tma_load_2d(st, tma_a, &bars->full[s], 0, ((tc.a_row / kBM) * p.k_tiles + kt) * kBM);
           if (DUAL)
@@ -220,7 +217,34 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const C
           ptx::tma_load_2d(st, tma_a, &bars->full[s], kx, tc.a_row);
           if (DUAL) ptx::tma_load_2d(st + kABytes, tma_a, &bars->full[s], kx, tc.a_row + p.dual_off);
         }
-        ptx::tma_load_2d(st + kABytes * (DUAL ? 2 : 1), tma_b, &bars->full[s], kx, n0);
+      };
+      auto load_b = [&](int i) {
+        const int s = i % stages;
+        uint8_t* st = smem + (size_t)s * kStage;
+        ptx::tma_load_2d(st + kABytes * (DUAL ? 2 : 1), tma_b, &bars->full[s], (it_begin + i) * kBK, n0);
+      };
+      int i0 = 0;
+      if (p.a_static) {
+        // A (weights) is not produced by any earlier kernel: fill the pipeline with A tiles while
+        // the predecessor kernel is still running, then wait for it and fetch the B tiles.
+        const int pre = n_iters < stages ? n_iters : stages;
+        for (int i = 0; i < pre; ++i) load_a(i);
+        ptx::griddep_wait();
+        for (int i = 0; i < pre; ++i) load_b(i);
+        i0 = pre;
+      } else {
+        ptx::griddep_wait();
+      }
+      for (int i = i0; i < n_iters; ++i) {
+        const int s = i % stages;
+        const uint32_t ph = (i / stages) & 1;
+        if (!ptx::mbar_wait(&bars->empty[s], ph ^ 1)) {
+          bars->failed = 1;
+          if (p.status) atomicExch(p.status, 101);
+          break;
+        }
+        load_a(i);
+        load_b(i);
       }
     }
   } else if (warp == 1) {

@@ -36,6 +36,18 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute
+// may start while its predecessor on the stream still runs. `griddep_launch_dependents` lets the
+// successor's CTAs be scheduled early; `griddep_wait` blocks until every predecessor grid has
+// completed and its writes are visible. Code before the wait may only touch memory that no
+// earlier kernel writes (weights, constants, its own shared memory).
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // system-scope signalling between GPUs
 // ---------------------------------------------------------------------------------------------
@@ -207,6 +219,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, ui
       " [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
+}
+// Untiled bulk copy global -> shared (no multicast): both addresses 16-byte aligned, size a
+// multiple of 16 bytes; completion is signalled on the mbarrier as transaction bytes.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const void* tmap, const void* smem_src, int32_t x,
                                              int32_t y) {

@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "6d99678bac48ccd2325915631b494121a1415d29"
+git_version = "1f528759742ec017cddbbc7db7215629c9ee94ad"
