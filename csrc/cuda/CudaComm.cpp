@@ -220,7 +220,8 @@ static int threads_for(size_t vecs, int nblocks, int max_threads) {
 }
 
 int CudaComm::blocks_for(size_t vecs, int cap) const {
-  const size_t per_block = (size_t)cfg_.threads * 4;
+  // one 16-byte vector per thread and peer up to the CTA cap, more beyond it
+  const size_t per_block = (size_t)cfg_.threads;
   size_t b = (vecs + per_block - 1) / per_block;
   if (b < 1) b = 1;
   if (b > (size_t)cap) b = cap;

@@ -96,6 +96,69 @@ __device__ __forceinline__ void copy_user_to_user(const T* src, T* dst, size_t c
     store_vec(dst, vbase + j, count, ald, load_vec(src, vbase + j, count, als));
 }
 
+// Peer-parallel copies: the transfers to / from all peers advance together, so a thread has one
+// independent load per peer in flight instead of walking the peers one after the other (the
+// per-peer latency, not the bandwidth, dominates mid-sized messages). Each peer keeps its own
+// CTA partition (sub_slice of ITS length): the flag of CTA b covers exactly what CTA b of the
+// other side reads or wrote.
+constexpr int kNP = kMaxRanks - 1;
+template <typename T>
+struct PeerSet {
+  const T* user_src[kNP];  // push: source in user memory
+  T* user_dst[kNP];        // pull: destination in user memory
+  size_t count[kNP];       // elements of that user array
+  size_t vbase[kNP];       // vector offset in the user array
+  char* stage[kNP];        // staging address of vector 0 of the transfer
+  Range r[kNP];            // this CTA's share, in vectors
+  int np;
+};
+
+template <typename T>
+__device__ __forceinline__ void push_peers(const PeerSet<T>& ps) {
+  size_t span = 0;
+  bool al[kNP];
+#pragma unroll
+  for (int q = 0; q < kNP; ++q) {
+    if (q < ps.np) {
+      const size_t n = ps.r[q].j1 - ps.r[q].j0;
+      span = n > span ? n : span;
+      al[q] = is_aligned16(ps.user_src[q]);
+    }
+  }
+  for (size_t k = threadIdx.x; k < span; k += blockDim.x) {
+    Vec<T> v[kNP];
+#pragma unroll
+    for (int q = 0; q < kNP; ++q)
+      if (q < ps.np && ps.r[q].j0 + k < ps.r[q].j1) v[q] = load_vec(ps.user_src[q], ps.vbase[q] + ps.r[q].j0 + k, ps.count[q], al[q]);
+#pragma unroll
+    for (int q = 0; q < kNP; ++q)
+      if (q < ps.np && ps.r[q].j0 + k < ps.r[q].j1) store_stage(ps.stage[q] + (ps.r[q].j0 + k) * 16, v[q]);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void pull_peers(const PeerSet<T>& ps) {
+  size_t span = 0;
+  bool al[kNP];
+#pragma unroll
+  for (int q = 0; q < kNP; ++q) {
+    if (q < ps.np) {
+      const size_t n = ps.r[q].j1 - ps.r[q].j0;
+      span = n > span ? n : span;
+      al[q] = is_aligned16(ps.user_dst[q]);
+    }
+  }
+  for (size_t k = threadIdx.x; k < span; k += blockDim.x) {
+    Vec<T> v[kNP];
+#pragma unroll
+    for (int q = 0; q < kNP; ++q)
+      if (q < ps.np && ps.r[q].j0 + k < ps.r[q].j1) v[q] = load_stage<T>(ps.stage[q] + (ps.r[q].j0 + k) * 16);
+#pragma unroll
+    for (int q = 0; q < kNP; ++q)
+      if (q < ps.np && ps.r[q].j0 + k < ps.r[q].j1) store_vec(ps.user_dst[q], ps.vbase[q] + ps.r[q].j0 + k, ps.count[q], al[q], v[q]);
+  }
+}
+
 template <typename T>
 __device__ __forceinline__ Vec<T> finish_vec(const typename Acc<T>::type (&acc)[Vec<T>::kN],
                                              const CollArgs& a) {
@@ -221,12 +284,20 @@ __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const __grid_co
     const size_t spr = ceil_div(n, (size_t)W);
     // phase 0: scatter my contribution to each shard's owner
     if (do_work) {
-      for (int q = 1; q < W; ++q) {
-        const int p = (me + q) % W;
-        const size_t len = clamp_len(n, (size_t)p * spr, spr);
-        copy_user_to_stage(in, count, base + (size_t)p * spr,
-                           sy.half(p, rd) + (size_t)me * stride_v * 16, sub_slice(len));
+      PeerSet<T> ps;
+      ps.np = W - 1;
+#pragma unroll
+      for (int q = 0; q < kNP; ++q) {
+        if (q < W - 1) {
+          const int p = (me + q + 1) % W;
+          ps.user_src[q] = in;
+          ps.count[q] = count;
+          ps.vbase[q] = base + (size_t)p * spr;
+          ps.stage[q] = sy.half(p, rd) + (size_t)me * stride_v * 16;
+          ps.r[q] = sub_slice(clamp_len(n, (size_t)p * spr, spr));
+        }
       }
+      push_peers<T>(ps);
     }
     sy.signal_all(0, rd);
     ok = sy.wait_all(0, rd);
@@ -257,12 +328,20 @@ __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const __grid_co
       ok = sy.wait_all(1, rd);
       if (!ok) break;
       if (do_work) {
-        for (int q = 1; q < W; ++q) {
-          const int p = (me + q) % W;
-          const size_t len = clamp_len(n, (size_t)p * spr, spr);
-          copy_stage_to_user(sy.half(p, rd) + (size_t)W * stride_v * 16, out, count,
-                             base + (size_t)p * spr, sub_slice(len));
+        PeerSet<T> ps;
+        ps.np = W - 1;
+#pragma unroll
+        for (int q = 0; q < kNP; ++q) {
+          if (q < W - 1) {
+            const int p = (me + q + 1) % W;
+            ps.user_dst[q] = out;
+            ps.count[q] = count;
+            ps.vbase[q] = base + (size_t)p * spr;
+            ps.stage[q] = sy.half(p, rd) + (size_t)W * stride_v * 16;
+            ps.r[q] = sub_slice(clamp_len(n, (size_t)p * spr, spr));
+          }
         }
+        pull_peers<T>(ps);
       }
     }
   }
@@ -292,13 +371,21 @@ __global__ void __launch_bounds__(1024) reduce_scatter_kernel(const __grid_const
   for (int rd = 0; rd < rounds && ok; ++rd) {
     const size_t vb = (size_t)rd * stride_v;
     if (do_work) {
-      for (int q = 1; q < W; ++q) {
-        const int p = (me + q) % W;
-        const size_t nv = ceil_div((size_t)a.in_cnt[p], (size_t)N);
-        const size_t len = clamp_len(nv, vb, stride_v);
-        copy_user_to_stage(reinterpret_cast<const TIn*>(a.in_piece[p]), (size_t)a.in_cnt[p], vb,
-                           sy.half(p, rd) + (size_t)me * stride_v * 16, sub_slice(len));
+      PeerSet<TIn> ps;
+      ps.np = W - 1;
+#pragma unroll
+      for (int q = 0; q < kNP; ++q) {
+        if (q < W - 1) {
+          const int p = (me + q + 1) % W;
+          const size_t nv = ceil_div((size_t)a.in_cnt[p], (size_t)N);
+          ps.user_src[q] = reinterpret_cast<const TIn*>(a.in_piece[p]);
+          ps.count[q] = (size_t)a.in_cnt[p];
+          ps.vbase[q] = vb;
+          ps.stage[q] = sy.half(p, rd) + (size_t)me * stride_v * 16;
+          ps.r[q] = sub_slice(clamp_len(nv, vb, stride_v));
+        }
       }
+      push_peers<TIn>(ps);
     }
     sy.signal_all(0, rd);
     ok = sy.wait_all(0, rd);
@@ -376,13 +463,21 @@ __global__ void __launch_bounds__(1024) all_gather_kernel(const __grid_constant_
     ok = sy.wait_all(0, rd);
     if (!ok) break;
     if (do_work) {
-      for (int q = 1; q < W; ++q) {
-        const int p = (me + q) % W;
-        const size_t pb = a.out_cnt[p];
-        const size_t len = clamp_len(ceil_div(pb, (size_t)16), vb, stride_v);
-        const char* src = (a.mode == 0) ? sy.half(p, rd) : sy.half(me, rd) + (size_t)p * stride_v * 16;
-        copy_stage_to_user(src, reinterpret_cast<T*>(a.out_piece[p]), pb, vb, sub_slice(len));
+      PeerSet<T> ps;
+      ps.np = W - 1;
+#pragma unroll
+      for (int q = 0; q < kNP; ++q) {
+        if (q < W - 1) {
+          const int p = (me + q + 1) % W;
+          const size_t pb = a.out_cnt[p];
+          ps.user_dst[q] = reinterpret_cast<T*>(a.out_piece[p]);
+          ps.count[q] = pb;
+          ps.vbase[q] = vb;
+          ps.stage[q] = (a.mode == 0) ? sy.half(p, rd) : sy.half(me, rd) + (size_t)p * stride_v * 16;
+          ps.r[q] = sub_slice(clamp_len(ceil_div(pb, (size_t)16), vb, stride_v));
+        }
       }
+      pull_peers<T>(ps);
     }
   }
   sy.finish(rounds);
@@ -429,13 +524,21 @@ __global__ void __launch_bounds__(1024) all_to_all_kernel(const __grid_constant_
     const int rd = first + i;
     const size_t vb = (size_t)i * stride_v;
     if (do_work) {
-      for (int q = 1; q < W; ++q) {
-        const int p = (me + q) % W;
-        const size_t pb = a.in_cnt[p];
-        const size_t len = clamp_len(ceil_div(pb, (size_t)16), vb, stride_v);
-        copy_user_to_stage(reinterpret_cast<const T*>(a.in_piece[p]), pb, vb,
-                           sy.half(p, rd) + (size_t)me * stride_v * 16, sub_slice(len));
+      PeerSet<T> ps;
+      ps.np = W - 1;
+#pragma unroll
+      for (int q = 0; q < kNP; ++q) {
+        if (q < W - 1) {
+          const int p = (me + q + 1) % W;
+          const size_t pb = a.in_cnt[p];
+          ps.user_src[q] = reinterpret_cast<const T*>(a.in_piece[p]);
+          ps.count[q] = pb;
+          ps.vbase[q] = vb;
+          ps.stage[q] = sy.half(p, rd) + (size_t)me * stride_v * 16;
+          ps.r[q] = sub_slice(clamp_len(ceil_div(pb, (size_t)16), vb, stride_v));
+        }
       }
+      push_peers<T>(ps);
       const size_t sb = a.in_cnt[me];
       copy_user_to_user(reinterpret_cast<const T*>(a.in_piece[me]), reinterpret_cast<T*>(a.out_piece[me]),
                         sb, vb, sub_slice(clamp_len(ceil_div(sb, (size_t)16), vb, stride_v)));
@@ -444,13 +547,21 @@ __global__ void __launch_bounds__(1024) all_to_all_kernel(const __grid_constant_
     ok = sy.wait_all(0, rd);
     if (!ok) break;
     if (do_work) {
-      for (int q = 1; q < W; ++q) {
-        const int p = (me + q) % W;
-        const size_t pb = a.out_cnt[p];
-        const size_t len = clamp_len(ceil_div(pb, (size_t)16), vb, stride_v);
-        copy_stage_to_user(sy.half(me, rd) + (size_t)p * stride_v * 16,
-                           reinterpret_cast<T*>(a.out_piece[p]), pb, vb, sub_slice(len));
+      PeerSet<T> ps;
+      ps.np = W - 1;
+#pragma unroll
+      for (int q = 0; q < kNP; ++q) {
+        if (q < W - 1) {
+          const int p = (me + q + 1) % W;
+          const size_t pb = a.out_cnt[p];
+          ps.user_dst[q] = reinterpret_cast<T*>(a.out_piece[p]);
+          ps.count[q] = pb;
+          ps.vbase[q] = vb;
+          ps.stage[q] = sy.half(me, rd) + (size_t)p * stride_v * 16;
+          ps.r[q] = sub_slice(clamp_len(ceil_div(pb, (size_t)16), vb, stride_v));
+        }
       }
+      pull_peers<T>(ps);
     }
   }
   sy.finish(first + rounds);

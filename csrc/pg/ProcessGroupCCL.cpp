@@ -593,6 +593,30 @@ c10::intrusive_ptr<Work> ProcessGroupCCL::_allgather_base(at::Tensor& outputBuff
   TORCH_CHECK(inputBuffer.numel() * size_ == outputBuffer.numel(), "output tensor size must be equal to world_size times input tensor size");
   RECORD_FUNCTION("oneccl_bindings_for_pytorch::_allgather_base", std::vector<c10::IValue>({inputBuffer}));
   CCL_OP_PROLOGUE("_allgather_base", inputBuffer, "", tensors_str(inputBuffer), (uint64_t)outputBuffer.numel() * outputBuffer.element_size())
+  if (on_cuda) {
+    // flat buffers: piece p of the output is at p * bytes, no per-piece tensors are needed
+    at::Tensor in = inputBuffer, ob = outputBuffer;
+    auto w = cudaImpl(in.device()).run(OpType::_ALLGATHER_BASE, "oneccl_bindings_for_pytorch::cuda::_allgather_base", in.device(),
+        [in, ob](ccl::CudaComm& c, cudaStream_t s) {
+          const size_t bytes = (size_t)in.numel() * in.element_size();
+          if (bytes == 0) return std::string("noop");
+          char* o = static_cast<char*>(ob.data_ptr());
+          if (c.world() == 1) {
+            if (o != in.data_ptr()) C10_CUDA_CHECK(cudaMemcpyAsync(o, in.data_ptr(), bytes, cudaMemcpyDeviceToDevice, s));
+            return std::string("copy");
+          }
+          ccl::CollArgs a;
+          a.in = in.data_ptr();
+          for (int p = 0; p < c.world(); ++p) {
+            a.out_piece[p] = o + (size_t)p * bytes;
+            a.out_cnt[p] = bytes;
+          }
+          C10_CUDA_CHECK(c.all_gather({a}, s));
+          return std::string("all_gather");
+        }, {in, ob}, {ob}, {}, false, bytes__);
+    CCL_TRACK_COALESCED(w);
+    return w;
+  }
   std::vector<at::Tensor> ins{inputBuffer};
   std::vector<std::vector<at::Tensor>> outs{split_flat(outputBuffer, size_)};
   at::Tensor ob = outputBuffer;
@@ -810,6 +834,36 @@ c10::intrusive_ptr<Work> ProcessGroupCCL::_reduce_scatter_base(at::Tensor& outpu
   TORCH_CHECK(outputBuffer.numel() * size_ == inputBuffer.numel(), "input tensor size must be equal to world_size times output tensor size");
   RECORD_FUNCTION("oneccl_bindings_for_pytorch::_reduce_scatter_base", std::vector<c10::IValue>({inputBuffer}));
   CCL_OP_PROLOGUE("_reduce_scatter_base", inputBuffer, "", tensors_str(inputBuffer), (uint64_t)inputBuffer.numel() * inputBuffer.element_size())
+  if (on_cuda) {
+    at::Tensor in = inputBuffer, ob = outputBuffer;
+    const ccl::ReduceSpec spec = ccl::make_reduce_spec(opts.reduceOp, ob.scalar_type(), size_);
+    auto w = cudaImpl(in.device()).run(OpType::_REDUCE_SCATTER_BASE, "oneccl_bindings_for_pytorch::cuda::_reduce_scatter_base", in.device(),
+        [in, ob, spec](ccl::CudaComm& c, cudaStream_t s) {
+          const size_t n = ob.numel();
+          if (n == 0) return std::string("noop");
+          if (c.world() == 1) {
+            if (ob.data_ptr() != in.data_ptr()) C10_CUDA_CHECK(cudaMemcpyAsync(ob.data_ptr(), in.data_ptr(), n * ob.element_size(), cudaMemcpyDeviceToDevice, s));
+            if (spec.has_scale && !spec.is_avg) {
+              c10::cuda::CUDAStreamGuard g(c10::cuda::getStreamFromExternal(s, ob.device().index()));
+              const_cast<at::Tensor&>(ob).mul_(spec.scale);
+            }
+            return std::string("copy");
+          }
+          ccl::CollArgs a;
+          const char* i = static_cast<const char*>(in.data_ptr());
+          for (int p = 0; p < c.world(); ++p) {
+            a.in_piece[p] = i + (size_t)p * n * in.element_size();
+            a.in_cnt[p] = n;
+          }
+          a.out = ob.data_ptr();
+          fill_reduce(a, spec, ob.scalar_type());
+          const int dt = ccl_py::to_ccl_dtype(ob.scalar_type());
+          C10_CUDA_CHECK(c.reduce_scatter(dt, dt, {a}, s));
+          return std::string("reduce_scatter");
+        }, {in, ob}, {ob}, {}, false, bytes__);
+    CCL_TRACK_COALESCED(w);
+    return w;
+  }
   std::vector<std::vector<at::Tensor>> ins{split_flat(inputBuffer, size_)};
   std::vector<at::Tensor> outs{outputBuffer};
   auto w = reduce_scatter_pieces(*this, OpType::_REDUCE_SCATTER_BASE, "oneccl_bindings_for_pytorch::cuda::_reduce_scatter_base", ins, outs, opts.reduceOp,
@@ -914,6 +968,28 @@ c10::intrusive_ptr<Work> ProcessGroupCCL::alltoall_base(at::Tensor& outputTensor
   ccl::check_split_sizes(outputSplitSizes, outputTensor, size_);
   RECORD_FUNCTION("oneccl_bindings_for_pytorch::alltoall_base", std::vector<c10::IValue>({inputTensor}));
   CCL_OP_PROLOGUE("alltoall_base", inputTensor, "", tensors_str(inputTensor), (uint64_t)inputTensor.numel() * inputTensor.element_size())
+  if (on_cuda && !uneven) {
+    at::Tensor in = inputTensor, ot2 = outputTensor;
+    return cudaImpl(in.device()).run(OpType::ALLTOALL_BASE, "oneccl_bindings_for_pytorch::cuda::alltoall_base", in.device(),
+        [in, ot2](ccl::CudaComm& c, cudaStream_t s) {
+          const size_t total = (size_t)in.numel() * in.element_size();
+          if (total == 0) return std::string("noop");
+          if (c.world() == 1) {
+            if (ot2.data_ptr() != in.data_ptr()) C10_CUDA_CHECK(cudaMemcpyAsync(ot2.data_ptr(), in.data_ptr(), total, cudaMemcpyDeviceToDevice, s));
+            return std::string("copy");
+          }
+          const size_t piece = total / c.world();
+          ccl::CollArgs a;
+          for (int p = 0; p < c.world(); ++p) {
+            a.in_piece[p] = static_cast<const char*>(in.data_ptr()) + (size_t)p * piece;
+            a.out_piece[p] = static_cast<char*>(ot2.data_ptr()) + (size_t)p * piece;
+            a.in_cnt[p] = piece;
+            a.out_cnt[p] = piece;
+          }
+          C10_CUDA_CHECK(c.all_to_all({a}, false, s));
+          return std::string("all_to_all");
+        }, {in, ot2}, {ot2}, {}, false, bytes__);
+  }
   auto ins = split_rows(inputTensor, inputSplitSizes, size_);
   auto outs = split_rows(outputTensor, outputSplitSizes, size_);
   at::Tensor ot = outputTensor;

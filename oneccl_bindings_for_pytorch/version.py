@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "1f528759742ec017cddbbc7db7215629c9ee94ad"
+git_version = "9b0505d6a1cf95f2b3b1509da22ba8404fdffc16"
