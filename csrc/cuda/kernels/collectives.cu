@@ -159,6 +159,29 @@ __device__ __forceinline__ void pull_peers(const PeerSet<T>& ps) {
   }
 }
 
+// Latency-bound shares (a few vectors per thread) go peer-parallel; long shares stream one peer
+// after the other with four loads in flight per thread, which needs fewer registers.
+template <typename T>
+__device__ __forceinline__ void push_auto(const PeerSet<T>& ps) {
+  size_t span = 0;
+  for (int q = 0; q < ps.np; ++q) span = max(span, ps.r[q].j1 - ps.r[q].j0);
+  if (span <= 2 * (size_t)blockDim.x) {
+    push_peers<T>(ps);
+  } else {
+    for (int q = 0; q < ps.np; ++q) copy_user_to_stage(ps.user_src[q], ps.count[q], ps.vbase[q], ps.stage[q], ps.r[q]);
+  }
+}
+template <typename T>
+__device__ __forceinline__ void pull_auto(const PeerSet<T>& ps) {
+  size_t span = 0;
+  for (int q = 0; q < ps.np; ++q) span = max(span, ps.r[q].j1 - ps.r[q].j0);
+  if (span <= 2 * (size_t)blockDim.x) {
+    pull_peers<T>(ps);
+  } else {
+    for (int q = 0; q < ps.np; ++q) copy_stage_to_user(ps.stage[q], ps.user_dst[q], ps.count[q], ps.vbase[q], ps.r[q]);
+  }
+}
+
 template <typename T>
 __device__ __forceinline__ Vec<T> finish_vec(const typename Acc<T>::type (&acc)[Vec<T>::kN],
                                              const CollArgs& a) {
@@ -297,7 +320,7 @@ __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const __grid_co
           ps.r[q] = sub_slice(clamp_len(n, (size_t)p * spr, spr));
         }
       }
-      push_peers<T>(ps);
+      push_auto<T>(ps);
     }
     sy.signal_all(0, rd);
     ok = sy.wait_all(0, rd);
@@ -341,7 +364,7 @@ __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const __grid_co
             ps.r[q] = sub_slice(clamp_len(n, (size_t)p * spr, spr));
           }
         }
-        pull_peers<T>(ps);
+        pull_auto<T>(ps);
       }
     }
   }
@@ -385,7 +408,7 @@ __global__ void __launch_bounds__(1024) reduce_scatter_kernel(const __grid_const
           ps.r[q] = sub_slice(clamp_len(nv, vb, stride_v));
         }
       }
-      push_peers<TIn>(ps);
+      push_auto<TIn>(ps);
     }
     sy.signal_all(0, rd);
     ok = sy.wait_all(0, rd);
@@ -477,7 +500,7 @@ __global__ void __launch_bounds__(1024) all_gather_kernel(const __grid_constant_
           ps.r[q] = sub_slice(clamp_len(ceil_div(pb, (size_t)16), vb, stride_v));
         }
       }
-      pull_peers<T>(ps);
+      pull_auto<T>(ps);
     }
   }
   sy.finish(rounds);
@@ -493,7 +516,7 @@ __global__ void __launch_bounds__(1024) all_to_all_kernel(const __grid_constant_
   CCL_GET_CTX
   using T = uint8_t;
   const int W = ctx.world, me = ctx.rank;
-  const size_t stride_v = a.chunk_vecs;
+  size_t stride_v = a.chunk_vecs;
   int rounds = a.rounds;
   int first = 0;
   bool ok = true;
@@ -517,6 +540,10 @@ __global__ void __launch_bounds__(1024) all_to_all_kernel(const __grid_constant_
       const size_t v = ptx::ld_relaxed_sys(ctx.state + 16 + par * kMaxRanks + p);
       gmx = v > gmx ? v : gmx;
     }
+    // every rank now knows the largest piece of the whole group: pack the slots accordingly
+    // (slots tens of MB apart cost more in address translation than the transfer itself)
+    const size_t want = round_up(gmx > 8 ? gmx : 8, 8);
+    if (want < stride_v) stride_v = want;
     rounds = (int)ceil_div(gmx, stride_v);
     first = 1;
   }
@@ -538,7 +565,7 @@ __global__ void __launch_bounds__(1024) all_to_all_kernel(const __grid_constant_
           ps.r[q] = sub_slice(clamp_len(ceil_div(pb, (size_t)16), vb, stride_v));
         }
       }
-      push_peers<T>(ps);
+      push_auto<T>(ps);
       const size_t sb = a.in_cnt[me];
       copy_user_to_user(reinterpret_cast<const T*>(a.in_piece[me]), reinterpret_cast<T*>(a.out_piece[me]),
                         sb, vb, sub_slice(clamp_len(ceil_div(sb, (size_t)16), vb, stride_v)));
@@ -561,7 +588,7 @@ __global__ void __launch_bounds__(1024) all_to_all_kernel(const __grid_constant_
           ps.r[q] = sub_slice(clamp_len(ceil_div(pb, (size_t)16), vb, stride_v));
         }
       }
-      pull_peers<T>(ps);
+      pull_auto<T>(ps);
     }
   }
   sy.finish(first + rounds);

@@ -180,7 +180,8 @@ __device__ __forceinline__ Vec<T> load_vec(const T* base, size_t i, size_t count
   if (aligned && (i + 1) * N <= count) {
     *reinterpret_cast<uint4*>(&r) = *reinterpret_cast<const uint4*>(base + i * N);
   } else {
-#pragma unroll
+    // unaligned base or ragged tail: rare, kept as a rolled loop to stay small
+#pragma unroll 1
     for (int j = 0; j < N; ++j) r.v[j] = (i * N + j < count) ? base[i * N + j] : zero_of<T>();
   }
   return r;
@@ -191,7 +192,7 @@ __device__ __forceinline__ void store_vec(T* base, size_t i, size_t count, bool 
   if (aligned && (i + 1) * N <= count) {
     *reinterpret_cast<uint4*>(base + i * N) = *reinterpret_cast<const uint4*>(&r);
   } else {
-#pragma unroll
+#pragma unroll 1
     for (int j = 0; j < N; ++j)
       if (i * N + j < count) base[i * N + j] = r.v[j];
   }

@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "9b0505d6a1cf95f2b3b1509da22ba8404fdffc16"
+git_version = "8dbd6f50d42db14a614b645275c693d25a32b8aa"
