@@ -306,7 +306,7 @@ CudaComm& CudaBackendImpl::comm(const at::Device& device) {
                                                   : (uint64_t)std::max<int64_t>(1000, std::min<int64_t>(pg_ms, 30000));
     if (env.oneshot_max_bytes >= 0) cfg.oneshot_max_bytes = (size_t)env.oneshot_max_bytes;
     cfg.max_blocks = env.max_blocks;
-    cfg.threads = std::max(32, std::min(1024, env.threads / 32 * 32));
+    cfg.threads = std::max(32, std::min(512, env.threads / 32 * 32));
     if (env.algo == "oneshot") cfg.algo = Algo::kOneShot;
     else if (env.algo == "twoshot") cfg.algo = Algo::kTwoShot;
     if (env.work_only) cfg.ablate = kAblateWorkOnly;

@@ -37,8 +37,8 @@ struct CommConfig {
   uint64_t spin_timeout_ms = 30000;   // device-side wait budget
   size_t oneshot_max_bytes = 0;        // 0: pick from the world size (see default_oneshot_max)
   size_t ag_push_max_bytes = 256 << 10;  // per-piece size below which all_gather pushes
-  int max_blocks = 128;               // CTAs for bandwidth-bound collectives
-  int threads = 1024;
+  int max_blocks = 256;               // CTAs for bandwidth-bound collectives
+  int threads = 512;
   Algo algo = Algo::kAuto;
   int ablate = kAblateNone;
 };

@@ -98,87 +98,90 @@ __device__ __forceinline__ void copy_user_to_user(const T* src, T* dst, size_t c
 
 // Peer-parallel copies: the transfers to / from all peers advance together, so a thread has one
 // independent load per peer in flight instead of walking the peers one after the other (the
-// per-peer latency, not the bandwidth, dominates mid-sized messages). Each peer keeps its own
-// CTA partition (sub_slice of ITS length): the flag of CTA b covers exactly what CTA b of the
-// other side reads or wrote.
+// per-peer latency, not the bandwidth, dominates mid-sized messages). Used when every peer's
+// share has the same length (the equal-split case); `F(q)` describes peer number q = 0..np-1 and
+// is evaluated inside fully unrolled loops, so nothing is indexed dynamically and everything
+// stays in registers. Long or uneven shares stream one peer after the other instead.
 constexpr int kNP = kMaxRanks - 1;
 template <typename T>
-struct PeerSet {
-  const T* user_src[kNP];  // push: source in user memory
-  T* user_dst[kNP];        // pull: destination in user memory
-  size_t count[kNP];       // elements of that user array
-  size_t vbase[kNP];       // vector offset in the user array
-  char* stage[kNP];        // staging address of vector 0 of the transfer
-  Range r[kNP];            // this CTA's share, in vectors
-  int np;
+struct PeerDesc {
+  T* user;        // user-memory array (source of a push, destination of a pull)
+  size_t count;   // its element count
+  size_t vbase;   // vector offset of the transfer in it
+  char* stage;    // staging address of vector 0 of the transfer
 };
 
-template <typename T>
-__device__ __forceinline__ void push_peers(const PeerSet<T>& ps) {
-  size_t span = 0;
-  bool al[kNP];
-#pragma unroll
-  for (int q = 0; q < kNP; ++q) {
-    if (q < ps.np) {
-      const size_t n = ps.r[q].j1 - ps.r[q].j0;
-      span = n > span ? n : span;
-      al[q] = is_aligned16(ps.user_src[q]);
-    }
-  }
-  for (size_t k = threadIdx.x; k < span; k += blockDim.x) {
+template <typename T, typename F>
+__device__ __forceinline__ void push_uniform(int np, Range r, F desc) {
+  for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
     Vec<T> v[kNP];
 #pragma unroll
-    for (int q = 0; q < kNP; ++q)
-      if (q < ps.np && ps.r[q].j0 + k < ps.r[q].j1) v[q] = load_vec(ps.user_src[q], ps.vbase[q] + ps.r[q].j0 + k, ps.count[q], al[q]);
+    for (int q = 0; q < kNP; ++q) {
+      if (q < np) {
+        const PeerDesc<T> d = desc(q);
+        v[q] = load_vec(d.user, d.vbase + j, d.count, is_aligned16(d.user));
+      }
+    }
 #pragma unroll
-    for (int q = 0; q < kNP; ++q)
-      if (q < ps.np && ps.r[q].j0 + k < ps.r[q].j1) store_stage(ps.stage[q] + (ps.r[q].j0 + k) * 16, v[q]);
+    for (int q = 0; q < kNP; ++q) {
+      if (q < np) {
+        const PeerDesc<T> d = desc(q);
+        store_stage(d.stage + j * 16, v[q]);
+      }
+    }
   }
 }
 
-template <typename T>
-__device__ __forceinline__ void pull_peers(const PeerSet<T>& ps) {
-  size_t span = 0;
-  bool al[kNP];
-#pragma unroll
-  for (int q = 0; q < kNP; ++q) {
-    if (q < ps.np) {
-      const size_t n = ps.r[q].j1 - ps.r[q].j0;
-      span = n > span ? n : span;
-      al[q] = is_aligned16(ps.user_dst[q]);
-    }
-  }
-  for (size_t k = threadIdx.x; k < span; k += blockDim.x) {
+template <typename T, typename F>
+__device__ __forceinline__ void pull_uniform(int np, Range r, F desc) {
+  for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
     Vec<T> v[kNP];
 #pragma unroll
-    for (int q = 0; q < kNP; ++q)
-      if (q < ps.np && ps.r[q].j0 + k < ps.r[q].j1) v[q] = load_stage<T>(ps.stage[q] + (ps.r[q].j0 + k) * 16);
+    for (int q = 0; q < kNP; ++q) {
+      if (q < np) {
+        const PeerDesc<T> d = desc(q);
+        v[q] = load_stage<T>(d.stage + j * 16);
+      }
+    }
 #pragma unroll
-    for (int q = 0; q < kNP; ++q)
-      if (q < ps.np && ps.r[q].j0 + k < ps.r[q].j1) store_vec(ps.user_dst[q], ps.vbase[q] + ps.r[q].j0 + k, ps.count[q], al[q], v[q]);
+    for (int q = 0; q < kNP; ++q) {
+      if (q < np) {
+        const PeerDesc<T> d = desc(q);
+        store_vec(d.user, d.vbase + j, d.count, is_aligned16(d.user), v[q]);
+      }
+    }
   }
 }
 
-// Latency-bound shares (a few vectors per thread) go peer-parallel; long shares stream one peer
-// after the other with four loads in flight per thread, which needs fewer registers.
-template <typename T>
-__device__ __forceinline__ void push_auto(const PeerSet<T>& ps) {
-  size_t span = 0;
-  for (int q = 0; q < ps.np; ++q) span = max(span, ps.r[q].j1 - ps.r[q].j0);
-  if (span <= 2 * (size_t)blockDim.x) {
-    push_peers<T>(ps);
+// `len(q)` is the share length of peer q in vectors. Short equal shares go peer-parallel.
+template <typename T, typename F, typename L>
+__device__ __forceinline__ void push_auto(int np, F desc, L len) {
+  const size_t l0 = len(0);
+  bool uniform = true;
+  for (int q = 1; q < np; ++q) uniform &= (len(q) == l0);
+  const Range r0 = sub_slice(l0);
+  if (uniform && (r0.j1 - r0.j0) <= 2 * (size_t)blockDim.x) {
+    push_uniform<T>(np, r0, desc);
   } else {
-    for (int q = 0; q < ps.np; ++q) copy_user_to_stage(ps.user_src[q], ps.count[q], ps.vbase[q], ps.stage[q], ps.r[q]);
+    for (int q = 0; q < np; ++q) {
+      const PeerDesc<T> d = desc(q);
+      copy_user_to_stage(const_cast<const T*>(d.user), d.count, d.vbase, d.stage, sub_slice(len(q)));
+    }
   }
 }
-template <typename T>
-__device__ __forceinline__ void pull_auto(const PeerSet<T>& ps) {
-  size_t span = 0;
-  for (int q = 0; q < ps.np; ++q) span = max(span, ps.r[q].j1 - ps.r[q].j0);
-  if (span <= 2 * (size_t)blockDim.x) {
-    pull_peers<T>(ps);
+template <typename T, typename F, typename L>
+__device__ __forceinline__ void pull_auto(int np, F desc, L len) {
+  const size_t l0 = len(0);
+  bool uniform = true;
+  for (int q = 1; q < np; ++q) uniform &= (len(q) == l0);
+  const Range r0 = sub_slice(l0);
+  if (uniform && (r0.j1 - r0.j0) <= 2 * (size_t)blockDim.x) {
+    pull_uniform<T>(np, r0, desc);
   } else {
-    for (int q = 0; q < ps.np; ++q) copy_stage_to_user(ps.stage[q], ps.user_dst[q], ps.count[q], ps.vbase[q], ps.r[q]);
+    for (int q = 0; q < np; ++q) {
+      const PeerDesc<T> d = desc(q);
+      copy_stage_to_user(d.stage, d.user, d.count, d.vbase, sub_slice(len(q)));
+    }
   }
 }
 
@@ -238,7 +241,7 @@ __device__ __forceinline__ void reduce_ranks(const Vec<T> (&v)[kMaxRanks], int W
 // Latency-optimal: one NVLink traversal plus one flag.
 // ---------------------------------------------------------------------------------------------
 template <typename T, bool EMU>
-__global__ void __launch_bounds__(1024) allreduce_oneshot_kernel(const __grid_constant__ Launch<EMU> L) {
+__global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_constant__ Launch<EMU> L) {
   CCL_GET_CTX
   using A = typename Acc<T>::type;
   constexpr int N = Vec<T>::kN;
@@ -285,7 +288,7 @@ __global__ void __launch_bounds__(1024) allreduce_oneshot_kernel(const __grid_co
 // Large messages run as several rounds through the double-buffered arena inside ONE launch.
 // ---------------------------------------------------------------------------------------------
 template <typename T, bool EMU>
-__global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const __grid_constant__ Launch<EMU> L) {
+__global__ void __launch_bounds__(512) allreduce_twoshot_kernel(const __grid_constant__ Launch<EMU> L) {
   CCL_GET_CTX
   using A = typename Acc<T>::type;
   constexpr int N = Vec<T>::kN;
@@ -307,20 +310,13 @@ __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const __grid_co
     const size_t spr = ceil_div(n, (size_t)W);
     // phase 0: scatter my contribution to each shard's owner
     if (do_work) {
-      PeerSet<T> ps;
-      ps.np = W - 1;
-#pragma unroll
-      for (int q = 0; q < kNP; ++q) {
-        if (q < W - 1) {
-          const int p = (me + q + 1) % W;
-          ps.user_src[q] = in;
-          ps.count[q] = count;
-          ps.vbase[q] = base + (size_t)p * spr;
-          ps.stage[q] = sy.half(p, rd) + (size_t)me * stride_v * 16;
-          ps.r[q] = sub_slice(clamp_len(n, (size_t)p * spr, spr));
-        }
-      }
-      push_auto<T>(ps);
+      auto peer = [&](int q) { const int p = me + q + 1; return p >= W ? p - W : p; };
+      push_auto<T>(W - 1,
+          [&](int q) {
+            const int p = peer(q);
+            return PeerDesc<T>{const_cast<T*>(in), count, base + (size_t)p * spr, sy.half(p, rd) + (size_t)me * stride_v * 16};
+          },
+          [&](int q) { return clamp_len(n, (size_t)peer(q) * spr, spr); });
     }
     sy.signal_all(0, rd);
     ok = sy.wait_all(0, rd);
@@ -351,20 +347,13 @@ __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const __grid_co
       ok = sy.wait_all(1, rd);
       if (!ok) break;
       if (do_work) {
-        PeerSet<T> ps;
-        ps.np = W - 1;
-#pragma unroll
-        for (int q = 0; q < kNP; ++q) {
-          if (q < W - 1) {
-            const int p = (me + q + 1) % W;
-            ps.user_dst[q] = out;
-            ps.count[q] = count;
-            ps.vbase[q] = base + (size_t)p * spr;
-            ps.stage[q] = sy.half(p, rd) + (size_t)W * stride_v * 16;
-            ps.r[q] = sub_slice(clamp_len(n, (size_t)p * spr, spr));
-          }
-        }
-        pull_auto<T>(ps);
+        auto peer = [&](int q) { const int p = me + q + 1; return p >= W ? p - W : p; };
+        pull_auto<T>(W - 1,
+            [&](int q) {
+              const int p = peer(q);
+              return PeerDesc<T>{out, count, base + (size_t)p * spr, sy.half(p, rd) + (size_t)W * stride_v * 16};
+            },
+            [&](int q) { return clamp_len(n, (size_t)peer(q) * spr, spr); });
       }
     }
   }
@@ -377,7 +366,7 @@ __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const __grid_co
 // (gradient average) is applied in the same pass.
 // ---------------------------------------------------------------------------------------------
 template <typename TIn, typename TOut, bool EMU>
-__global__ void __launch_bounds__(1024) reduce_scatter_kernel(const __grid_constant__ Launch<EMU> L) {
+__global__ void __launch_bounds__(512) reduce_scatter_kernel(const __grid_constant__ Launch<EMU> L) {
   CCL_GET_CTX
   using A = typename Acc<TIn>::type;
   constexpr int N = Vec<TIn>::kN;
@@ -394,21 +383,14 @@ __global__ void __launch_bounds__(1024) reduce_scatter_kernel(const __grid_const
   for (int rd = 0; rd < rounds && ok; ++rd) {
     const size_t vb = (size_t)rd * stride_v;
     if (do_work) {
-      PeerSet<TIn> ps;
-      ps.np = W - 1;
-#pragma unroll
-      for (int q = 0; q < kNP; ++q) {
-        if (q < W - 1) {
-          const int p = (me + q + 1) % W;
-          const size_t nv = ceil_div((size_t)a.in_cnt[p], (size_t)N);
-          ps.user_src[q] = reinterpret_cast<const TIn*>(a.in_piece[p]);
-          ps.count[q] = (size_t)a.in_cnt[p];
-          ps.vbase[q] = vb;
-          ps.stage[q] = sy.half(p, rd) + (size_t)me * stride_v * 16;
-          ps.r[q] = sub_slice(clamp_len(nv, vb, stride_v));
-        }
-      }
-      push_auto<TIn>(ps);
+      auto peer = [&](int q) { const int p = me + q + 1; return p >= W ? p - W : p; };
+      push_auto<TIn>(W - 1,
+          [&](int q) {
+            const int p = peer(q);
+            return PeerDesc<TIn>{const_cast<TIn*>(reinterpret_cast<const TIn*>(a.in_piece[p])), (size_t)a.in_cnt[p], vb,
+                                 sy.half(p, rd) + (size_t)me * stride_v * 16};
+          },
+          [&](int q) { return clamp_len(ceil_div((size_t)a.in_cnt[peer(q)], (size_t)N), vb, stride_v); });
     }
     sy.signal_all(0, rd);
     ok = sy.wait_all(0, rd);
@@ -458,7 +440,7 @@ __global__ void __launch_bounds__(1024) reduce_scatter_kernel(const __grid_const
 // rank then copies locally (lower latency for small pieces). Pieces may differ in size.
 // ---------------------------------------------------------------------------------------------
 template <bool EMU>
-__global__ void __launch_bounds__(1024) all_gather_kernel(const __grid_constant__ Launch<EMU> L) {
+__global__ void __launch_bounds__(512) all_gather_kernel(const __grid_constant__ Launch<EMU> L) {
   CCL_GET_CTX
   using T = uint8_t;
   const int W = ctx.world, me = ctx.rank;
@@ -486,21 +468,14 @@ __global__ void __launch_bounds__(1024) all_gather_kernel(const __grid_constant_
     ok = sy.wait_all(0, rd);
     if (!ok) break;
     if (do_work) {
-      PeerSet<T> ps;
-      ps.np = W - 1;
-#pragma unroll
-      for (int q = 0; q < kNP; ++q) {
-        if (q < W - 1) {
-          const int p = (me + q + 1) % W;
-          const size_t pb = a.out_cnt[p];
-          ps.user_dst[q] = reinterpret_cast<T*>(a.out_piece[p]);
-          ps.count[q] = pb;
-          ps.vbase[q] = vb;
-          ps.stage[q] = (a.mode == 0) ? sy.half(p, rd) : sy.half(me, rd) + (size_t)p * stride_v * 16;
-          ps.r[q] = sub_slice(clamp_len(ceil_div(pb, (size_t)16), vb, stride_v));
-        }
-      }
-      pull_auto<T>(ps);
+      auto peer = [&](int q) { const int p = me + q + 1; return p >= W ? p - W : p; };
+      pull_auto<T>(W - 1,
+          [&](int q) {
+            const int p = peer(q);
+            return PeerDesc<T>{reinterpret_cast<T*>(a.out_piece[p]), (size_t)a.out_cnt[p], vb,
+                               (a.mode == 0) ? sy.half(p, rd) : sy.half(me, rd) + (size_t)p * stride_v * 16};
+          },
+          [&](int q) { return clamp_len(ceil_div((size_t)a.out_cnt[peer(q)], (size_t)16), vb, stride_v); });
     }
   }
   sy.finish(rounds);
@@ -512,7 +487,7 @@ __global__ void __launch_bounds__(1024) all_gather_kernel(const __grid_constant_
 // peers' state words and every CTA derives the same number of data rounds from the maximum.
 // ---------------------------------------------------------------------------------------------
 template <bool EMU>
-__global__ void __launch_bounds__(1024) all_to_all_kernel(const __grid_constant__ Launch<EMU> L) {
+__global__ void __launch_bounds__(512) all_to_all_kernel(const __grid_constant__ Launch<EMU> L) {
   CCL_GET_CTX
   using T = uint8_t;
   const int W = ctx.world, me = ctx.rank;
@@ -551,21 +526,14 @@ __global__ void __launch_bounds__(1024) all_to_all_kernel(const __grid_constant_
     const int rd = first + i;
     const size_t vb = (size_t)i * stride_v;
     if (do_work) {
-      PeerSet<T> ps;
-      ps.np = W - 1;
-#pragma unroll
-      for (int q = 0; q < kNP; ++q) {
-        if (q < W - 1) {
-          const int p = (me + q + 1) % W;
-          const size_t pb = a.in_cnt[p];
-          ps.user_src[q] = reinterpret_cast<const T*>(a.in_piece[p]);
-          ps.count[q] = pb;
-          ps.vbase[q] = vb;
-          ps.stage[q] = sy.half(p, rd) + (size_t)me * stride_v * 16;
-          ps.r[q] = sub_slice(clamp_len(ceil_div(pb, (size_t)16), vb, stride_v));
-        }
-      }
-      push_auto<T>(ps);
+      auto peer = [&](int q) { const int p = me + q + 1; return p >= W ? p - W : p; };
+      push_auto<T>(W - 1,
+          [&](int q) {
+            const int p = peer(q);
+            return PeerDesc<T>{const_cast<T*>(reinterpret_cast<const T*>(a.in_piece[p])), (size_t)a.in_cnt[p], vb,
+                               sy.half(p, rd) + (size_t)me * stride_v * 16};
+          },
+          [&](int q) { return clamp_len(ceil_div((size_t)a.in_cnt[peer(q)], (size_t)16), vb, stride_v); });
       const size_t sb = a.in_cnt[me];
       copy_user_to_user(reinterpret_cast<const T*>(a.in_piece[me]), reinterpret_cast<T*>(a.out_piece[me]),
                         sb, vb, sub_slice(clamp_len(ceil_div(sb, (size_t)16), vb, stride_v)));
@@ -574,21 +542,14 @@ __global__ void __launch_bounds__(1024) all_to_all_kernel(const __grid_constant_
     ok = sy.wait_all(0, rd);
     if (!ok) break;
     if (do_work) {
-      PeerSet<T> ps;
-      ps.np = W - 1;
-#pragma unroll
-      for (int q = 0; q < kNP; ++q) {
-        if (q < W - 1) {
-          const int p = (me + q + 1) % W;
-          const size_t pb = a.out_cnt[p];
-          ps.user_dst[q] = reinterpret_cast<T*>(a.out_piece[p]);
-          ps.count[q] = pb;
-          ps.vbase[q] = vb;
-          ps.stage[q] = sy.half(me, rd) + (size_t)p * stride_v * 16;
-          ps.r[q] = sub_slice(clamp_len(ceil_div(pb, (size_t)16), vb, stride_v));
-        }
-      }
-      pull_auto<T>(ps);
+      auto peer = [&](int q) { const int p = me + q + 1; return p >= W ? p - W : p; };
+      pull_auto<T>(W - 1,
+          [&](int q) {
+            const int p = peer(q);
+            return PeerDesc<T>{reinterpret_cast<T*>(a.out_piece[p]), (size_t)a.out_cnt[p], vb,
+                               sy.half(me, rd) + (size_t)p * stride_v * 16};
+          },
+          [&](int q) { return clamp_len(ceil_div((size_t)a.out_cnt[peer(q)], (size_t)16), vb, stride_v); });
     }
   }
   sy.finish(first + rounds);
@@ -599,7 +560,7 @@ __global__ void __launch_bounds__(1024) all_to_all_kernel(const __grid_constant_
 // round so that nobody can run more than one round ahead of a rank that still reads staging.
 // ---------------------------------------------------------------------------------------------
 template <bool EMU>
-__global__ void __launch_bounds__(1024) rooted_kernel(const __grid_constant__ Launch<EMU> L) {
+__global__ void __launch_bounds__(512) rooted_kernel(const __grid_constant__ Launch<EMU> L) {
   CCL_GET_CTX
   using T = uint8_t;
   const int W = ctx.world, me = ctx.rank, root = a.root;

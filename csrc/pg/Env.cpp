@@ -56,8 +56,8 @@ Env parse() {
   e.log_level = (int)parse_env_int("CCL_LOG_LEVEL", 0);
   e.arena_mb = parse_env_int("CCL_ARENA_MB", 256);
   e.shm_slot_mb = parse_env_int("CCL_SHM_SLOT_MB", 4);
-  e.max_blocks = (int)parse_env_int("CCL_MAX_BLOCKS", 128);
-  e.threads = (int)parse_env_int("CCL_THREADS", 1024);
+  e.max_blocks = (int)parse_env_int("CCL_MAX_BLOCKS", 256);
+  e.threads = (int)parse_env_int("CCL_THREADS", 512);
   // launcher detection (reference: ProcessGroupCCL.cpp:825-830,930-945; dpcpp_ccl.cpp:137-152)
   e.with_mpirun = std::getenv("MPI_LOCALRANKID") || std::getenv("MPI_LOCALNRANKS") ||
                   std::getenv("PMI_RANK") || std::getenv("PMI_SIZE") || std::getenv("PMIX_RANK");

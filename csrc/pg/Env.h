@@ -32,8 +32,8 @@ struct Env {
   int log_level = 0;           // CCL_LOG_LEVEL
   int64_t arena_mb = 256;      // CCL_ARENA_MB: one staging half per rank
   int64_t shm_slot_mb = 4;     // CCL_SHM_SLOT_MB: CPU shared-memory slot per rank
-  int max_blocks = 128;        // CCL_MAX_BLOCKS: CTAs of bandwidth-bound collectives
-  int threads = 1024;          // CCL_THREADS: threads per CTA of the collective kernels
+  int max_blocks = 256;        // CCL_MAX_BLOCKS: CTAs of bandwidth-bound collectives
+  int threads = 512;           // CCL_THREADS: threads per CTA of the collective kernels
   int local_rank = -1;         // LOCAL_RANK / MPI_LOCALRANKID / ...
   int local_world_size = -1;   // LOCAL_WORLD_SIZE / MPI_LOCALNRANKS / PALS_LOCAL_SIZE
   bool with_mpirun = false;
