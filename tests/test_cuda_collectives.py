@@ -226,3 +226,37 @@ def _fused_gemm_ops(rank, world):
 
 def test_cuda_fused_gemm_collectives():
     run_ranks(_fused_gemm_ops, world=_world(), device="cuda", env={"NCCL_NVLS_ENABLE": "0", "CCL_ARENA_MB": "64"}, timeout=300)
+
+
+def _fsdp_engine(rank, world):
+    """The fused full-shard engine must train exactly like the same schedule on plain c10d calls."""
+    import torch.nn as nn
+
+    from torch_ccl_b200.parallel.fsdp import FullyShardedSequential
+
+    def make():
+        torch.manual_seed(0)
+        return [nn.Sequential(nn.Linear(64, 96), nn.GELU()).cuda(), nn.Linear(96, 64).cuda(), nn.Linear(64, 8).cuda()]
+
+    losses = {}
+    for comm in ("ccl", "c10d"):
+        eng = FullyShardedSequential(make(), comm=comm)
+        opt = torch.optim.SGD(eng.master_params(), lr=0.1)
+        out = []
+        for it in range(3):
+            x = _data(rank, 16 * 64, salt=it).view(16, 64).cuda().to(torch.bfloat16)
+            loss = eng(x).float().pow(2).mean()
+            loss.backward()
+            eng.master_params()
+            opt.step()
+            eng.after_step()
+            out.append(float(loss))
+        losses[comm] = out
+    for a, b in zip(losses["ccl"], losses["c10d"]):
+        assert abs(a - b) <= 2e-2 * max(1.0, abs(b)), (losses)
+    assert losses["ccl"][-1] < losses["ccl"][0]
+    dist.barrier()
+
+
+def test_cuda_fsdp_engine_and_moe_ops():
+    run_ranks(_fsdp_engine, world=_world(), device="cuda", env={"NCCL_NVLS_ENABLE": "0", "CCL_ARENA_MB": "64", "CCL_SPIN_TIMEOUT_MS": "3000"}, timeout=120)

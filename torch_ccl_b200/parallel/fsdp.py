@@ -1,0 +1,199 @@
+"""Full-shard data parallelism (ZeRO-3 style) built on the fused collectives of the `ccl` backend.
+
+Every wrapped unit (typically one transformer layer) keeps only its 1/world shard of a flat bf16
+parameter, an fp32 master copy of that shard and an fp32 gradient shard. Around the unit's compute:
+
+  * un-shard: ONE all_gather whose pieces land directly in the unit's full flat parameter buffer
+    (`ops.all_gather_copy_out`; the module's parameters are views of that buffer, so there is no
+    copy-out pass afterwards);
+  * gradients accumulate in views of one flat bf16 gradient buffer; ONE reduce_scatter then sums
+    them over the ranks, averages, and writes fp32 into the gradient shard in the same kernel
+    (`ops.reduce_scatter_cast`: no separate divide and no separate cast).
+
+Activations inside a unit are recomputed in backward (the unit runs under no_grad in forward), so
+only unit boundaries are kept. The all_gather of the next unit (previous unit in backward) is
+prefetched on a side stream while the current unit computes.
+
+`comm="c10d"` runs the same schedule with plain torch.distributed calls (all_gather_into_tensor,
+reduce_scatter_tensor, then divide and cast) on any backend; it is the comparison arm of the
+benchmarks and the oracle of the tests.
+
+The reference enables FSDP only as a workload on top of its collectives (tests/test_fsdp.py:113-180
+of intel/torch-ccl wraps a CNN in torch's FSDP); torch's own FSDP also runs unmodified on this
+backend. This engine exists to exercise the fused reduce_scatter / all_gather kernels.
+"""
+import torch
+import torch.distributed as dist
+
+from .. import ops
+
+
+class ShardedUnit:
+    def __init__(self, module, group=None, comm="ccl", param_dtype=torch.bfloat16):
+        self.module = module
+        self.group = group
+        self.comm = comm
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.params = [p for p in module.parameters()]
+        dev = self.params[0].device
+        self.device = dev
+        self.dtype = param_dtype
+        self.meta = []
+        off = 0
+        for p in self.params:
+            self.meta.append((off, p.numel(), p.shape))
+            off += p.numel()
+        align = self.world * 8  # shards stay 16-byte aligned
+        self.total = off
+        self.padded = (off + align - 1) // align * align
+        self.shard_numel = self.padded // self.world
+        flat = torch.zeros(self.padded, device=dev, dtype=param_dtype)
+        for p, (o, n, _) in zip(self.params, self.meta):
+            flat[o:o + n] = p.data.to(param_dtype).view(-1)
+        lo = self.rank * self.shard_numel
+        self.shard = flat[lo:lo + self.shard_numel].clone()
+        self.master = self.shard.float()               # fp32 master weights of the shard
+        self.grad_shard = torch.zeros_like(self.master)  # fp32 gradient of the shard
+        self._rs_out = torch.empty_like(self.master)
+        del flat
+        for p in self.params:
+            p.data = torch.empty(0, device=dev, dtype=param_dtype)
+        self.full = None
+        self.gfull = None
+        self.ready = None  # event: gathered parameters are complete
+
+    # -- parameters ---------------------------------------------------------------------------
+    def gather(self, stream):
+        """All-gather the flat parameter; parameters become views of the gathered buffer."""
+        if self.full is not None:
+            return
+        cur = torch.cuda.current_stream(self.device)
+        s = stream
+        with torch.cuda.stream(s):
+            full = torch.empty(self.padded, device=self.device, dtype=self.dtype)
+            if self.comm == "ccl":
+                ops.all_gather_copy_out(self.shard, list(full.chunk(self.world)), group=self.group)
+            else:
+                dist.all_gather_into_tensor(full, self.shard, group=self.group)
+            self.ready = torch.cuda.Event()
+            self.ready.record(s)
+        full.record_stream(cur)
+        self.full = full
+        for p, (o, n, shape) in zip(self.params, self.meta):
+            p.data = full[o:o + n].view(shape)
+
+    def wait_ready(self):
+        if self.ready is not None:
+            torch.cuda.current_stream(self.device).wait_event(self.ready)
+
+    def release(self):
+        self.full = None
+        self.ready = None
+        for p in self.params:
+            p.data = torch.empty(0, device=self.device, dtype=self.dtype)
+
+    # -- gradients ----------------------------------------------------------------------------
+    def prepare_grads(self):
+        self.gfull = torch.zeros(self.padded, device=self.device, dtype=self.dtype)
+        for p, (o, n, shape) in zip(self.params, self.meta):
+            p.grad = self.gfull[o:o + n].view(shape)
+
+    def reduce_grads(self, stream):
+        """grad_shard += mean over ranks of this rank's piece of the flat gradient (fp32).
+
+        Runs on `stream` — the same stream as the parameter gathers: the kernels of one
+        communicator must never run concurrently, so all of the engine's collectives share one
+        stream and are ordered against the compute stream with events."""
+        cur = torch.cuda.current_stream(self.device)
+        done = torch.cuda.Event()
+        done.record(cur)
+        gfull = self.gfull
+        with torch.cuda.stream(stream):
+            stream.wait_event(done)
+            if self.comm == "ccl":
+                ops.reduce_scatter_cast(gfull, self._rs_out, scale=1.0 / self.world, group=self.group)
+                self.grad_shard += self._rs_out
+            else:
+                tmp = torch.empty(self.shard_numel, device=self.device, dtype=self.dtype)
+                dist.reduce_scatter_tensor(tmp, gfull, group=self.group)
+                self.grad_shard += tmp.float() / self.world
+        gfull.record_stream(stream)
+        for p in self.params:
+            p.grad = None
+        self.gfull = None
+
+    def optimizer_views(self):
+        """(fp32 master shard with .grad set) for an optimizer; call `sync_shard` after the step."""
+        self.master.grad = self.grad_shard
+        return self.master
+
+    def sync_shard(self):
+        self.shard.copy_(self.master)
+        self.grad_shard.zero_()
+
+
+class _UnitFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, anchor, engine, index):
+        unit = engine.units[index]
+        unit.gather(engine.comm_stream)
+        unit.wait_ready()
+        if index + 1 < len(engine.units):
+            engine.units[index + 1].gather(engine.comm_stream)  # prefetch
+        with torch.no_grad():
+            y = unit.module(x)
+        unit.release()
+        ctx.engine, ctx.index = engine, index
+        ctx.save_for_backward(x)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        engine, index = ctx.engine, ctx.index
+        unit = engine.units[index]
+        (x,) = ctx.saved_tensors
+        unit.gather(engine.comm_stream)
+        unit.wait_ready()
+        if index > 0:
+            engine.units[index - 1].gather(engine.comm_stream)  # prefetch for the previous unit
+        unit.prepare_grads()
+        with torch.enable_grad():
+            xd = x.detach().requires_grad_(x.is_floating_point())
+            y = unit.module(xd)
+        torch.autograd.backward(y, gy)
+        unit.reduce_grads(engine.comm_stream)
+        unit.release()
+        return (xd.grad if xd.requires_grad else None), None, None, None
+
+
+class FullyShardedSequential:
+    """A chain of modules, each sharded as one unit: y = m_n(...m_1(x))."""
+
+    def __init__(self, modules, group=None, comm="ccl", param_dtype=torch.bfloat16):
+        self.units = [ShardedUnit(m, group, comm, param_dtype) for m in modules]
+        self.comm_stream = torch.cuda.Stream()
+        self.anchor = torch.zeros((), device=self.units[0].device, requires_grad=True)
+        self.group = group
+
+    def __call__(self, x):
+        # `anchor` requires grad, so every unit's backward runs even when the chain starts from
+        # token ids (which cannot carry gradients themselves)
+        for i in range(len(self.units)):
+            x = _UnitFn.apply(x, self.anchor, self, i)
+        return x
+
+    def finish_backward(self):
+        """The gradient reduce_scatters run on the communication stream: join it."""
+        torch.cuda.current_stream(self.units[0].device).wait_stream(self.comm_stream)
+
+    def master_params(self):
+        """fp32 master shards with their gradient shards attached (call after backward)."""
+        self.finish_backward()
+        return [u.optimizer_views() for u in self.units]
+
+    def after_step(self):
+        for u in self.units:
+            u.sync_shard()
+        # the next forward's gathers (communication stream) must see the updated shards
+        self.comm_stream.wait_stream(torch.cuda.current_stream(self.units[0].device))
