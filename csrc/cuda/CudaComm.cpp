@@ -37,7 +37,7 @@ size_t default_oneshot_max(int world) {
 
 namespace {
 
-size_t arena_size(size_t half) { return 2 * half + kFlagBytes + kStateBytes; }
+size_t arena_size(size_t half) { return 2 * half + kFlagBytes + kStateBytes + kLLBytes; }
 
 void fill_ctx(RankCtx& c, int rank, int world, const std::vector<void*>& bases, size_t half,
               uint64_t spin_ms, int* status) {
@@ -45,6 +45,7 @@ void fill_ctx(RankCtx& c, int rank, int world, const std::vector<void*>& bases, 
   for (int p = 0; p < world; ++p) {
     c.data[p] = static_cast<char*>(bases[p]);
     c.flags[p] = reinterpret_cast<uint32_t*>(static_cast<char*>(bases[p]) + 2 * half);
+    c.ll[p] = static_cast<char*>(bases[p]) + 2 * half + kFlagBytes + kStateBytes;
   }
   c.state = reinterpret_cast<uint32_t*>(static_cast<char*>(bases[rank]) + 2 * half + kFlagBytes);
   c.status = status;
@@ -486,7 +487,11 @@ cudaError_t CudaComm::allreduce_residual_rmsnorm(int dtype, std::vector<FusedNor
   int threads = std::min(1024, std::max(32, ((a0.hidden / 8 + 31) / 32) * 32));
   if (a0.hidden / 8 > threads * 4) return cudaErrorInvalidValue;
   if ((size_t)a0.rows * a0.hidden * 2 > fused_norm_capacity() && world_ > 1) return cudaErrorInvalidValue;
-  for (auto& a : args) a.ablate = cfg_.ablate;
+  for (auto& a : args) {
+    a.ablate = cfg_.ablate;
+    // small decode-sized inputs take the low-latency protocol (payload and epoch in one store)
+    a.use_ll = (world_ > 1 && cfg_.ablate == kAblateNone && (size_t)a0.rows * a0.hidden * 4 <= kLLSlotBytes) ? 1 : 0;
+  }
   LaunchCfg lc = launch_cfg(std::min(a0.rows, kMaxBlocks), threads, stream);
   cudaError_t e = launch_allreduce_residual_rmsnorm(dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
   if (e == cudaSuccess) ++launches_;

@@ -667,7 +667,27 @@ __global__ void __launch_bounds__(1024) allreduce_residual_rmsnorm_kernel(const 
   T* out = reinterpret_cast<T*>(a.out);
   const size_t slot = round_up((size_t)a.rows * a.hidden * sizeof(T), 128);
 
-  if (W > 1 && a.ablate != kAblateSyncOnly) {
+  const bool ll = a.use_ll != 0 && W > 1;
+  const uint32_t llflag = sy.epoch + 1;
+  if (ll) {
+    // low-latency push: each 16-byte store = {payload, epoch, payload, epoch}; the receiver polls the
+    // payload slots themselves, so there is no release fence and no flag round trip
+    for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
+      for (int i = threadIdx.x; i < hv; i += blockDim.x) {
+        const size_t off = ((size_t)row * hv + i) * 16;
+        const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + off);
+        const uint4 s0 = make_uint4(v.x, llflag, v.y, llflag), s1 = make_uint4(v.z, llflag, v.w, llflag);
+#pragma unroll
+        for (int p = 0; p < kMaxRanks; ++p) {
+          if (p < W && p != me) {
+            char* dst = ctx.ll[p] + ((size_t)sy.parity(0) * kMaxRanks + me) * kLLSlotBytes + off * 2;
+            ptx::st_v4(dst, s0);
+            ptx::st_v4(dst + 16, s1);
+          }
+        }
+      }
+    }
+  } else if (W > 1 && a.ablate != kAblateSyncOnly) {
     for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
       for (int i = threadIdx.x; i < hv; i += blockDim.x) {
         const size_t off = ((size_t)row * hv + i) * 16;
@@ -679,7 +699,7 @@ __global__ void __launch_bounds__(1024) allreduce_residual_rmsnorm_kernel(const 
     }
   }
   bool ok = true;
-  if (W > 1) {
+  if (W > 1 && !ll) {
     sy.signal_all(0, 0);
     ok = sy.wait_all(0, 0);
   }
@@ -698,8 +718,28 @@ __global__ void __launch_bounds__(1024) allreduce_residual_rmsnorm_kernel(const 
           for (int p = 0; p < kMaxRanks; ++p) {
             if (p < W) {
               Vec<T> v;
-              if (p == me) *reinterpret_cast<uint4*>(&v) = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + off);
-              else v = load_stage<T>(mine + (size_t)p * slot + off);
+              if (p == me) {
+                *reinterpret_cast<uint4*>(&v) = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + off);
+              } else if (ll) {
+                const char* src = ctx.ll[me] + ((size_t)sy.parity(0) * kMaxRanks + p) * kLLSlotBytes + off * 2;
+                uint4 s0 = ptx::ld_volatile_v4(src), s1 = ptx::ld_volatile_v4(src + 16);
+                if (!(s0.y == llflag && s0.w == llflag && s1.y == llflag && s1.w == llflag)) {
+                  const uint64_t t0 = ptx::globaltimer_ns();
+                  uint32_t it = 0;
+                  while (true) {
+                    s0 = ptx::ld_volatile_v4(src);
+                    s1 = ptx::ld_volatile_v4(src + 16);
+                    if (s0.y == llflag && s0.w == llflag && s1.y == llflag && s1.w == llflag) break;
+                    if ((++it & 63u) == 0 && ptx::globaltimer_ns() - t0 > ctx.spin_ns) {
+                      sy.report(p, 0);
+                      break;
+                    }
+                  }
+                }
+                *reinterpret_cast<uint4*>(&v) = make_uint4(s0.x, s0.z, s1.x, s1.z);
+              } else {
+                v = load_stage<T>(mine + (size_t)p * slot + off);
+              }
 #pragma unroll
               for (int t = 0; t < N; ++t) acc[t] = (p == 0) ? to_acc(v.v[t]) : acc[t] + to_acc(v.v[t]);
             }

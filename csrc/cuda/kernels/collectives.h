@@ -75,6 +75,7 @@ struct FusedNormArgs {
   int hidden = 0;
   float eps = 1e-5f;
   int ablate = kAblateNone;
+  int use_ll = 0;   // 1: low-latency protocol (rows * hidden * 4 bytes must fit kLLSlotBytes)
 };
 cudaError_t launch_allreduce_residual_rmsnorm(int dtype, const RankCtx* ctx, const FusedNormArgs* args, const LaunchCfg& cfg);
 

@@ -11,7 +11,11 @@ constexpr int kMaxRanks = 8;
 constexpr int kMaxBlocks = 256;   // CTAs per collective kernel (flag slots per source rank)
 constexpr int kNumPhases = 5;     // phases 0-3: epoch flags of the collectives; 4: arrival counters of the fused GEMM ops
 constexpr size_t kFlagBytes = (size_t)kNumPhases * kMaxRanks * kMaxBlocks * sizeof(uint32_t);
-constexpr size_t kStateBytes = 4096;  // epoch, ticket, scratch tables (all-to-all counts, ...)
+constexpr size_t kStateBytes = 4096;
+// Low-latency ("LL") region: per parity and source rank one slot in which every 16-byte store carries
+// 8 bytes of payload and two copies of the call's epoch, so the receiver needs no separate flag.
+constexpr size_t kLLSlotBytes = 512 << 10;
+constexpr size_t kLLBytes = 2 * kMaxRanks * kLLSlotBytes;  // epoch, ticket, scratch tables (all-to-all counts, ...)
 
 // Status codes written to RankCtx::status[0]; status[1..3] = rank, peer, phase.
 enum : int { kStatusOk = 0, kStatusTimeout = 1, kStatusBounds = 2 };
@@ -23,6 +27,7 @@ struct RankCtx {
   int* status;                  // host-visible error record (4 ints)
   unsigned long long half_bytes;  // size of one data half
   unsigned long long spin_ns;     // wait budget
+  char* ll[kMaxRanks];          // peers' low-latency regions
   char* mc_data;                // NVLS multicast mapping of the arenas (nullptr if unavailable)
   int rank;
   int world;

@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "1446ecce481a152212983c6acec83772e4bc1d48"
+git_version = "c40f7d358ad5ff5eee0493c679461c427113f7eb"
