@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "c40f7d358ad5ff5eee0493c679461c427113f7eb"
+git_version = "954cb6ac0de02145c87d2d06ef884b6fd61a433e"
