@@ -3,11 +3,14 @@
 // tensor-parallel model code that wants the fused ops on its own stream.
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
+#include <sys/mman.h>
 #include <torch/csrc/distributed/c10d/Store.hpp>
 #include <torch/extension.h>
+#include <unistd.h>
 
 #include "bindings/common.h"
 #include "cuda/CudaComm.h"
+#include "cuda/Tuner.h"
 
 namespace ccl_py {
 
@@ -301,7 +304,65 @@ struct PyComm {
 
 }  // namespace
 
+// Two probes of the bootstrap layer, for tests and for checking a new machine.
+//
+// fd_exchange_probe: every rank creates an anonymous memory file holding its rank, the ranks
+// all-gather the descriptors over UNIX sockets, and every rank reads every file back. No GPU.
+bool fd_exchange_probe(const c10::intrusive_ptr<c10d::Store>& store, int rank, int world, const std::string& prefix) {
+  ccl::KvStore kv = make_kv(store);
+  const int fd = ::memfd_create("ccl-fdx-probe", MFD_CLOEXEC);
+  TORCH_CHECK(fd >= 0, "memfd_create failed");
+  const int32_t mine[2] = {0x0cc1, rank};
+  TORCH_CHECK(::pwrite(fd, mine, sizeof(mine), 0) == (ssize_t)sizeof(mine), "pwrite failed");
+  std::vector<int> fds = ccl::exchange_fds(kv, prefix, rank, world, fd, 30000);
+  ::close(fd);
+  bool ok = (int)fds.size() == world;
+  for (int p = 0; p < world && ok; ++p) {
+    int32_t got[2] = {0, -1};
+    ok = ::pread(fds[p], got, sizeof(got), 0) == (ssize_t)sizeof(got) && got[0] == 0x0cc1 && got[1] == p;
+  }
+  for (int f : fds) ::close(f);
+  return ok;
+}
+
+// symm_mem_probe: every rank allocates `bytes` of symmetric memory on the current device, fills
+// it with a pattern of its rank, and after a store barrier reads every peer's buffer through its
+// own mapping (plain copies, no kernel waits on another rank, so the ranks may share one GPU).
+bool symm_mem_probe(const c10::intrusive_ptr<c10d::Store>& store, int rank, int world, const std::string& kind,
+                    int64_t bytes, const std::string& prefix) {
+  ccl::KvStore kv = make_kv(store);
+  const int dev = (int)c10::cuda::current_device();
+  ccl::SymmMem mem(ccl::parse_symm_kind(kind), rank, world, dev, (size_t)bytes, kv, prefix);
+  const size_t n = (size_t)bytes / sizeof(uint32_t);
+  std::vector<uint32_t> host(n);
+  for (size_t i = 0; i < n; ++i) host[i] = (uint32_t)(rank + 1) * 0x01000193u + (uint32_t)i;
+  C10_CUDA_CHECK(cudaMemcpy(mem.local(), host.data(), n * sizeof(uint32_t), cudaMemcpyHostToDevice));
+  C10_CUDA_CHECK(cudaDeviceSynchronize());
+  ccl::barrier_kv(kv, prefix + "/probe/written", world, 30000);
+  bool ok = true;
+  for (int p = 0; p < world && ok; ++p) {
+    C10_CUDA_CHECK(cudaMemcpy(host.data(), mem.peer(p), n * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < n && ok; ++i) ok = host[i] == (uint32_t)(p + 1) * 0x01000193u + (uint32_t)i;
+  }
+  // nobody unmaps while a peer still reads
+  ccl::barrier_kv(kv, prefix + "/probe/read", world, 30000);
+  return ok;
+}
+
 void bind_cuda_comm(py::module& m) {
+  m.def("fd_exchange_probe", &fd_exchange_probe, py::arg("store"), py::arg("rank"), py::arg("world"),
+        py::arg("prefix") = "ccl/probe/fdx", py::call_guard<py::gil_scoped_release>());
+  m.def("symm_mem_probe", &symm_mem_probe, py::arg("store"), py::arg("rank"), py::arg("world"), py::arg("kind") = "vmm",
+        py::arg("bytes") = (int64_t)(4 << 20), py::arg("prefix") = "ccl/probe/symm", py::call_guard<py::gil_scoped_release>());
+  m.def("parse_tune_text", [](const std::string& text) {
+    py::dict out;
+    for (const auto& w : ccl::parse_tune_text(text, "<text>")) {
+      py::dict d;
+      for (const auto& kv : w.second) d[py::str(kv.first)] = kv.second;
+      out[py::int_(w.first)] = d;
+    }
+    return out;
+  });
   m.def("emu_missing_peer_probe", [](PyComm& c) {
     return c.comm->barrier_single_rank(0, c.stream()) == cudaSuccess;
   });

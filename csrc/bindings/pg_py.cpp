@@ -231,6 +231,32 @@ void bind_process_group(py::module& m) {
         int code = c.poll_status(&r, &p, &ph);
         return std::vector<int>{code, r, p, ph};
       })
+      .def("cuda_comm_config", [](ProcessGroupCCL& pg, const at::Tensor& t) {
+        const ccl::CommConfig& c = cuda_comm_of(pg, t).config();
+        py::dict d;
+        d["half_bytes"] = c.half_bytes;
+        d["oneshot_max_bytes"] = c.oneshot_max_bytes;
+        d["ag_push_max_bytes"] = c.ag_push_max_bytes;
+        d["max_blocks"] = c.max_blocks;
+        d["threads"] = c.threads;
+        d["spin_timeout_ms"] = c.spin_timeout_ms;
+        d["symm_mem"] = c.symm == ccl::SymmKind::kVmm ? "vmm" : "ipc";
+        return d;
+      })
+      .def("set_cuda_tuning", [](ProcessGroupCCL& pg, const at::Tensor& t, const py::dict& kv) {
+        // every rank of the group must apply the same values before its next collective
+        ccl::CommConfig& c = cuda_comm_of(pg, t).mutable_config();
+        for (auto item : kv) {
+          const std::string k = py::cast<std::string>(item.first);
+          const int64_t v = py::cast<int64_t>(item.second);
+          TORCH_CHECK(v >= 0, "tuning values are non-negative");
+          if (k == "oneshot_max_bytes") c.oneshot_max_bytes = (size_t)v;
+          else if (k == "ag_push_max_bytes") c.ag_push_max_bytes = (size_t)v;
+          else if (k == "max_blocks") { TORCH_CHECK(v >= 1 && v <= ccl::kMaxBlocks, "max_blocks out of range"); c.max_blocks = (int)v; }
+          else if (k == "threads") { TORCH_CHECK(v >= 32 && v <= 512 && v % 32 == 0, "threads out of range"); c.threads = (int)v; }
+          else TORCH_CHECK(false, "unknown tuning key '", k, "'");
+        }
+      })
       .def("cuda_kernel_launches", [](ProcessGroupCCL& pg, const at::Tensor& t) { return cuda_comm_of(pg, t).launches(); });
 
   m.def("reparse_env", [] { ccl::Env::reparse(); });
@@ -247,6 +273,9 @@ void bind_process_group(py::module& m) {
     d["arena_mb"] = e.arena_mb;
     d["shm_slot_mb"] = e.shm_slot_mb;
     d["max_blocks"] = e.max_blocks;
+    d["threads"] = e.threads;
+    d["symm_mem"] = e.symm_mem;
+    d["tune_file"] = e.tune_file;
     d["nvls"] = e.nvls;
     d["with_mpirun"] = e.with_mpirun;
     d["local_rank"] = e.local_rank;

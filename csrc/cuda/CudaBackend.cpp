@@ -1,4 +1,5 @@
 #include "cuda/CudaBackend.h"
+#include "cuda/Tuner.h"
 
 #include <c10/cuda/CUDACachingAllocator.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -304,9 +305,12 @@ CudaComm& CudaBackendImpl::comm(const at::Device& device) {
     const int64_t pg_ms = pg_->timeout().count();
     cfg.spin_timeout_ms = env.spin_timeout_ms > 0 ? (uint64_t)env.spin_timeout_ms
                                                   : (uint64_t)std::max<int64_t>(1000, std::min<int64_t>(pg_ms, 30000));
+    // measured thresholds for this machine first, explicit environment variables on top
+    if (!env.tune_file.empty()) apply_tuning(parse_tune_file(env.tune_file), size_, &cfg);
     if (env.oneshot_max_bytes >= 0) cfg.oneshot_max_bytes = (size_t)env.oneshot_max_bytes;
-    cfg.max_blocks = env.max_blocks;
-    cfg.threads = std::max(32, std::min(512, env.threads / 32 * 32));
+    if (env.max_blocks > 0) cfg.max_blocks = std::min(env.max_blocks, (int)kMaxBlocks);
+    if (env.threads > 0) cfg.threads = std::max(32, std::min(512, env.threads / 32 * 32));
+    cfg.symm = parse_symm_kind(env.symm_mem);
     if (env.algo == "oneshot") cfg.algo = Algo::kOneShot;
     else if (env.algo == "twoshot") cfg.algo = Algo::kTwoShot;
     if (env.work_only) cfg.ablate = kAblateWorkOnly;

@@ -56,17 +56,6 @@ void fill_ctx(RankCtx& c, int rank, int world, const std::vector<void*>& bases, 
   c.world = world;
 }
 
-void barrier_kv(KvStore& kv, const std::string& key, int world, uint64_t timeout_ms) {
-  if (!kv.add) return;
-  kv.add(key, 1);
-  const auto t0 = std::chrono::steady_clock::now();
-  while (kv.add(key, 0) < world) {
-    if (std::chrono::steady_clock::now() - t0 > std::chrono::milliseconds(timeout_ms))
-      throw std::runtime_error("ccl: timeout in bootstrap barrier '" + key + "'");
-    std::this_thread::sleep_for(std::chrono::milliseconds(1));
-  }
-}
-
 }  // namespace
 
 CudaComm::CudaComm(int rank, int world, int device, const CommConfig& cfg, KvStore kv,
@@ -78,45 +67,13 @@ CudaComm::CudaComm(int rank, int world, int device, const CommConfig& cfg, KvSto
   cfg_.half_bytes = round_up(cfg_.half_bytes, 1 << 20);
   if (cfg_.oneshot_max_bytes == 0) cfg_.oneshot_max_bytes = default_oneshot_max(world_);
   arena_bytes_ = arena_size(cfg_.half_bytes);
-  void* base = nullptr;
-  check(cudaMalloc(&base, arena_bytes_), "cudaMalloc(arena)");
-  check(cudaMemset(base, 0, arena_bytes_), "cudaMemset(arena)");
-  check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
-  local_arenas_.push_back(base);
-  peer_arenas_.assign(world_, nullptr);
-  peer_arenas_[rank_] = base;
-
   check(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped | cudaHostAllocPortable),
         "cudaHostAlloc(status)");
   std::memset(status_host_, 0, 64);
   check(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev_), status_host_, 0), "cudaHostGetDevicePointer");
-
-  if (world_ > 1) {
-    cudaIpcMemHandle_t h;
-    check(cudaIpcGetMemHandle(&h, base), "cudaIpcGetMemHandle");
-    std::vector<uint8_t> blob(sizeof(h) + sizeof(int));
-    std::memcpy(blob.data(), &h, sizeof(h));
-    std::memcpy(blob.data() + sizeof(h), &device_, sizeof(int));
-    kv_.set(prefix_ + "/ipc/" + std::to_string(rank_), blob);
-    for (int p = 0; p < world_; ++p) {
-      if (p == rank_) continue;
-      std::vector<uint8_t> pb = kv_.get(prefix_ + "/ipc/" + std::to_string(p));
-      if (pb.size() != blob.size()) throw std::runtime_error("ccl: malformed IPC handle from peer");
-      cudaIpcMemHandle_t ph;
-      int pdev = 0;
-      std::memcpy(&ph, pb.data(), sizeof(ph));
-      std::memcpy(&pdev, pb.data() + sizeof(ph), sizeof(int));
-      int can = 0;
-      check(cudaDeviceCanAccessPeer(&can, device_, pdev), "cudaDeviceCanAccessPeer");
-      if (!can && pdev != device_)
-        throw std::runtime_error("ccl: GPU " + std::to_string(device_) + " cannot access peer GPU " + std::to_string(pdev));
-      void* pp = nullptr;
-      check(cudaIpcOpenMemHandle(&pp, ph, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
-      peer_arenas_[p] = pp;
-    }
-    // nobody may signal into an arena before its owner has zeroed it and everyone has mapped it
-    barrier_kv(kv_, prefix_ + "/ready", world_, 120000);
-  }
+  // allocates and zeroes this rank's arena, maps every peer's, and returns once all ranks have
+  symm_ = std::make_unique<SymmMem>(cfg_.symm, rank_, world_, device_, arena_bytes_, kv_, prefix_);
+  peer_arenas_ = symm_->bases();
   init_tables();
 }
 
@@ -165,9 +122,8 @@ CudaComm::~CudaComm() {
       barrier_kv(kv_, prefix_ + "/bye", world_, 5000);
     } catch (...) {
     }
-    for (int p = 0; p < world_; ++p)
-      if (p != rank_ && peer_arenas_[p]) cudaIpcCloseMemHandle(peer_arenas_[p]);
   }
+  symm_.reset();
   for (void* a : local_arenas_) cudaFree(a);
   if (dev_ctx_table_) cudaFree(dev_ctx_table_);
   if (dev_args_table_) cudaFree(dev_args_table_);

@@ -5,7 +5,8 @@
 // Counterpart of the reference's IPC bring-up (`exchange_peer_ipc_mem`,
 // src/gpu/allreduce.h:1208-1248, which all-gathers Level-Zero IPC handles over UNIX sockets and
 // needs MPI_Barrier) and of its per-op branches in src/gpu/dpcpp_ccl.cpp:731-1656. Here the
-// handles are cudaIpc handles published through the c10d Store; no MPI is involved.
+// handles travel through the c10d Store (cudaIpc) or over UNIX sockets (driver virtual-memory
+// objects), see SymmMem.h; no MPI is involved.
 //
 // A CudaComm is either *real* (one process per GPU; nctx() == 1) or *emulated* (all ranks'
 // arenas on one GPU and one cooperative launch per collective; nctx() == world) — the latter
@@ -18,17 +19,12 @@
 #include <string>
 #include <vector>
 
+#include "cuda/SymmMem.h"
 #include "cuda/kernels/collectives.h"
 #include "cuda/kernels/gemm_collective.h"
 #include "cuda/kernels/moe_a2a.h"
 
 namespace ccl {
-
-struct KvStore {
-  std::function<void(const std::string&, const std::vector<uint8_t>&)> set;
-  std::function<std::vector<uint8_t>(const std::string&)> get;  // blocks until the key exists
-  std::function<int64_t(const std::string&, int64_t)> add;      // atomic counter
-};
 
 enum class Algo : int { kAuto = 0, kOneShot = 1, kTwoShot = 2, kNvls = 3 };
 
@@ -41,6 +37,7 @@ struct CommConfig {
   int threads = 512;
   Algo algo = Algo::kAuto;
   int ablate = kAblateNone;
+  SymmKind symm = SymmKind::kIpc;     // how the arenas are shared (CCL_SYMM_MEM = ipc | vmm)
 };
 
 // One-shot all_reduce moves (W-1)*S bytes into every GPU, two-shot 2*S*(W-1)/W: with two ranks
@@ -121,7 +118,8 @@ class CudaComm {
   KvStore kv_;
   std::string prefix_;
   size_t arena_bytes_ = 0;
-  std::vector<void*> local_arenas_;   // 1 (real) or world (emulated)
+  std::unique_ptr<SymmMem> symm_;     // real communicators: owns the arena and the peer mappings
+  std::vector<void*> local_arenas_;   // emulated communicators: one cudaMalloc per played rank
   std::vector<void*> peer_arenas_;    // real: mapped peer bases (own at [rank])
   std::vector<RankCtx> host_ctx_;     // nctx entries
   RankCtx* dev_ctx_table_ = nullptr;  // emulation only

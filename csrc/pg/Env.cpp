@@ -53,11 +53,12 @@ Env parse() {
   e.spin_timeout_ms = parse_env_int("CCL_SPIN_TIMEOUT_MS", -1);
   e.debug_bounds = parse_env_flag("CCL_DEBUG_BOUNDS", false);
   e.tune_file = env_str("CCL_TUNE_FILE", "");
+  e.symm_mem = env_str("CCL_SYMM_MEM", "ipc");
   e.log_level = (int)parse_env_int("CCL_LOG_LEVEL", 0);
   e.arena_mb = parse_env_int("CCL_ARENA_MB", 256);
   e.shm_slot_mb = parse_env_int("CCL_SHM_SLOT_MB", 4);
-  e.max_blocks = (int)parse_env_int("CCL_MAX_BLOCKS", 256);
-  e.threads = (int)parse_env_int("CCL_THREADS", 512);
+  e.max_blocks = (int)parse_env_int("CCL_MAX_BLOCKS", -1);
+  e.threads = (int)parse_env_int("CCL_THREADS", -1);
   // launcher detection (reference: ProcessGroupCCL.cpp:825-830,930-945; dpcpp_ccl.cpp:137-152)
   e.with_mpirun = std::getenv("MPI_LOCALRANKID") || std::getenv("MPI_LOCALNRANKS") ||
                   std::getenv("PMI_RANK") || std::getenv("PMI_SIZE") || std::getenv("PMIX_RANK");

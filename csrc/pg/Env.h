@@ -28,12 +28,13 @@ struct Env {
   int nvls = 0;                // CCL_NVLS
   int64_t spin_timeout_ms = -1;  // CCL_SPIN_TIMEOUT_MS (-1: derived from the group timeout)
   bool debug_bounds = false;   // CCL_DEBUG_BOUNDS
-  std::string tune_file;       // CCL_TUNE_FILE
+  std::string tune_file;       // CCL_TUNE_FILE: per-world algorithm thresholds (see cuda/Tuner.h)
+  std::string symm_mem = "ipc";  // CCL_SYMM_MEM = ipc | vmm: how CUDA arenas are shared
   int log_level = 0;           // CCL_LOG_LEVEL
   int64_t arena_mb = 256;      // CCL_ARENA_MB: one staging half per rank
   int64_t shm_slot_mb = 4;     // CCL_SHM_SLOT_MB: CPU shared-memory slot per rank
-  int max_blocks = 256;        // CCL_MAX_BLOCKS: CTAs of bandwidth-bound collectives
-  int threads = 512;           // CCL_THREADS: threads per CTA of the collective kernels
+  int max_blocks = -1;         // CCL_MAX_BLOCKS: CTAs of bandwidth-bound collectives (-1: 256 or the tuning file)
+  int threads = -1;            // CCL_THREADS: threads per CTA of the collective kernels (-1: 512 or the tuning file)
   int local_rank = -1;         // LOCAL_RANK / MPI_LOCALRANKID / ...
   int local_world_size = -1;   // LOCAL_WORLD_SIZE / MPI_LOCALNRANKS / PALS_LOCAL_SIZE
   bool with_mpirun = false;

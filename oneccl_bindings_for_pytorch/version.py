@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "954cb6ac0de02145c87d2d06ef884b6fd61a433e"
+git_version = "d0bdc7dd038ea40a0bc26ea7641e8c4b997dd693"

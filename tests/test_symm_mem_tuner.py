@@ -1,0 +1,85 @@
+"""Bootstrap layer: descriptor exchange over UNIX sockets, symmetric memory through cudaIpc and
+through driver virtual-memory objects, and the tuning file.
+
+The reference's counterparts are hand-run native programs (src/test/segfault/simple_test.cpp,
+src/test/writeremote/simple_test.cpp: map a peer's buffer through an IPC handle passed over a
+UNIX socket, then read / write it) with print-and-eyeball checking; here the same steps are
+asserted."""
+import os
+
+import pytest
+import torch
+
+from mp_util import run_ranks
+
+
+def _fdx(rank, world):
+    import torch.distributed as dist
+    import torch_ccl_b200._C as C
+
+    store = dist.distributed_c10d._get_default_store()
+    for i in range(3):  # repeated exchanges use fresh socket names
+        assert C.fd_exchange_probe(store, rank, world, "t/fdx/%d" % i)
+
+
+def test_fd_exchange_world4():
+    run_ranks(_fdx, world=4)
+
+
+def test_fd_exchange_world1():
+    run_ranks(_fdx, world=1)
+
+
+def test_tune_text_parser():
+    import torch_ccl_b200._C as C
+
+    t = C.parse_tune_text("# measured on 8 GPUs\n8 oneshot_max_bytes=524288 max_blocks=128  # x\n\n2 threads=256 ag_push_max_bytes=0\n")
+    assert t == {8: {"oneshot_max_bytes": 524288, "max_blocks": 128}, 2: {"threads": 256, "ag_push_max_bytes": 0}}
+    for bad, msg in [("8 foo=1", "unknown key"), ("9 threads=64", "world size"), ("8 threads=100", "out of range"),
+                     ("8 threads", "key=value"), ("8", "no key=value"), ("8 threads=64\n8 threads=64", "twice"),
+                     ("8 max_blocks=9999", "out of range"), ("x threads=64", "world size")]:
+        with pytest.raises(RuntimeError, match=msg):
+            C.parse_tune_text(bad)
+
+
+def _symm(rank, world, kind):
+    import torch.distributed as dist
+    import torch_ccl_b200._C as C
+
+    store = dist.distributed_c10d._get_default_store()
+    assert C.symm_mem_probe(store, rank, world, kind, 3 << 20, "t/symm/" + kind)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["ipc", "vmm"])
+def test_symm_mem_two_processes(kind):
+    # both processes may share one GPU: the probe only copies, no kernel waits for another rank
+    run_ranks(_symm, world=2, device="cuda", args=(kind,))
+
+
+def _tuned(rank, world, path):
+    import torch.distributed as dist
+
+    x = torch.ones(1024, device="cuda")
+    dist.all_reduce(x)
+    assert torch.equal(x, torch.full_like(x, world))
+    cfg = dist.distributed_c10d._get_default_group()._get_backend(torch.device("cuda")).cuda_comm_config(x)
+    assert cfg["oneshot_max_bytes"] == 12345 * 16 and cfg["threads"] == 256, cfg
+    assert cfg["max_blocks"] == 64, cfg  # CCL_MAX_BLOCKS wins over the file's 32
+    assert cfg["symm_mem"] == "vmm"
+    be = dist.distributed_c10d._get_default_group()._get_backend(torch.device("cuda"))
+    be.set_cuda_tuning(x, {"oneshot_max_bytes": 1})  # same call on every rank: forces two-shot
+    y = torch.full((1 << 16,), float(rank + 1), device="cuda")
+    dist.all_reduce(y)
+    assert torch.equal(y, torch.full_like(y, world * (world + 1) / 2))
+    assert be.cuda_comm_config(x)["oneshot_max_bytes"] == 1
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_tune_file_and_vmm_arena_applied(tmp_path):
+    world = 2
+    p = tmp_path / "tune.txt"
+    p.write_text("%d oneshot_max_bytes=%d threads=256 max_blocks=32\n" % (world, 12345 * 16))
+    run_ranks(_tuned, world=world, device="cuda", args=(str(p),),
+              env={"CCL_TUNE_FILE": str(p), "CCL_MAX_BLOCKS": "64", "CCL_SYMM_MEM": "vmm"})
