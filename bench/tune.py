@@ -108,7 +108,7 @@ def main():
                 head = line.split("#")[0].split()
                 if not head or head[0] != str(world):
                     keep.append(line.rstrip("\n"))
-        keep.append("%d oneshot_max_bytes=%d ag_push_max_bytes=%d" % (world, max(1, oneshot_max), ag_push_max))
+        keep.append("%d oneshot_max_bytes=%d ag_push_max_bytes=%d" % (world, max(1, oneshot_max), max(1, ag_push_max)))  # 0 would mean "built-in default"
         with open(a.out, "w") as f:
             f.write("\n".join(keep) + "\n")
         print(json.dumps({"world": world, "oneshot_max_bytes": oneshot_max, "ag_push_max_bytes": ag_push_max, "rows": rows}))

@@ -30,7 +30,9 @@ struct DeviceGuard {
 }  // namespace
 
 size_t default_oneshot_max(int world) {
-  if (world <= 2) return 8u << 20;
+  // two ranks: both algorithms move the same bytes and one-shot has one phase less; it was never
+  // slower up to 16 MB (bench/tune.py), so it is used whenever the tensor fits the staging half
+  if (world <= 2) return (size_t)1 << 40;
   if (world <= 4) return 1u << 20;
   return 512u << 10;
 }
@@ -66,6 +68,7 @@ CudaComm::CudaComm(int rank, int world, int device, const CommConfig& cfg, KvSto
   DeviceGuard g(device_);
   cfg_.half_bytes = round_up(cfg_.half_bytes, 1 << 20);
   if (cfg_.oneshot_max_bytes == 0) cfg_.oneshot_max_bytes = default_oneshot_max(world_);
+  if (cfg_.ag_push_max_bytes == 0) cfg_.ag_push_max_bytes = world_ <= 2 ? (2u << 20) : (256u << 10);
   arena_bytes_ = arena_size(cfg_.half_bytes);
   check(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped | cudaHostAllocPortable),
         "cudaHostAlloc(status)");
@@ -83,6 +86,7 @@ CudaComm::CudaComm(int world, int device, const CommConfig& cfg)
   DeviceGuard g(device_);
   cfg_.half_bytes = round_up(cfg_.half_bytes, 1 << 20);
   if (cfg_.oneshot_max_bytes == 0) cfg_.oneshot_max_bytes = default_oneshot_max(world_);
+  if (cfg_.ag_push_max_bytes == 0) cfg_.ag_push_max_bytes = 256u << 10;
   arena_bytes_ = arena_size(cfg_.half_bytes);
   for (int r = 0; r < world_; ++r) {
     void* base = nullptr;

@@ -32,7 +32,7 @@ struct CommConfig {
   size_t half_bytes = 256ull << 20;   // one staging half per rank (arena = 2 halves + flags)
   uint64_t spin_timeout_ms = 30000;   // device-side wait budget
   size_t oneshot_max_bytes = 0;        // 0: pick from the world size (see default_oneshot_max)
-  size_t ag_push_max_bytes = 256 << 10;  // per-piece size below which all_gather pushes
+  size_t ag_push_max_bytes = 0;        // per-piece size up to which all_gather pushes (0: 2 MB for 2 ranks, else 256 KB)
   int max_blocks = 256;               // CTAs for bandwidth-bound collectives
   int threads = 512;
   Algo algo = Algo::kAuto;

@@ -3,7 +3,7 @@
 //
 // Format: one line per world size, `#` starts a comment:
 //     <world> key=value [key=value ...]
-// keys: oneshot_max_bytes, ag_push_max_bytes, max_blocks, threads. Unknown keys and malformed
+// keys: oneshot_max_bytes, ag_push_max_bytes (0 = built-in default, 1 = never), max_blocks, threads. Unknown keys and malformed
 // lines are errors (a silently ignored tuning file is worse than none). Environment variables
 // that set the same knob explicitly win over the file.
 //

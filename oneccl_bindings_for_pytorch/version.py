@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "d0bdc7dd038ea40a0bc26ea7641e8c4b997dd693"
+git_version = "9d5c1fde7652430e1d25dbc36b3f717fba3c685d"
