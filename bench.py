@@ -179,7 +179,13 @@ def main():
 
     # ---- device-timed region: K decode steps --------------------------------------------------
     C.launch_count_reset()
+    # a profiler started with "--profile-from-start off" captures exactly the timed steps
+    profile_range = os.environ.get("CCL_BENCH_PROFILE_RANGE") == "1"
+    if profile_range:
+        torch.cuda.cudart().cudaProfilerStart()
     ms, clocks = timed(lambda: run_steps(K))
+    if profile_range:
+        torch.cuda.cudart().cudaProfilerStop()
     tokens_per_s = B * K / (ms * 1e-3)
 
     # ---- end to end through the public API: ids from pinned host memory, result read back ------

@@ -5,6 +5,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <dlfcn.h>
 #include <nccl.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <iostream>
 
@@ -368,6 +369,11 @@ c10::intrusive_ptr<c10d::Work> CudaBackendImpl::run(c10d::OpType type, const cha
   std::string algo;
   {
     RECORD_FUNCTION(title, std::vector<c10::IValue>{});
+    // NVTX range around the launches (a no-op unless a tool has injected the NVTX library)
+    nvtxRangePushA(title);
+    struct Pop {
+      ~Pop() { nvtxRangePop(); }
+    } pop;
     algo = fn(c, stream.stream());
   }
   work->end_ = acquire_event(dev, work->timed_);

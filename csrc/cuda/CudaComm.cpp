@@ -444,7 +444,7 @@ cudaError_t CudaComm::allreduce_residual_rmsnorm(int dtype, std::vector<FusedNor
   DeviceGuard g(device_);
   const FusedNormArgs& a0 = args[0];
   if (a0.hidden % 8 != 0 || a0.rows <= 0) return cudaErrorInvalidValue;
-  int threads = std::min(1024, std::max(32, ((a0.hidden / 8 + 31) / 32) * 32));
+  int threads = std::min(512, std::max(32, ((a0.hidden / 8 + 31) / 32) * 32));  // kernel is compiled for <= 512 threads
   if (a0.hidden / 8 > threads * 4) return cudaErrorInvalidValue;
   if ((size_t)a0.rows * a0.hidden * 2 > fused_norm_capacity() && world_ > 1) return cudaErrorInvalidValue;
   for (auto& a : args) {

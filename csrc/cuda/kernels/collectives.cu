@@ -652,7 +652,7 @@ template <> __device__ __forceinline__ __half round_to<__half>(float v) { return
 constexpr int kNormMaxVecPerThread = 4;
 
 template <typename T, bool EMU>
-__global__ void __launch_bounds__(1024) allreduce_residual_rmsnorm_kernel(const __grid_constant__ LaunchNorm<EMU> L) {
+__global__ void __launch_bounds__(512) allreduce_residual_rmsnorm_kernel(const __grid_constant__ LaunchNorm<EMU> L) {
   const RankCtx& ctx = EMU ? L.ctx_table[blockIdx.y] : L.ctx;
   const FusedNormArgs& a = EMU ? L.args_table[blockIdx.y] : L.args;
   __shared__ int s_failed;
@@ -705,6 +705,14 @@ __global__ void __launch_bounds__(1024) allreduce_residual_rmsnorm_kernel(const 
   }
   if (ok && a.ablate != kAblateSyncOnly) {
     const char* mine = sy.half(me, 0);
+    // the norm weights do not depend on the reduction: fetch them first so that their latency
+    // overlaps the peer waits and the block reduction
+    Vec<T> wv[kNormMaxVecPerThread];
+#pragma unroll
+    for (int k = 0; k < kNormMaxVecPerThread; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < hv) *reinterpret_cast<uint4*>(&wv[k]) = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(wgt) + (size_t)i * 16);
+    }
     for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
       float h[kNormMaxVecPerThread][N];
       float ss = 0.f;
@@ -776,11 +784,9 @@ __global__ void __launch_bounds__(1024) allreduce_residual_rmsnorm_kernel(const 
       for (int k = 0; k < kNormMaxVecPerThread; ++k) {
         const int i = threadIdx.x + k * blockDim.x;
         if (i < hv) {
-          Vec<T> w;
-          *reinterpret_cast<uint4*>(&w) = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(wgt) + (size_t)i * 16);
           Vec<T> o;
 #pragma unroll
-          for (int t = 0; t < N; ++t) o.v[t] = round_to<T>(to_acc(round_to<T>(h[k][t] * rstd)) * to_acc(w.v[t]));
+          for (int t = 0; t < N; ++t) o.v[t] = round_to<T>(to_acc(round_to<T>(h[k][t] * rstd)) * to_acc(wv[k].v[t]));
           *reinterpret_cast<uint4*>(reinterpret_cast<char*>(out) + ((size_t)row * hv + i) * 16) = *reinterpret_cast<const uint4*>(&o);
         }
       }

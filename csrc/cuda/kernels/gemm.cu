@@ -85,6 +85,19 @@ cudaError_t launch_persistent(const GemmDesc& d, cudaStream_t stream) {
   return e;
 }
 
+// Pipeline depth for a given split: narrow (decode) tiles are memory-bound, so when one CTA per SM
+// does not cover the grid the pipeline shrinks until two CTAs fit on an SM.
+template <int BN, bool DUAL>
+int stages_for(int64_t ctas, int k_iters, int splitk) {
+  size_t budget = 200 * 1024;
+  if (BN <= 32 && ctas > 148) budget = 104 * 1024;  // measured: 48/64/80 KB budgets were 0.2-6 % slower end to end
+  int stages = kMaxStages;
+  while (stages > 2 && smem_bytes<BN, DUAL>(stages, splitk) > budget) --stages;
+  const int per = (k_iters + splitk - 1) / splitk;
+  if (stages > per && per >= 2) stages = per;
+  return stages;
+}
+
 template <int BN, bool DUAL, typename OutT>
 cudaError_t launch(const GemmDesc& d, int splitk, cudaStream_t stream) {
   const int m_tiles = (int)((d.M + kBM - 1) / kBM);
@@ -92,18 +105,21 @@ cudaError_t launch(const GemmDesc& d, int splitk, cudaStream_t stream) {
   const int k_iters = (int)((d.K + kBK - 1) / kBK);
 
   constexpr size_t kSmemMax = 200 * 1024;
+  auto kern = gemm_kernel<BN, DUAL, OutT>;
+  static thread_local size_t configured = 0;
+  if (configured == 0) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax + 2048);
+    if (e != cudaSuccess) return e;
+    // the kernel keeps nothing in L1: give shared memory the whole array so that two CTAs fit
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return e;
+    configured = kSmemMax + 2048;
+  }
   // split-K: bounded by the portable cluster size and by the amount of K work per CTA
   if (splitk > 8) splitk = 8;
   while (splitk > 1 && k_iters / splitk < 2) --splitk;
   if (splitk < 1) splitk = 1;
-  // Narrow (decode) tiles are memory-bound: when one CTA per SM does not cover the grid, shrink
-  // the pipeline so that two CTAs fit on an SM and the whole grid is resident as one wave.
-  size_t budget = kSmemMax;
-  if (BN <= 32 && (int64_t)m_tiles * n_tiles * splitk > 148) budget = 104 * 1024;
-  int stages = kMaxStages;
-  while (stages > 2 && smem_bytes<BN, DUAL>(stages, splitk) > budget) --stages;
-  const int per = (k_iters + splitk - 1) / splitk;
-  if (stages > per && per >= 2) stages = per;
+  const int stages = stages_for<BN, DUAL>((int64_t)m_tiles * n_tiles * splitk, k_iters, splitk);
   const size_t smem = smem_bytes<BN, DUAL>(stages, splitk);
 
   CUtensorMap ta, tb;
@@ -134,13 +150,6 @@ cudaError_t launch(const GemmDesc& d, int splitk, cudaStream_t stream) {
   p.a_static = d.a_tiled;  // packed operands are weights: nothing on the stream produces them
   p.k_tiles = k_iters;
 
-  auto kern = gemm_kernel<BN, DUAL, OutT>;
-  static thread_local size_t configured = 0;
-  if (configured < smem) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax + 2048);
-    if (e != cudaSuccess) return e;
-    configured = kSmemMax + 2048;
-  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(m_tiles, n_tiles, splitk);
   cfg.blockDim = dim3(kThreads, 1, 1);
@@ -193,9 +202,12 @@ cudaError_t gemm_bf16_tn(const GemmDesc& d, cudaStream_t stream) {
     const int64_t k_iters = (d.K + 63) / 64;
     splitk = 1;
     if (bn <= 32) {
-      // memory-bound: measured best on B200 with roughly 200 CTAs in flight (between one and
-      // two per SM), keeping >= 4 K-steps per CTA
-      splitk = (int)((200 + tiles / 2) / tiles);
+      // memory-bound: the best split measured on B200 is the largest one that keeps the grid at
+      // no more than ~264 CTAs (just under two per SM, leaving room for cluster placement inside
+      // a GPC): 96 tiles -> 2, 86 SwiGLU tiles -> 3, 32 tiles -> 8, 250 tiles -> 1; one more step
+      // (e.g. 96 tiles x 3 = 288 CTAs) no longer fits one wave and costs 40 %. At least 4 K-steps
+      // stay in every CTA.
+      splitk = (int)(264 / tiles);
       if (splitk > 8) splitk = 8;
       while (splitk > 1 && k_iters / splitk < 4) --splitk;
       if (splitk < 1) splitk = 1;

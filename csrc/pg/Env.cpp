@@ -52,6 +52,7 @@ Env parse() {
   e.nvls = (int)parse_env_int("CCL_NVLS", 0);
   e.spin_timeout_ms = parse_env_int("CCL_SPIN_TIMEOUT_MS", -1);
   e.debug_bounds = parse_env_flag("CCL_DEBUG_BOUNDS", false);
+  e.debug_checks = parse_env_flag("CCL_DEBUG_CHECKS", false);
   e.tune_file = env_str("CCL_TUNE_FILE", "");
   e.symm_mem = env_str("CCL_SYMM_MEM", "ipc");
   e.log_level = (int)parse_env_int("CCL_LOG_LEVEL", 0);

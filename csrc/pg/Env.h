@@ -28,6 +28,7 @@ struct Env {
   int nvls = 0;                // CCL_NVLS
   int64_t spin_timeout_ms = -1;  // CCL_SPIN_TIMEOUT_MS (-1: derived from the group timeout)
   bool debug_bounds = false;   // CCL_DEBUG_BOUNDS
+  bool debug_checks = false;   // CCL_DEBUG_CHECKS: ranks compare {op, dtype, bytes} before every collective
   std::string tune_file;       // CCL_TUNE_FILE: per-world algorithm thresholds (see cuda/Tuner.h)
   std::string symm_mem = "ipc";  // CCL_SYMM_MEM = ipc | vmm: how CUDA arenas are shared
   int log_level = 0;           // CCL_LOG_LEVEL

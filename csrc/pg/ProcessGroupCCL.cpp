@@ -323,7 +323,42 @@ c10::intrusive_ptr<Work> ProcessGroupCCL::enqueueCpuP2P(OpType type, const char*
     const char* op; const char* dev; uint64_t bytes; double t0;                                          \
     ~HostTimer__() { Telemetry::get().record_host_time(op, dev, bytes, "", Telemetry::now_us() - t0); }  \
   } host_timer__{OPNAME, devname, bytes__, Telemetry::now_us()};                                         \
-  (void)flight__;
+  (void)flight__;                                                                                        \
+  if (Env::get().debug_checks) debugConsistencyCheck(OPNAME, (FIRST_TENSOR).scalar_type(), bytes__);
+
+// Debug mode (CCL_DEBUG_CHECKS=1): before a collective is enqueued, every rank publishes
+// {op, dtype, bytes} under the group's own collective counter and compares with every peer, so that
+// ranks that call different collectives (or the same one with different sizes) get an exception
+// naming both sides instead of a timeout or silently wrong data. The reference has no such check
+// (a mismatch there hangs inside oneCCL until the timeout, src/utils.h:295-319).
+void ProcessGroupCCL::debugConsistencyCheck(const char* op, at::ScalarType dtype, uint64_t bytes) {
+  const std::string name(op);
+  if (size_ == 1 || name == "send" || name == "recv") return;
+  // sizes may legitimately differ between ranks for the list / uneven forms
+  const bool sized = name == "allreduce" || name == "allreduce_coalesced" || name == "broadcast" || name == "reduce" ||
+                     name == "_allgather_base" || name == "_reduce_scatter_base" || name == "barrier";
+  const uint64_t n = check_seq_++;
+  const std::string mine = name + " " + c10::toString(dtype) + (sized ? " " + std::to_string(bytes) + " bytes" : "");
+  const std::string base = "ccl/chk/";
+  store_->set(base + std::to_string(n) + "/" + std::to_string(rank_), std::vector<uint8_t>(mine.begin(), mine.end()));
+  for (int p = 0; p < size_; ++p) {
+    if (p == rank_) continue;
+    const std::string key = base + std::to_string(n) + "/" + std::to_string(p);
+    try {
+      store_->wait({key}, timeout_);
+    } catch (const std::exception&) {
+      C10_THROW_ERROR(DistBackendError, "ccl: collective #" + std::to_string(n) + " (" + mine + ") on rank " + std::to_string(rank_) +
+                                            ": rank " + std::to_string(p) + " did not enter a collective within the timeout");
+    }
+    const std::vector<uint8_t> v = store_->get(key);
+    const std::string theirs(v.begin(), v.end());
+    if (theirs != mine)
+      C10_THROW_ERROR(DistBackendError, "ccl: collective mismatch at collective #" + std::to_string(n) + ": rank " + std::to_string(rank_) +
+                                            " called [" + mine + "] but rank " + std::to_string(p) + " called [" + theirs + "]");
+  }
+  // everyone has passed collective n-1 only after reading this rank's key of n-2: safe to drop it
+  if (n >= 2) store_->deleteKey(base + std::to_string(n - 2) + "/" + std::to_string(rank_));
+}
 
 static std::string flow_str(int from, int to) {
   return "[" + std::to_string(from) + "->" + std::to_string(to) + "]";

@@ -135,6 +135,7 @@ class ProcessGroupCCL : public Backend {
   bool blockingWait() const { return blocking_wait_; }
   bool sameStream() const { return same_stream_; }
   uint64_t nextSeq() { return seq_.fetch_add(1); }
+  void debugConsistencyCheck(const char* op, at::ScalarType dtype, uint64_t bytes);
   bool timingEnabled() const { return timing_enabled_; }
 
  private:
@@ -153,6 +154,7 @@ class ProcessGroupCCL : public Backend {
   bool same_stream_ = false;
   bool timing_enabled_ = false;
   std::atomic<uint64_t> seq_{0};
+  uint64_t check_seq_ = 0;  // collectives seen by debugConsistencyCheck (p2p excluded)
   std::atomic<bool> aborted_{false};
   int coalescing_depth_ = 0;
   std::vector<c10::intrusive_ptr<Work>> coalesced_works_;

@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "9d5c1fde7652430e1d25dbc36b3f717fba3c685d"
+git_version = "60d869f6482e34216bc6ea1997d8375e4bb550ab"

@@ -120,3 +120,36 @@ def _leaves_between_steps(rank, world):
 
 def test_regroup_after_a_rank_leaves():
     run_ranks(_leaves_between_steps, world=3, env={"CCL_TEST_NO_DESTROY": "1"})
+
+
+def _mismatched(rank, world):
+    """CCL_DEBUG_CHECKS=1: ranks that call different collectives get an error naming both sides."""
+    t = torch.ones(8)
+    dist.all_reduce(t)  # matching call passes
+    assert torch.all(t == world)
+    with pytest.raises(dist.DistBackendError, match="collective mismatch at collective #1.*8 bytes.*64 bytes|collective mismatch at collective #1.*64 bytes.*8 bytes"):
+        dist.all_reduce(torch.ones(2 if rank == 0 else 16))
+    with pytest.raises(dist.DistBackendError, match="collective mismatch"):
+        if rank == 0:
+            dist.broadcast(torch.ones(4), 0)
+        else:
+            dist.all_reduce(torch.ones(4))
+    with pytest.raises(dist.DistBackendError, match="collective mismatch.*Float.*Double|collective mismatch.*Double.*Float"):
+        dist.all_reduce(torch.ones(4, dtype=torch.float32 if rank == 0 else torch.float64))
+    # uneven all_to_all legitimately differs in size per rank: only the op and dtype are compared
+    ins = torch.arange(rank + 1 + world - 1, dtype=torch.float32)
+    in_split = [rank + 1] + [1] * (world - 1)
+    out_split = [p + 1 for p in range(world)] if rank == 0 else [1] * world
+    out = torch.empty(sum(out_split))
+    dist.all_to_all_single(out, ins, out_split, in_split)
+    assert out.numel() == (world * (world + 1) // 2 if rank == 0 else world)
+    # point-to-point traffic between two collectives does not disturb the counter
+    if rank == 0:
+        dist.send(torch.ones(3), 1)
+    elif rank == 1:
+        dist.recv(torch.empty(3), 0)
+    dist.all_reduce(t)
+
+
+def test_debug_checks_name_mismatched_collectives():
+    run_ranks(_mismatched, world=2, env={"CCL_DEBUG_CHECKS": "1", "CCL_TEST_TIMEOUT_S": "20"})
