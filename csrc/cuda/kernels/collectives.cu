@@ -558,6 +558,15 @@ __global__ void __launch_bounds__(512) all_to_all_kernel(const __grid_constant__
 // ---------------------------------------------------------------------------------------------
 // rooted ops (bytes): broadcast, gather, scatter. The root and the other ranks acknowledge each
 // round so that nobody can run more than one round ahead of a rank that still reads staging.
+//
+// Every kernel of this file keeps one invariant: a rank leaves round r only after EVERY rank has
+// entered round r. The unrooted kernels get it from their all-to-all flag exchange; gather gets it
+// because the root answers only after it has heard from everybody. Broadcast and scatter need a
+// third step for it: after the last acknowledgement the root releases the other ranks (phase 2).
+// Without the release a non-root rank could finish the round knowing only that the ROOT had
+// entered it, get two rounds ahead of a third rank that is still pulling from a peer's staging
+// half in an earlier all_gather / two-shot kernel, and (as the root of a later broadcast) overwrite
+// that half. tests/native/epoch_model.cpp reproduces exactly that on host threads.
 // ---------------------------------------------------------------------------------------------
 template <bool EMU>
 __global__ void __launch_bounds__(512) rooted_kernel(const __grid_constant__ Launch<EMU> L) {
@@ -579,10 +588,12 @@ __global__ void __launch_bounds__(512) rooted_kernel(const __grid_constant__ Lau
           for (int q = 1; q < W; ++q) copy_user_to_stage(buf, bytes, vb, sy.half((me + q) % W, rd), r);
         sy.signal_all(0, rd);
         ok = sy.wait_all(1, rd);
+        sy.signal_all(2, rd);  // release, see the note above the kernel
       } else {
         ok = sy.wait_one(root, 0, rd);
         if (ok && do_work) copy_stage_to_user(sy.half(me, rd), buf, bytes, vb, r);
         sy.signal_one(root, 1, rd);
+        if (ok) ok = sy.wait_one(root, 2, rd);
       }
     } else if (a.mode == kGather) {
       const T* in = reinterpret_cast<const T*>(a.in);
@@ -613,10 +624,12 @@ __global__ void __launch_bounds__(512) rooted_kernel(const __grid_constant__ Lau
         }
         sy.signal_all(0, rd);
         ok = sy.wait_all(1, rd);
+        sy.signal_all(2, rd);  // release
       } else {
         ok = sy.wait_one(root, 0, rd);
         if (ok && do_work) copy_stage_to_user(sy.half(me, rd), out, bytes, vb, r);
         sy.signal_one(root, 1, rd);
+        if (ok) ok = sy.wait_one(root, 2, rd);
       }
     }
   }

@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "60d869f6482e34216bc6ea1997d8375e4bb550ab"
+git_version = "3d0cdeceb6f67ae9d14cff0ef9a8b959bc8ab19b"

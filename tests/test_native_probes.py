@@ -30,3 +30,45 @@ def test_probe_runs(mode):
     _build()
     r = subprocess.run([BIN, mode], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "PASS" in r.stdout, r.stdout + r.stderr
+
+
+def _build_shm_stress(tag, flags):
+    import torch
+
+    out = os.path.join(HERE, "shm_stress_" + tag)
+    root = os.path.dirname(os.path.dirname(HERE))
+    srcs = [os.path.join(HERE, "shm_stress.cpp"), os.path.join(root, "csrc", "cpu", "ShmComm.cpp"),
+            os.path.join(root, "csrc", "cpu", "CpuCollectives.cpp")]
+    if os.path.exists(out) and all(os.path.getmtime(out) >= os.path.getmtime(s) for s in srcs):
+        return out
+    inc = ["-I" + os.path.join(root, "csrc"), "-I" + os.path.join(os.path.dirname(torch.__file__), "include"),
+           "-I/usr/local/cuda/include"]
+    subprocess.run(["g++", "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer"] + flags + inc + srcs + ["-o", out, "-lrt", "-lpthread"],
+                   check=True)
+    return out
+
+
+@pytest.mark.parametrize("tag,flags", [("asan", ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"]),
+                                       ("tsan", ["-fsanitize=thread"])])
+def test_cpu_backend_under_sanitizers(tag, flags):
+    """The shared-memory collectives and send/recv channels, ranks as threads, under ASan+UBSan and TSan."""
+    exe = _build_shm_stress(tag, flags)
+    env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=0", TSAN_OPTIONS="halt_on_error=1")
+    r = subprocess.run([exe, "4", "12"], capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0 and "PASS" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+    assert "ERROR: AddressSanitizer" not in r.stderr and "WARNING: ThreadSanitizer" not in r.stderr and "runtime error" not in r.stderr
+
+
+def test_epoch_protocol_model_under_tsan():
+    """Host-thread model of the flag / epoch / parity protocol: random programs of all_reduce,
+    all_gather and broadcast with slow ranks are race-free under ThreadSanitizer, and the same model
+    without the broadcast release step shows the corruption that the step prevents."""
+    src = os.path.join(HERE, "epoch_model.cpp")
+    exe = os.path.join(HERE, "epoch_model_tsan")
+    if not (os.path.exists(exe) and os.path.getmtime(exe) >= os.path.getmtime(src)):
+        subprocess.run(["g++", "-std=c++17", "-O1", "-g", "-fsanitize=thread", src, "-o", exe, "-lpthread"], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "PASS" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+    assert "ThreadSanitizer" not in r.stderr, r.stderr[-4000:]
+    r = subprocess.run([exe, "norelease"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 3, "the model must detect the hazard when the release step is removed: " + r.stdout
