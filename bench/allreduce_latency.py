@@ -27,11 +27,14 @@ def main():
     dist.init_process_group("ccl", rank=rank, world_size=world)
     be = get_backend(None, "cuda")
     mode = "sync_only" if os.environ.get("TORCH_CCL_SYNC_ONLY") == "1" else ("work_only" if os.environ.get("TORCH_CCL_WORK_ONLY") == "1" else "full")
-    sizes = [8 << 10, 32 << 10, 128 << 10, 512 << 10, 1 << 20, 2 << 20, 4 << 20, 8 << 20, 32 << 20]
+    sizes = [8 << 10, 32 << 10, 128 << 10, 512 << 10, 1 << 20, 2 << 20, 4 << 20, 8 << 20, 32 << 20, 128 << 20]
+    probe = torch.ones(8, device=dev)
+    dist.all_reduce(probe)
+    nvls = bool(be.cuda_comm_config(probe)["nvls_available"])  # CCL_NVLS=1: sizes >= 4 MB go through the switch
     for dtype in (torch.bfloat16,):
         for size in sizes:
             t = torch.ones(size // dtype.itemsize, device=dev, dtype=dtype)
-            iters = 50
+            iters = 50 if size <= (8 << 20) else 10
             g = torch.cuda.CUDAGraph()
             be.fused_allreduce(t, 1.0)
             torch.cuda.synchronize()
@@ -54,7 +57,8 @@ def main():
             us = torch.tensor([e0.elapsed_time(e1) / iters * 1e3], device=dev, dtype=torch.float64)
             dist.all_reduce(us, op=dist.ReduceOp.MAX)
             if rank == 0:
-                print(json.dumps({"mode": mode, "world": world, "dtype": str(dtype).split(".")[-1], "bytes": size, "us": round(float(us), 2)}), flush=True)
+                print(json.dumps({"mode": mode, "world": world, "dtype": str(dtype).split(".")[-1], "bytes": size, "us": round(float(us), 2),
+                                  "busbw_GBps": round(size * 2 * (world - 1) / world / float(us) / 1e3, 1), "nvls": nvls}), flush=True)
             del g
     dist.destroy_process_group()
 

@@ -107,7 +107,8 @@ struct PyComm {
     cudaError_t e = comm->allreduce(to_ccl_dtype(ins[0].scalar_type()), args, stream(), &ch);
     comm->mutable_config().algo = saved;
     cu(e, "allreduce");
-    return std::string(ch.algo == ccl::Algo::kOneShot ? "oneshot" : "twoshot") + ":" + std::to_string(ch.nblocks);
+    const char* name = ch.algo == ccl::Algo::kOneShot ? "oneshot" : (ch.algo == ccl::Algo::kNvls ? "nvls" : "twoshot");
+    return std::string(name) + ":" + std::to_string(ch.nblocks);
   }
 
   void reduce(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, int op, int root) {
@@ -385,10 +386,12 @@ void bind_cuda_comm(py::module& m) {
       .def_static(
           "create",
           [](const c10::intrusive_ptr<c10d::Store>& store, int rank, int world, int64_t half_bytes,
-             int64_t spin_ms, const std::string& prefix) {
+             int64_t spin_ms, const std::string& prefix, const std::string& symm, bool nvls) {
             ccl::CommConfig cfg;
             cfg.half_bytes = (size_t)half_bytes;
             cfg.spin_timeout_ms = (uint64_t)spin_ms;
+            cfg.symm = ccl::parse_symm_kind(symm);
+            cfg.nvls = nvls;
             auto p = std::make_unique<PyComm>();
             py::gil_scoped_release nogil;
             p->comm = std::make_unique<CudaComm>(rank, world, (int)c10::cuda::current_device(), cfg,
@@ -396,7 +399,8 @@ void bind_cuda_comm(py::module& m) {
             return p;
           },
           py::arg("store"), py::arg("rank"), py::arg("world"), py::arg("half_bytes") = (int64_t)(64 << 20),
-          py::arg("spin_ms") = 30000, py::arg("prefix") = "ccl/direct")
+          py::arg("spin_ms") = 30000, py::arg("prefix") = "ccl/direct", py::arg("symm") = "ipc", py::arg("nvls") = false)
+      .def_property_readonly("nvls_available", [](PyComm& c) { return c.comm->nvls_available(); })
       .def_property_readonly("world", [](PyComm& c) { return c.comm->world(); })
       .def_property_readonly("rank", [](PyComm& c) { return c.comm->rank(); })
       .def_property_readonly("nctx", [](PyComm& c) { return c.comm->nctx(); })

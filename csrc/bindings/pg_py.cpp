@@ -241,6 +241,8 @@ void bind_process_group(py::module& m) {
         d["threads"] = c.threads;
         d["spin_timeout_ms"] = c.spin_timeout_ms;
         d["symm_mem"] = c.symm == ccl::SymmKind::kVmm ? "vmm" : "ipc";
+        d["nvls"] = c.nvls;
+        d["nvls_available"] = cuda_comm_of(pg, t).nvls_available();
         return d;
       })
       .def("set_cuda_tuning", [](ProcessGroupCCL& pg, const at::Tensor& t, const py::dict& kv) {

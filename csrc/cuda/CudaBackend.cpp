@@ -312,8 +312,14 @@ CudaComm& CudaBackendImpl::comm(const at::Device& device) {
     if (env.max_blocks > 0) cfg.max_blocks = std::min(env.max_blocks, (int)kMaxBlocks);
     if (env.threads > 0) cfg.threads = std::max(32, std::min(512, env.threads / 32 * 32));
     cfg.symm = parse_symm_kind(env.symm_mem);
+    if (env.nvls || env.algo == "nvls") {
+      // the multicast object binds driver virtual-memory allocations only
+      cfg.nvls = true;
+      cfg.symm = SymmKind::kVmm;
+    }
     if (env.algo == "oneshot") cfg.algo = Algo::kOneShot;
     else if (env.algo == "twoshot") cfg.algo = Algo::kTwoShot;
+    else if (env.algo == "nvls") cfg.algo = Algo::kNvls;
     if (env.work_only) cfg.ablate = kAblateWorkOnly;
     if (env.sync_only) cfg.ablate = kAblateSyncOnly;
     comm_ = std::make_shared<CudaComm>(rank_, size_, dev, cfg, ccl_py::make_kv(store_), "ccl/cuda/" + device_key(at::Device(at::kCUDA, 0)));

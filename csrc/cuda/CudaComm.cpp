@@ -42,7 +42,7 @@ namespace {
 size_t arena_size(size_t half) { return 2 * half + kFlagBytes + kStateBytes + kLLBytes; }
 
 void fill_ctx(RankCtx& c, int rank, int world, const std::vector<void*>& bases, size_t half,
-              uint64_t spin_ms, int* status) {
+              uint64_t spin_ms, int* status, void* multicast_base) {
   std::memset(&c, 0, sizeof(c));
   for (int p = 0; p < world; ++p) {
     c.data[p] = static_cast<char*>(bases[p]);
@@ -53,7 +53,7 @@ void fill_ctx(RankCtx& c, int rank, int world, const std::vector<void*>& bases, 
   c.status = status;
   c.half_bytes = half;
   c.spin_ns = spin_ms * 1000000ull;
-  c.mc_data = nullptr;
+  c.mc_data = static_cast<char*>(multicast_base);
   c.rank = rank;
   c.world = world;
 }
@@ -75,7 +75,8 @@ CudaComm::CudaComm(int rank, int world, int device, const CommConfig& cfg, KvSto
   std::memset(status_host_, 0, 64);
   check(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev_), status_host_, 0), "cudaHostGetDevicePointer");
   // allocates and zeroes this rank's arena, maps every peer's, and returns once all ranks have
-  symm_ = std::make_unique<SymmMem>(cfg_.symm, rank_, world_, device_, arena_bytes_, kv_, prefix_);
+  symm_ = std::make_unique<SymmMem>(cfg_.symm, rank_, world_, device_, arena_bytes_, kv_, prefix_,
+                                    cfg_.nvls && cfg_.symm == SymmKind::kVmm);
   peer_arenas_ = symm_->bases();
   init_tables();
 }
@@ -108,7 +109,8 @@ void CudaComm::init_tables() {
   host_ctx_.resize(n);
   for (int i = 0; i < n; ++i) {
     const int r = emulated_ ? i : rank_;
-    fill_ctx(host_ctx_[i], r, world_, peer_arenas_, cfg_.half_bytes, cfg_.spin_timeout_ms, status_dev_);
+    fill_ctx(host_ctx_[i], r, world_, peer_arenas_, cfg_.half_bytes, cfg_.spin_timeout_ms, status_dev_,
+             symm_ ? symm_->multicast_base() : nullptr);
   }
   if (emulated_) {
     check(cudaMalloc(reinterpret_cast<void**>(&dev_ctx_table_), sizeof(RankCtx) * n), "cudaMalloc(ctx table)");
@@ -212,7 +214,12 @@ cudaError_t CudaComm::allreduce(int dtype, std::vector<CollArgs> args, cudaStrea
   Algo algo = cfg_.algo;
   const size_t slot = round_up(nvec * 16, 128);
   const bool fits_oneshot = slot * world_ <= cfg_.half_bytes;
-  if (algo == Algo::kAuto || algo == Algo::kNvls)
+  // the switch reduces SUMs of bf16 / f16 / f32 only; the emulation plays it in software when forced
+  const bool nvls_ok = (emulated_ || nvls_available()) && args[0].op == kSum && (dtype == kBF16 || dtype == kF16 || dtype == kF32) &&
+                       world_ > (emulated_ ? 1 : 0);
+  if (algo == Algo::kNvls && !nvls_ok) algo = Algo::kAuto;
+  if (algo == Algo::kAuto && !emulated_ && cfg_.nvls && nvls_ok && bytes >= cfg_.nvls_min_bytes) algo = Algo::kNvls;
+  if (algo == Algo::kAuto)
     algo = (bytes <= cfg_.oneshot_max_bytes && fits_oneshot) ? Algo::kOneShot : Algo::kTwoShot;
   if (algo == Algo::kOneShot && !fits_oneshot) algo = Algo::kTwoShot;
   for (auto& a : args) {
@@ -224,6 +231,13 @@ cudaError_t CudaComm::allreduce(int dtype, std::vector<CollArgs> args, cudaStrea
   if (algo == Algo::kOneShot) {
     lc = launch_cfg(blocks_for(nvec, cfg_.max_blocks), threads_for(nvec, blocks_for(nvec, cfg_.max_blocks), cfg_.threads), stream);
     e = launch_allreduce_oneshot(dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  } else if (algo == Algo::kNvls) {
+    size_t stride = cfg_.half_bytes / (16 * (size_t)world_);
+    stride = compact_stride(stride / 8 * 8, (nvec + world_ - 1) / world_);
+    for (auto& a : args) a.chunk_vecs = stride;
+    const size_t per_shard = (nvec + world_ - 1) / world_;
+    lc = launch_cfg(blocks_for(per_shard, cfg_.max_blocks), threads_for(per_shard, blocks_for(per_shard, cfg_.max_blocks), cfg_.threads), stream);
+    e = launch_allreduce_nvls(dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
   } else {
     size_t stride = cfg_.half_bytes / (16 * (size_t)(world_ + 1));
     stride = compact_stride(stride / 8 * 8, (nvec + world_ - 1) / world_);

@@ -38,6 +38,10 @@ struct CommConfig {
   Algo algo = Algo::kAuto;
   int ablate = kAblateNone;
   SymmKind symm = SymmKind::kIpc;     // how the arenas are shared (CCL_SYMM_MEM = ipc | vmm)
+  // NVLS: bind the arenas to an NVLink multicast object (needs symm = kVmm and device support) and
+  // route SUM all_reduces of bf16 / f16 / f32 of at least nvls_min_bytes through the switch.
+  bool nvls = false;                  // CCL_NVLS
+  size_t nvls_min_bytes = 4u << 20;
 };
 
 // One-shot all_reduce moves (W-1)*S bytes into every GPU, two-shot 2*S*(W-1)/W: with two ranks
@@ -65,6 +69,8 @@ class CudaComm {
   int nctx() const { return emulated_ ? world_ : 1; }
   int device() const { return device_; }
   bool emulated() const { return emulated_; }
+  // True when the arenas are mapped through a multicast object (real communicators only).
+  bool nvls_available() const { return symm_ && symm_->multicast_base() != nullptr; }
   const CommConfig& config() const { return cfg_; }
   CommConfig& mutable_config() { return cfg_; }
   const RankCtx& ctx(int i = 0) const { return host_ctx_[i]; }

@@ -197,6 +197,13 @@ struct Driver {
   decltype(&cuMemImportFromShareableHandle) MemImport = nullptr;
   decltype(&cuMemGetAllocationGranularity) MemGranularity = nullptr;
   decltype(&cuGetErrorString) GetErrorString = nullptr;
+  decltype(&cuDeviceGet) DeviceGet = nullptr;
+  decltype(&cuDeviceGetAttribute) DeviceGetAttribute = nullptr;
+  decltype(&cuMulticastCreate) MulticastCreate = nullptr;
+  decltype(&cuMulticastAddDevice) MulticastAddDevice = nullptr;
+  decltype(&cuMulticastBindMem) MulticastBindMem = nullptr;
+  decltype(&cuMulticastUnbind) MulticastUnbind = nullptr;
+  decltype(&cuMulticastGetGranularity) MulticastGetGranularity = nullptr;
 
   template <typename F>
   static void load(const char* name, F* fn) {
@@ -219,6 +226,13 @@ struct Driver {
     load("cuMemImportFromShareableHandle", &MemImport);
     load("cuMemGetAllocationGranularity", &MemGranularity);
     load("cuGetErrorString", &GetErrorString);
+    load("cuDeviceGet", &DeviceGet);
+    load("cuDeviceGetAttribute", &DeviceGetAttribute);
+    load("cuMulticastCreate", &MulticastCreate);
+    load("cuMulticastAddDevice", &MulticastAddDevice);
+    load("cuMulticastBindMem", &MulticastBindMem);
+    load("cuMulticastUnbind", &MulticastUnbind);
+    load("cuMulticastGetGranularity", &MulticastGetGranularity);
   }
 
   void ok(CUresult r, const char* what) const {
@@ -236,15 +250,26 @@ const Driver& driver() {
 
 }  // namespace
 
-SymmMem::SymmMem(SymmKind kind, int rank, int world, int device, size_t bytes, KvStore& kv, const std::string& prefix)
+bool SymmMem::multicast_supported(int device) {
+  const Driver& d = driver();
+  CUdevice dev;
+  if (d.DeviceGet(&dev, device) != CUDA_SUCCESS) return false;
+  int ok = 0;
+  if (d.DeviceGetAttribute(&ok, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, dev) != CUDA_SUCCESS) return false;
+  return ok != 0;
+}
+
+SymmMem::SymmMem(SymmKind kind, int rank, int world, int device, size_t bytes, KvStore& kv, const std::string& prefix,
+                 bool multicast)
     : kind_(kind), rank_(rank), world_(world), device_(device), bytes_(bytes), mapped_(bytes) {
   bases_.assign(world_, nullptr);
   check(cudaSetDevice(device_), "cudaSetDevice");
   check(cudaFree(nullptr), "context creation");
+  if (multicast && kind_ != SymmKind::kVmm) throw std::runtime_error("ccl: multicast needs CCL_SYMM_MEM=vmm");
   if (kind_ == SymmKind::kIpc)
     init_ipc(kv, prefix);
   else
-    init_vmm(kv, prefix);
+    init_vmm(kv, prefix, multicast && world_ > 1 && multicast_supported(device_));  // an object needs >= 2 devices
   // nobody may write into a buffer before its owner has zeroed it and everyone has mapped it
   if (world_ > 1) barrier_kv(kv, prefix + "/ready", world_, 120000);
 }
@@ -280,7 +305,7 @@ void SymmMem::init_ipc(KvStore& kv, const std::string& prefix) {
   }
 }
 
-void SymmMem::init_vmm(KvStore& kv, const std::string& prefix) {
+void SymmMem::init_vmm(KvStore& kv, const std::string& prefix, bool multicast) {
   const Driver& d = driver();
   CUmemAllocationProp prop;
   std::memset(&prop, 0, sizeof(prop));
@@ -291,6 +316,17 @@ void SymmMem::init_vmm(KvStore& kv, const std::string& prefix) {
   size_t gran = 0;
   d.ok(d.MemGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED), "cuMemGetAllocationGranularity");
   if (gran == 0) gran = 2u << 20;
+  if (multicast) {
+    // the bound range must also be a multiple of the multicast granularity
+    CUmulticastObjectProp mp;
+    std::memset(&mp, 0, sizeof(mp));
+    mp.numDevices = (unsigned)world_;
+    mp.size = bytes_;
+    mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+    size_t mg = 0;
+    d.ok(d.MulticastGetGranularity(&mg, &mp, CU_MULTICAST_GRANULARITY_RECOMMENDED), "cuMulticastGetGranularity");
+    if (mg > gran) gran = (mg + gran - 1) / gran * gran;
+  }
   mapped_ = (bytes_ + gran - 1) / gran * gran;
   handles_.assign(world_, 0);
 
@@ -314,7 +350,10 @@ void SymmMem::init_vmm(KvStore& kv, const std::string& prefix) {
   bases_[rank_] = map(own);
   check(cudaMemset(bases_[rank_], 0, mapped_), "cudaMemset(symmetric memory)");
   check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
-  if (world_ == 1) return;
+  if (world_ == 1) {
+    if (multicast) init_multicast(kv, prefix, gran);
+    return;
+  }
 
   int fd = -1;
   d.ok(d.MemExport(&fd, own, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0), "cuMemExportToShareableHandle");
@@ -340,6 +379,89 @@ void SymmMem::init_vmm(KvStore& kv, const std::string& prefix) {
     throw;
   }
   for (int f : fds) ::close(f);  // the imported handles keep the memory alive
+  if (multicast) init_multicast(kv, prefix, gran);
+}
+
+// One multicast object for the communicator: rank 0 creates it and hands its descriptor to the
+// others; every rank adds its device, then (once all devices are in) binds its own allocation and
+// maps the object. A store through the mapping lands in every rank's allocation, a
+// multimem.ld_reduce through it returns the sum over all of them.
+void SymmMem::release_multicast() {
+  const Driver& d = driver();
+  if (mc_base_) {
+    d.MemUnmap(reinterpret_cast<CUdeviceptr>(mc_base_), mapped_);
+    d.MemAddressFree(reinterpret_cast<CUdeviceptr>(mc_base_), mapped_);
+    mc_base_ = nullptr;
+  }
+  if (mc_handle_) {
+    CUdevice dev;
+    if (mc_bound_ && d.DeviceGet(&dev, device_) == CUDA_SUCCESS) d.MulticastUnbind(mc_handle_, dev, 0, mapped_);
+    mc_bound_ = false;
+    d.MemRelease(mc_handle_);
+    mc_handle_ = 0;
+  }
+}
+
+void SymmMem::init_multicast(KvStore& kv, const std::string& prefix, size_t gran) {
+  // a process must never go away with its memory still bound to the object: undo on any failure
+  try {
+    init_multicast_impl(kv, prefix, gran);
+  } catch (...) {
+    release_multicast();
+    throw;
+  }
+}
+
+void SymmMem::init_multicast_impl(KvStore& kv, const std::string& prefix, size_t gran) {
+  const Driver& d = driver();
+  CUmulticastObjectProp mp;
+  std::memset(&mp, 0, sizeof(mp));
+  mp.numDevices = (unsigned)world_;
+  mp.size = mapped_;
+  mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  CUmemGenericAllocationHandle mc = 0;
+  if (rank_ == 0) {
+    d.ok(d.MulticastCreate(&mc, &mp), "cuMulticastCreate");
+    mc_handle_ = mc;
+  }
+  if (world_ > 1) {
+    // all-gather of descriptors; only rank 0's matters, the others pass their own allocation's
+    int fd = -1;
+    d.ok(d.MemExport(&fd, rank_ == 0 ? mc : (CUmemGenericAllocationHandle)handles_[rank_], CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0),
+         "cuMemExportToShareableHandle(multicast)");
+    std::vector<int> fds;
+    try {
+      fds = exchange_fds(kv, prefix + "/mc", rank_, world_, fd, 120000);
+    } catch (...) {
+      ::close(fd);
+      throw;
+    }
+    ::close(fd);
+    CUresult r = CUDA_SUCCESS;
+    if (rank_ != 0)
+      r = d.MemImport(&mc, reinterpret_cast<void*>(static_cast<uintptr_t>(fds[0])), CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+    for (int f : fds) ::close(f);
+    d.ok(r, "cuMemImportFromShareableHandle(multicast)");
+  }
+  mc_handle_ = mc;
+  CUdevice dev;
+  d.ok(d.DeviceGet(&dev, device_), "cuDeviceGet");
+  d.ok(d.MulticastAddDevice(mc, dev), "cuMulticastAddDevice");
+  // memory may be bound only after every device has been added
+  if (world_ > 1) barrier_kv(kv, prefix + "/mc/added", world_, 120000);
+  d.ok(d.MulticastBindMem(mc, 0, (CUmemGenericAllocationHandle)handles_[rank_], 0, mapped_, 0), "cuMulticastBindMem");
+  mc_bound_ = true;
+  if (world_ > 1) barrier_kv(kv, prefix + "/mc/bound", world_, 120000);
+  CUmemAccessDesc access;
+  std::memset(&access, 0, sizeof(access));
+  access.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  access.location.id = device_;
+  access.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  CUdeviceptr va = 0;
+  d.ok(d.MemAddressReserve(&va, mapped_, gran, 0, 0), "cuMemAddressReserve(multicast)");
+  d.ok(d.MemMap(va, mapped_, 0, mc, 0), "cuMemMap(multicast)");
+  d.ok(d.MemSetAccess(va, mapped_, &access, 1), "cuMemSetAccess(multicast)");
+  mc_base_ = reinterpret_cast<void*>(va);
 }
 
 SymmMem::~SymmMem() {
@@ -352,6 +474,8 @@ SymmMem::~SymmMem() {
     return;
   }
   const Driver& d = driver();
+  // multicast first: unmap the view, unbind this device's memory, drop the object
+  release_multicast();
   for (int p = 0; p < world_; ++p) {
     if (bases_[p]) {
       d.MemUnmap(reinterpret_cast<CUdeviceptr>(bases_[p]), mapped_);

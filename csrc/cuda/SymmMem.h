@@ -45,7 +45,12 @@ class SymmMem {
  public:
   // Collective over the `world` processes of `kv` (world == 1 allocates locally only).
   // The memory is zeroed before any peer can see it.
-  SymmMem(SymmKind kind, int rank, int world, int device, size_t bytes, KvStore& kv, const std::string& prefix);
+  // `multicast`: additionally bind all ranks' allocations to one NVLink multicast object (NVLS) and
+  // map it, so that `multimem` instructions can reduce over / store to every rank's copy at once.
+  // Needs kVmm and at least two ranks (the driver refuses a one-device object); silently left off
+  // when the device does not report multicast support.
+  SymmMem(SymmKind kind, int rank, int world, int device, size_t bytes, KvStore& kv, const std::string& prefix,
+          bool multicast = false);
   ~SymmMem();
   SymmMem(const SymmMem&) = delete;
   SymmMem& operator=(const SymmMem&) = delete;
@@ -56,16 +61,25 @@ class SymmMem {
   size_t bytes() const { return bytes_; }        // requested size
   size_t mapped_bytes() const { return mapped_; }  // rounded up to the allocation granularity
   SymmKind kind() const { return kind_; }
+  // Multicast mapping of the allocation (same layout; nullptr when not enabled / not supported).
+  void* multicast_base() const { return mc_base_; }
+  static bool multicast_supported(int device);
 
  private:
   void init_ipc(KvStore& kv, const std::string& prefix);
-  void init_vmm(KvStore& kv, const std::string& prefix);
+  void init_vmm(KvStore& kv, const std::string& prefix, bool multicast);
+  void init_multicast(KvStore& kv, const std::string& prefix, size_t gran);
+  void init_multicast_impl(KvStore& kv, const std::string& prefix, size_t gran);
+  void release_multicast();
 
   SymmKind kind_;
   int rank_, world_, device_;
   size_t bytes_ = 0, mapped_ = 0;
   std::vector<void*> bases_;
   std::vector<unsigned long long> handles_;  // kVmm: CUmemGenericAllocationHandle per rank
+  unsigned long long mc_handle_ = 0;         // multicast object (0: none)
+  void* mc_base_ = nullptr;
+  bool mc_bound_ = false;
 };
 
 }  // namespace ccl

@@ -361,6 +361,107 @@ __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(const __grid_con
 }
 
 // ---------------------------------------------------------------------------------------------
+// all_reduce (SUM) through an NVLink multicast object (NVLS). Every rank stages its input in its
+// OWN arena half; rank r then reduces shard r inside the switch - one multimem.ld_reduce reads
+// the same offset of every rank's arena and returns the fp32-accumulated sum - and writes the
+// result into all arenas at once with multimem.st; finally everyone copies the whole result out
+// of its own arena. Each GPU sends S/W bytes up and receives S bytes down instead of moving
+// 2S(W-1)/W through its own load/store units, which is what the two-shot kernel cannot match at
+// large sizes. CTA b of a rank stages sub-slice b of EVERY shard, so that (shard r, slice b) on
+// all ranks is produced by CTAs number b: the per-CTA flag pairing of comm.cuh stays sufficient.
+//
+// EMU (all ranks on one GPU, no multicast object): the two multimem operations are played by
+// loops over the ranks' arenas with the same fp32-accumulate / round-once arithmetic, which
+// checks every index of the kernel on a single GPU.
+// ---------------------------------------------------------------------------------------------
+template <typename T> struct Multimem;
+template <> struct Multimem<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* p) { return ptx::multimem_ld_reduce_add_bf16x2(p); }
+};
+template <> struct Multimem<__half> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* p) { return ptx::multimem_ld_reduce_add_f16x2(p); }
+};
+template <> struct Multimem<float> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* p) { return ptx::multimem_ld_reduce_add_f32(p); }
+};
+
+template <typename T, bool EMU>
+__global__ void __launch_bounds__(512) allreduce_nvls_kernel(const __grid_constant__ Launch<EMU> L) {
+  CCL_GET_CTX
+  using A = typename Acc<T>::type;
+  constexpr int N = Vec<T>::kN;
+  const T* in = reinterpret_cast<const T*>(a.in);
+  T* out = reinterpret_cast<T*>(a.out);
+  const size_t count = a.count;
+  const size_t nvec = ceil_div(count, (size_t)N);
+  const int W = ctx.world, me = ctx.rank;
+  const size_t stride_v = a.chunk_vecs;  // vectors per shard slot
+  const size_t cv = stride_v * W;        // vectors per round
+  const int rounds = (int)ceil_div(nvec, cv);
+
+  bool ok = true;
+  for (int rd = 0; rd < rounds && ok; ++rd) {
+    const size_t base = (size_t)rd * cv;
+    const size_t n = clamp_len(nvec, base, cv);
+    const size_t spr = ceil_div(n, (size_t)W);
+    char* mine = sy.half(me, rd);
+    if (do_work) {
+      for (int s = 0; s < W; ++s) {
+        const Range r = sub_slice(clamp_len(n, (size_t)s * spr, spr));
+        copy_user_to_stage(in, count, base + (size_t)s * spr, mine + (size_t)s * stride_v * 16, r);
+      }
+    }
+    sy.signal_all(0, rd);
+    ok = sy.wait_all(0, rd);
+    if (!ok) break;
+    if (do_work) {
+      const Range r = sub_slice(clamp_len(n, (size_t)me * spr, spr));
+      const size_t off0 = (size_t)sy.parity(rd) * ctx.half_bytes + (size_t)me * stride_v * 16;
+      for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
+        const size_t off = off0 + j * 16;
+        Vec<T> v;
+        if constexpr (EMU) {
+          A acc[N];
+#pragma unroll
+          for (int p = 0; p < kMaxRanks; ++p) {
+            if (p < W) {
+              const Vec<T> x = load_stage<T>(ctx.data[p] + off);
+#pragma unroll
+              for (int t = 0; t < N; ++t) acc[t] = (p == 0) ? to_acc(x.v[t]) : acc[t] + to_acc(x.v[t]);
+            }
+          }
+#pragma unroll
+          for (int t = 0; t < N; ++t) v.v[t] = from_acc<T, A>(acc[t]);
+        } else {
+          *reinterpret_cast<uint4*>(&v) = Multimem<T>::ld_reduce(ctx.mc_data + off);
+        }
+        if (a.has_scale) {
+#pragma unroll
+          for (int t = 0; t < N; ++t) v.v[t] = from_acc<T, A>(static_cast<A>(to_acc(v.v[t]) * static_cast<A>(a.scale)));
+        }
+        if constexpr (EMU) {
+#pragma unroll
+          for (int p = 0; p < kMaxRanks; ++p)
+            if (p < W) store_stage(ctx.data[p] + off, v);
+        } else {
+          ptx::multimem_st_v4(ctx.mc_data + off, *reinterpret_cast<const uint4*>(&v));
+        }
+      }
+    }
+    sy.signal_all(1, rd);
+    ok = sy.wait_all(1, rd);
+    if (!ok) break;
+    if (do_work) {
+      for (int s = 0; s < W; ++s) {
+        const Range r = sub_slice(clamp_len(n, (size_t)s * spr, spr));
+        copy_stage_to_user(mine + (size_t)s * stride_v * 16, out, count, base + (size_t)s * spr, r);
+      }
+    }
+  }
+  sy.finish(rounds);
+}
+
+// ---------------------------------------------------------------------------------------------
 // reduce_scatter: rank p receives piece p of every rank and reduces. Pieces may have different
 // sizes; TOut may be wider than TIn (bf16 gradients reduced and stored as fp32) and the scale
 // (gradient average) is applied in the same pass.
@@ -878,6 +979,14 @@ cudaError_t launch_reduce_scatter(int in_dtype, int out_dtype, const RankCtx* ct
     RS_CASE(kI64, int64_t) RS_CASE(kF16, __half) RS_CASE(kBF16, __nv_bfloat16) RS_CASE(kF32, float)
     RS_CASE(kF64, double)
 #undef RS_CASE
+    default: return cudaErrorInvalidValue;
+  }
+}
+cudaError_t launch_allreduce_nvls(int dtype, const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg) {
+  switch (dtype) {
+    case kBF16: return launch_pair<CollArgs, Launch>(allreduce_nvls_kernel<__nv_bfloat16, false>, allreduce_nvls_kernel<__nv_bfloat16, true>, ctx, args, cfg);
+    case kF16: return launch_pair<CollArgs, Launch>(allreduce_nvls_kernel<__half, false>, allreduce_nvls_kernel<__half, true>, ctx, args, cfg);
+    case kF32: return launch_pair<CollArgs, Launch>(allreduce_nvls_kernel<float, false>, allreduce_nvls_kernel<float, true>, ctx, args, cfg);
     default: return cudaErrorInvalidValue;
   }
 }

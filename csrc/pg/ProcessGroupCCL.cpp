@@ -474,7 +474,7 @@ static c10::intrusive_ptr<Work> allreduce_impl(ProcessGroupCCL& pg, std::vector<
             fill_reduce(a, specs[i], t.scalar_type());
             ccl::AlgoChoice ch{};
             C10_CUDA_CHECK(c.allreduce(ccl_py::to_ccl_dtype(t.scalar_type()), {a}, s, &ch));
-            tag = ch.algo == ccl::Algo::kOneShot ? "oneshot" : "twoshot";
+            tag = ch.algo == ccl::Algo::kOneShot ? "oneshot" : (ch.algo == ccl::Algo::kNvls ? "nvls" : "twoshot");
           }
           return tag;
         }, ts, ts, {}, false, bytes);

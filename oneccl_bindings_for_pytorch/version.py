@@ -1,2 +1,2 @@
 __version__ = "2.8.0+b200"
-git_version = "3d0cdeceb6f67ae9d14cff0ef9a8b959bc8ab19b"
+git_version = "17dd01a0b1a5546746e5196e1404f65ca4efa7cb"

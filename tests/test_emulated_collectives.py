@@ -435,3 +435,42 @@ def test_moe_dispatch_combine(comms, world, epr):
             scaled = torch.stack([(xs[r].float() * (1.0 + le[:, k:k + 1])).to(torch.bfloat16).float() for k in range(K)], 1)
             ref = (scaled * gate[r][:, :, None]).sum(1)
             torch.testing.assert_close(outs[r].cpu().float(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("n", [1, 1000, 65537])
+def test_allreduce_switch_reduction_emulated(comms, world, dtype, n):
+    """The multicast (NVLS) all_reduce kernel with its two multimem operations played in software:
+    checks staging layout, shard ownership, flag pairing and copy-out for every world size."""
+    c = comms(world)
+    xs = [rand(n, dtype, 300 + r) for r in range(world)]
+    ins = [x.cuda() for x in xs]
+    outs = [torch.empty_like(t) for t in ins]
+    for _ in range(3):
+        tag = c.allreduce(ins, outs, SUM, 1.0, 0, 3)
+    torch.cuda.synchronize()
+    assert tag.startswith("nvls") and c.status()[0] == 0
+    ref = oracle_reduce(xs, SUM, dtype)
+    for o in outs:
+        close(o, ref, dtype, world)
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0]), "ranks must agree bitwise"
+
+
+def test_allreduce_switch_reduction_multi_round_scale_and_fallback(comms):
+    world = 4
+    c = comms(world, 1 << 20)
+    n = (3 << 20) // 4 + 13  # 3 MB through 1 MB halves: several rounds
+    xs = [rand(n, torch.float32, r) for r in range(world)]
+    ins = [x.cuda() for x in xs]
+    tag = c.allreduce(ins, ins, SUM, 1.0 / world, 1, 3)  # in place, averaged
+    torch.cuda.synchronize()
+    assert tag.startswith("nvls")
+    ref = oracle_reduce(xs, SUM, torch.float32) / world
+    for o in ins:
+        close(o, ref, torch.float32, world)
+    # the switch only adds: MAX falls back to the peer-memory kernels
+    ys = [rand(1000, torch.float32, 50 + r).cuda() for r in range(world)]
+    tag = c.allreduce(ys, ys, MAX, 1.0, 0, 3)
+    assert not tag.startswith("nvls")

@@ -83,3 +83,63 @@ def test_tune_file_and_vmm_arena_applied(tmp_path):
     p.write_text("%d oneshot_max_bytes=%d threads=256 max_blocks=32\n" % (world, 12345 * 16))
     run_ranks(_tuned, world=world, device="cuda", args=(str(p),),
               env={"CCL_TUNE_FILE": str(p), "CCL_MAX_BLOCKS": "64", "CCL_SYMM_MEM": "vmm"})
+
+
+def _nvls(rank, world):
+    import torch.distributed as dist
+    import torch_ccl_b200
+
+    be = dist.distributed_c10d._get_default_group()._get_backend(torch.device("cuda"))
+    ok = True
+    try:
+        x = torch.ones(8, device="cuda")
+        dist.all_reduce(x)  # creates the communicator (vmm arenas + multicast object)
+        cfg = be.cuda_comm_config(x)
+        assert cfg["symm_mem"] == "vmm" and cfg["nvls"]
+        if not cfg["nvls_available"]:
+            return  # no multicast support on this device: the plain kernels serve, nothing to check
+        for dtype, n in [(torch.bfloat16, (4 << 20) + 24), (torch.float16, 3 << 20), (torch.float32, (2 << 20) + 1)]:
+            t = ((torch.arange(n, device="cuda") % 13) + rank).to(dtype)
+            dist.all_reduce(t)
+            want = ((torch.arange(n, device="cuda") % 13) * world + world * (world - 1) // 2).to(dtype)
+            assert torch.equal(t, want), (dtype, n, (t != want).sum().item())
+        t = torch.full((4 << 20,), float(rank + 1), device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.AVG)
+        assert torch.allclose(t, torch.full_like(t, (world + 1) / 2))
+        torch.cuda.synchronize()
+        assert "nvls" in torch_ccl_b200.flight_recorder()
+    except BaseException:
+        ok = False
+        raise
+    finally:
+        # leave together and in order: nobody exits while a peer's memory is still bound
+        torch.cuda.synchronize()
+        store = dist.distributed_c10d._get_default_store()
+        store.add("nvls_done", 1)
+        import time
+
+        t0 = time.time()
+        while int(store.add("nvls_done", 0)) < world and time.time() - t0 < 20:
+            time.sleep(0.01)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_switch_reduction_all_reduce():
+    """CCL_NVLS=1: large SUM all_reduces go through the NVLink multicast object (multimem.ld_reduce
+    + multimem.st); exact integer-valued inputs, so the result is compared bit for bit."""
+    run_ranks(_nvls, world=min(torch.cuda.device_count(), 8), device="cuda", env={"CCL_NVLS": "1", "CCL_ARENA_MB": "64"})
+
+
+@pytest.mark.gpu
+def test_single_rank_never_builds_a_multicast_object():
+    import torch_ccl_b200._C as C
+
+    torch.cuda.set_device(0)
+    c = C.CudaComm.create(None, 0, 1, 8 << 20, 2000, "t/mc1", "vmm", True)
+    assert not c.nvls_available
+    x = torch.randn(1000, device="cuda")
+    out = torch.zeros_like(x)
+    assert not c.allreduce([x], [out], 0, 1.0, 0, 3).startswith("nvls")
+    torch.cuda.synchronize()
+    assert torch.equal(out, x)

@@ -197,3 +197,38 @@ class FullyShardedSequential:
             u.sync_shard()
         # the next forward's gathers (communication stream) must see the updated shards
         self.comm_stream.wait_stream(torch.cuda.current_stream(self.units[0].device))
+
+    # -- checkpoints ------------------------------------------------------------------------------
+    def sharded_state_dict(self):
+        """This rank's part of a checkpoint: the fp32 master shard of every unit (CPU tensors).
+
+        Every rank saves its own file; no communication. Reload with `load_sharded_state_dict` on
+        the same world size. (The reference only shows `model.state_dict()` + `torch.save` after a
+        barrier in its FSDP example, tests/test_fsdp.py:172-178.)"""
+        w, r = self.units[0].world, self.units[0].rank
+        return {"world": w, "rank": r,
+                "units": [{"numel": u.total, "padded": u.padded, "master": u.master.detach().cpu().clone()} for u in self.units]}
+
+    def load_sharded_state_dict(self, sd):
+        w, r = self.units[0].world, self.units[0].rank
+        if sd["world"] != w or sd["rank"] != r or len(sd["units"]) != len(self.units):
+            raise ValueError("sharded checkpoint of rank %d/%d with %d units does not fit rank %d/%d with %d units"
+                             % (sd["rank"], sd["world"], len(sd["units"]), r, w, len(self.units)))
+        for u, e in zip(self.units, sd["units"]):
+            if e["numel"] != u.total or e["padded"] != u.padded:
+                raise ValueError("sharded checkpoint: unit size mismatch")
+            u.master.copy_(e["master"])
+            u.sync_shard()
+        self.comm_stream.wait_stream(torch.cuda.current_stream(self.units[0].device))
+
+    def full_state_dict(self, dst=0):
+        """Consolidated fp32 parameters {"<unit>.<name>": tensor} on rank `dst` (None elsewhere):
+        one all_gather of the master shards per unit through torch.distributed."""
+        out = {} if self.units[0].rank == dst else None
+        for i, u in enumerate(self.units):
+            full = torch.empty(u.padded, device=u.device, dtype=torch.float32)
+            dist.all_gather_into_tensor(full, u.master, group=self.group)
+            if out is not None:
+                for (name, _), (o, n, shape) in zip(u.module.named_parameters(), u.meta):
+                    out["%d.%s" % (i, name)] = full[o:o + n].view(shape).cpu()
+        return out
