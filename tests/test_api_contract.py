@@ -214,3 +214,29 @@ def _p2p_patterns(rank, world):
 
 def test_p2p_relay_ring_ulysses_world3():
     run_ranks(_p2p_patterns, world=3)
+
+
+def _profiler_ranges(rank, world):
+    """Both levels of profiler ranges keep the reference's names (src/ProcessGroupCCL.cpp:995-1198
+    `oneccl_bindings_for_pytorch::<op>` with the tensors as inputs, src/cpu/cpu_ccl.cpp:568,605
+    `oneccl_bindings_for_pytorch::cpu::<op>`), so profiler scripts written against it keep working."""
+    t = torch.ones(4, 4)
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU], record_shapes=True) as prof:
+        dist.all_reduce(t)
+        dist.broadcast(t, 0)
+        outs = [torch.empty(4, 4) for _ in range(world)]
+        dist.all_gather(outs, t)
+        dist.barrier()
+    keys = {e.key: e for e in prof.key_averages(group_by_input_shape=True)}
+    names = {k for k in (e.key for e in prof.key_averages())}
+    for op in ("allreduce", "broadcast", "allgather", "barrier"):
+        assert "oneccl_bindings_for_pytorch::" + op in names, sorted(names)
+    for op in ("allreduce", "broadcast", "allgather"):
+        assert "oneccl_bindings_for_pytorch::cpu::" + op in names, sorted(names)
+    shaped = [e for e in prof.key_averages(group_by_input_shape=True) if e.key == "oneccl_bindings_for_pytorch::allreduce"]
+    assert shaped and any([4, 4] in e.input_shapes for e in shaped), [e.input_shapes for e in shaped]
+    del keys
+
+
+def test_profiler_ranges_world2():
+    run_ranks(_profiler_ranges, world=2)
