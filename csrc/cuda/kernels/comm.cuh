@@ -32,6 +32,39 @@ __device__ __forceinline__ uint32_t* flag_ptr(uint32_t* base, int phase, int src
   return base + ((size_t)phase * kMaxRanks + src) * kMaxBlocks + blk;
 }
 
+// Checked staging accesses (build with -DCCL_DEBUG_BOUNDS=1; compute-sanitizer's stand-in for
+// the one class of bug it would catch here, a staging offset outside the arenas). Every
+// load_stage / store_stage first checks that its 16 bytes lie inside the data halves or the
+// low-latency region of SOME rank's arena of the communicator the CTA works on. A bad access is
+// not performed: the first one is recorded in the host-visible status word as
+// {kStatusBounds, rank, low 31 bits of the address >> 4, is_store} and the load returns zeros.
+// The communicator then reports the error like an expired wait. Costs a few instructions per
+// access, so it is a separate build.
+#if defined(CCL_DEBUG_BOUNDS) && CCL_DEBUG_BOUNDS
+#define CCL_BOUNDS_CHECKED 1
+static __shared__ const RankCtx* s_dbg_ctx;
+__device__ __forceinline__ void dbg_bounds_bind(const RankCtx* c) { s_dbg_ctx = c; }  // one thread, before a barrier
+__device__ __forceinline__ bool dbg_in_bounds(const void* ptr, int is_store) {
+  const RankCtx* c = s_dbg_ctx;
+  if (!c) return true;
+  const char* p = static_cast<const char*>(ptr);
+  bool ok = false;
+  for (int r = 0; r < c->world; ++r) {
+    ok = ok || (p >= c->data[r] && p + 16 <= c->data[r] + 2 * c->half_bytes);
+    ok = ok || (c->ll[r] && p >= c->ll[r] && p + 16 <= c->ll[r] + kLLBytes);
+  }
+  if (!ok && c->status && atomicCAS(c->status, kStatusOk, kStatusBounds) == kStatusOk) {
+    c->status[1] = c->rank;
+    c->status[2] = (int)((reinterpret_cast<uintptr_t>(ptr) >> 4) & 0x7fffffff);
+    c->status[3] = is_store;
+    __threadfence_system();
+  }
+  return ok;
+}
+#else
+#define CCL_BOUNDS_CHECKED 0
+#endif
+
 // Per-CTA protocol helper.
 struct Sync {
   const RankCtx& ctx;
@@ -46,7 +79,12 @@ struct Sync {
     // kernels before this one (they produced the input and advanced the epoch)
     ptx::griddep_launch_dependents();
     ptx::griddep_wait();
-    if (threadIdx.x == 0) *failed = 0;
+    if (threadIdx.x == 0) {
+      *failed = 0;
+#if CCL_BOUNDS_CHECKED
+      dbg_bounds_bind(&ctx);
+#endif
+    }
     epoch = ctx.state ? *reinterpret_cast<volatile uint32_t*>(ctx.state) : 0u;
     __syncthreads();
   }
@@ -202,11 +240,20 @@ __device__ __forceinline__ void store_vec(T* base, size_t i, size_t count, bool 
 template <typename T>
 __device__ __forceinline__ Vec<T> load_stage(const void* p) {
   Vec<T> r;
+#if CCL_BOUNDS_CHECKED
+  if (!dbg_in_bounds(p, 0)) {
+    *reinterpret_cast<uint4*>(&r) = make_uint4(0, 0, 0, 0);
+    return r;
+  }
+#endif
   *reinterpret_cast<uint4*>(&r) = ptx::ld_relaxed_sys_v4(p);
   return r;
 }
 template <typename T>
 __device__ __forceinline__ void store_stage(void* p, const Vec<T>& r) {
+#if CCL_BOUNDS_CHECKED
+  if (!dbg_in_bounds(p, 1)) return;
+#endif
   ptx::st_v4(p, *reinterpret_cast<const uint4*>(&r));
 }
 

@@ -24,6 +24,37 @@ def test_probe_builds_for_sm100a():
     assert os.access(BIN, os.X_OK)
 
 
+BOUNDS = os.path.join(HERE, "bounds_probe")
+
+
+def _build_bounds():
+    src = os.path.join(HERE, "bounds_probe.cu")
+    root = os.path.dirname(os.path.dirname(HERE))
+    hdr = os.path.join(root, "csrc", "cuda", "kernels", "comm.cuh")
+    if os.path.exists(BOUNDS) and os.path.getmtime(BOUNDS) >= max(os.path.getmtime(src), os.path.getmtime(hdr)):
+        return
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "--expt-relaxed-constexpr", "-DCCL_DEBUG_BOUNDS=1",
+                    "-I" + os.path.join(root, "csrc"), "-I" + os.path.join(root, "csrc", "cuda", "kernels"), "-o", BOUNDS, src], check=True)
+
+
+def test_checked_accessor_build_compiles():
+    """The CCL_DEBUG_BOUNDS variant of the staging accessors builds for sm_100a (probe + the collective kernels)."""
+    _build_bounds()
+    root = os.path.dirname(os.path.dirname(HERE))
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "--expt-relaxed-constexpr", "-O1", "-DCCL_DEBUG_BOUNDS=1",
+                    "-I" + os.path.join(root, "csrc"), "-I" + os.path.join(root, "csrc", "cuda", "kernels"), "-c",
+                    os.path.join(root, "csrc", "cuda", "kernels", "moe_a2a.cu"), "-o", os.devnull], check=True)
+
+
+@pytest.mark.gpu
+def test_checked_accessors_skip_and_record_out_of_bounds():
+    _build_bounds()
+    r = subprocess.run([BOUNDS], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "PASS" in r.stdout, r.stdout + r.stderr
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("mode", ["ipc", "pingpong"])
 def test_probe_runs(mode):
