@@ -240,3 +240,19 @@ def _profiler_ranges(rank, world):
 
 def test_profiler_ranges_world2():
     run_ranks(_profiler_ranges, world=2)
+
+
+def test_bench_reference_arm_reports_unavailable():
+    """`bench.py --impl reference` must answer on any machine: the reference (a binding over Intel oneCCL + SYCL for
+    Intel GPUs) cannot be installed here, so the arm prints one JSON line saying so and exits 0."""
+    import json
+    import subprocess
+    import sys
+
+    from mp_util import ROOT
+
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "3"],
+                       capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and isinstance(line.get("unavailable"), str) and line["unavailable"]
