@@ -125,8 +125,18 @@ struct PyComm {
   }
 
   // ins[r]: list of `world` pieces (piece p goes to rank p); outs[r]: rank r's reduced piece
+  struct ForceNvls {  // scoped override used by the tests of the switch-reduction kernels
+    CudaComm* c;
+    ccl::Algo saved;
+    ForceNvls(CudaComm* comm, bool on) : c(comm), saved(comm->config().algo) {
+      if (on) c->mutable_config().algo = ccl::Algo::kNvls;
+    }
+    ~ForceNvls() { c->mutable_config().algo = saved; }
+  };
+
   void reduce_scatter(std::vector<std::vector<at::Tensor>> ins, std::vector<at::Tensor> outs, int op,
-                      double scale, int has_scale) {
+                      double scale, int has_scale, bool nvls) {
+    ForceNvls force(comm.get(), nvls);
     check_n(ins.size());
     std::vector<CollArgs> args(ins.size());
     const int W = comm->world();
@@ -145,7 +155,8 @@ struct PyComm {
        "reduce_scatter");
   }
 
-  void all_gather(std::vector<at::Tensor> ins, std::vector<std::vector<at::Tensor>> outs) {
+  void all_gather(std::vector<at::Tensor> ins, std::vector<std::vector<at::Tensor>> outs, bool nvls) {
+    ForceNvls force(comm.get(), nvls);
     check_n(ins.size());
     std::vector<CollArgs> args(ins.size());
     const int W = comm->world();
@@ -413,8 +424,9 @@ void bind_cuda_comm(py::module& m) {
            py::arg("scale") = 1.0, py::arg("has_scale") = 0, py::arg("algo") = 0)
       .def("reduce", &PyComm::reduce)
       .def("reduce_scatter", &PyComm::reduce_scatter, py::arg("ins"), py::arg("outs"), py::arg("op") = 0,
-           py::arg("scale") = 1.0, py::arg("has_scale") = 0)
-      .def("all_gather", &PyComm::all_gather)
+           py::arg("scale") = 1.0, py::arg("has_scale") = 0, py::arg("nvls") = false)
+      .def("all_gather", &PyComm::all_gather, py::arg("ins"), py::arg("outs"), py::arg("nvls") = false)
+      .def_property_readonly("last_used_nvls", [](PyComm& c) { return c.comm->last_used_nvls(); })
       .def("all_to_all", &PyComm::all_to_all, py::arg("ins"), py::arg("outs"), py::arg("uneven") = false)
       .def("broadcast", &PyComm::broadcast)
       .def("gather", &PyComm::gather)

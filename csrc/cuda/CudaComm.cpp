@@ -284,6 +284,18 @@ cudaError_t CudaComm::reduce_scatter(int in_dtype, int out_dtype, std::vector<Co
     a.ablate = cfg_.ablate;
   }
   LaunchCfg lc = launch_cfg(blocks_for(std::min(maxv, stride), cfg_.max_blocks), threads_for(std::min(maxv, stride), blocks_for(std::min(maxv, stride), cfg_.max_blocks), cfg_.threads), stream);
+  // in-switch reduction: SUM of bf16 / f16 / f32 into the same dtype (the switch returns the sum rounded to the
+  // input type, so the widened bf16 -> fp32 gradient path stays on the peer-load kernel, which keeps fp32)
+  const bool nvls_ok = (emulated_ ? world_ > 1 : nvls_available()) && args[0].op == kSum && in_dtype == out_dtype &&
+                       (in_dtype == kBF16 || in_dtype == kF16 || in_dtype == kF32);
+  const bool use_nvls = nvls_ok && (cfg_.algo == Algo::kNvls || (!emulated_ && cfg_.nvls && cfg_.algo == Algo::kAuto &&
+                                                                  maxv * 16 * world_ >= cfg_.nvls_min_bytes));
+  last_algo_ = use_nvls ? Algo::kNvls : Algo::kTwoShot;
+  if (use_nvls) {
+    cudaError_t en = launch_reduce_scatter_nvls(in_dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+    if (en == cudaSuccess) ++launches_;
+    return en;
+  }
   cudaError_t e = launch_reduce_scatter(in_dtype, out_dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
   if (e == cudaSuccess) ++launches_;
   return e;
@@ -296,7 +308,11 @@ cudaError_t CudaComm::all_gather(std::vector<CollArgs> args, cudaStream_t stream
   for (auto& a : args)
     for (int p = 0; p < world_; ++p) maxb = std::max(maxb, (size_t)a.out_cnt[p]);
   const size_t maxv = (maxb + 15) / 16;
-  const int mode = (maxb <= cfg_.ag_push_max_bytes) ? 1 : 0;
+  const bool nvls_ok = emulated_ ? world_ > 1 : nvls_available();
+  const bool use_nvls = nvls_ok && (cfg_.algo == Algo::kNvls || (!emulated_ && cfg_.nvls && cfg_.algo == Algo::kAuto &&
+                                                                  maxb * world_ >= cfg_.nvls_min_bytes));
+  last_algo_ = use_nvls ? Algo::kNvls : Algo::kTwoShot;
+  const int mode = (use_nvls || maxb <= cfg_.ag_push_max_bytes) ? 1 : 0;  // NVLS uses the push layout: one slot per source
   size_t stride = mode == 1 ? cfg_.half_bytes / (16 * (size_t)world_) : cfg_.half_bytes / 16;
   stride = compact_stride(stride / 8 * 8, maxv);
   const int rounds = (int)((maxv + stride - 1) / stride);
@@ -307,7 +323,8 @@ cudaError_t CudaComm::all_gather(std::vector<CollArgs> args, cudaStream_t stream
     a.ablate = cfg_.ablate;
   }
   LaunchCfg lc = launch_cfg(blocks_for(std::min(maxv, stride), cfg_.max_blocks), threads_for(std::min(maxv, stride), blocks_for(std::min(maxv, stride), cfg_.max_blocks), cfg_.threads), stream);
-  cudaError_t e = launch_all_gather(emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  cudaError_t e = use_nvls ? launch_all_gather_nvls(emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc)
+                           : launch_all_gather(emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
   if (e == cudaSuccess) ++launches_;
   return e;
 }

@@ -110,6 +110,8 @@ class CudaComm {
   size_t fused_norm_capacity() const { return cfg_.half_bytes / world_; }
 
   uint64_t launches() const { return launches_; }
+  // Whether the last reduce_scatter / all_gather went through the multicast object.
+  bool last_used_nvls() const { return last_algo_ == Algo::kNvls; }
 
  private:
   void init_tables();
@@ -133,6 +135,7 @@ class CudaComm {
   int* status_host_ = nullptr;        // pinned + mapped
   int* status_dev_ = nullptr;
   uint64_t launches_ = 0;
+  Algo last_algo_ = Algo::kAuto;
 };
 
 }  // namespace ccl

@@ -462,6 +462,118 @@ __global__ void __launch_bounds__(512) allreduce_nvls_kernel(const __grid_consta
 }
 
 // ---------------------------------------------------------------------------------------------
+// reduce_scatter (SUM) and all_gather through the multicast object; same staging layout, flag
+// pairing and software emulation as allreduce_nvls_kernel.
+//  * reduce_scatter: every rank stages all its W pieces in its own arena (piece s in slot s),
+//    then reduces slot `me` inside the switch straight into its output.
+//  * all_gather: every rank writes its piece into slot `me` of ALL arenas with one multimem.st
+//    per vector (the piece leaves the GPU once instead of W-1 times), then copies the other
+//    slots out of its own arena.
+// ---------------------------------------------------------------------------------------------
+template <typename T, bool EMU>
+__global__ void __launch_bounds__(512) reduce_scatter_nvls_kernel(const __grid_constant__ Launch<EMU> L) {
+  CCL_GET_CTX
+  using A = typename Acc<T>::type;
+  constexpr int N = Vec<T>::kN;
+  const int W = ctx.world, me = ctx.rank;
+  const size_t stride_v = a.chunk_vecs;
+  const int rounds = a.rounds;
+  T* out = reinterpret_cast<T*>(a.out);
+  const size_t mycount = a.in_cnt[me];
+  const bool al_out = is_aligned16(out);
+
+  bool ok = true;
+  for (int rd = 0; rd < rounds && ok; ++rd) {
+    const size_t vb = (size_t)rd * stride_v;
+    char* mine = sy.half(me, rd);
+    if (do_work) {
+      for (int s = 0; s < W; ++s) {
+        const size_t cnt = a.in_cnt[s];
+        const Range r = sub_slice(clamp_len(ceil_div(cnt, (size_t)N), vb, stride_v));
+        copy_user_to_stage(reinterpret_cast<const T*>(a.in_piece[s]), cnt, vb, mine + (size_t)s * stride_v * 16, r);
+      }
+    }
+    sy.signal_all(0, rd);
+    ok = sy.wait_all(0, rd);
+    if (!ok) break;
+    if (do_work) {
+      const Range r = sub_slice(clamp_len(ceil_div(mycount, (size_t)N), vb, stride_v));
+      const size_t off0 = (size_t)sy.parity(rd) * ctx.half_bytes + (size_t)me * stride_v * 16;
+      for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
+        const size_t off = off0 + j * 16;
+        Vec<T> v;
+        if constexpr (EMU) {
+          A acc[N];
+#pragma unroll
+          for (int p = 0; p < kMaxRanks; ++p) {
+            if (p < W) {
+              const Vec<T> x = load_stage<T>(ctx.data[p] + off);
+#pragma unroll
+              for (int t = 0; t < N; ++t) acc[t] = (p == 0) ? to_acc(x.v[t]) : acc[t] + to_acc(x.v[t]);
+            }
+          }
+#pragma unroll
+          for (int t = 0; t < N; ++t) v.v[t] = from_acc<T, A>(acc[t]);
+        } else {
+          *reinterpret_cast<uint4*>(&v) = Multimem<T>::ld_reduce(ctx.mc_data + off);
+        }
+        if (a.has_scale) {
+#pragma unroll
+          for (int t = 0; t < N; ++t) v.v[t] = from_acc<T, A>(static_cast<A>(to_acc(v.v[t]) * static_cast<A>(a.scale)));
+        }
+        store_vec(out, vb + j, mycount, al_out, v);
+      }
+    }
+  }
+  sy.finish(rounds);
+}
+
+template <bool EMU>
+__global__ void __launch_bounds__(512) all_gather_nvls_kernel(const __grid_constant__ Launch<EMU> L) {
+  CCL_GET_CTX
+  using T = uint8_t;
+  const int W = ctx.world, me = ctx.rank;
+  const size_t stride_v = a.chunk_vecs;
+  const int rounds = a.rounds;
+  const T* in = reinterpret_cast<const T*>(a.in);
+  const size_t mybytes = a.out_cnt[me];
+  const bool al_in = is_aligned16(in);
+
+  bool ok = true;
+  for (int rd = 0; rd < rounds && ok; ++rd) {
+    const size_t vb = (size_t)rd * stride_v;
+    if (do_work) {
+      const Range r = sub_slice(clamp_len(ceil_div(mybytes, (size_t)16), vb, stride_v));
+      const size_t off0 = (size_t)sy.parity(rd) * ctx.half_bytes + (size_t)me * stride_v * 16;
+      for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
+        const Vec<T> v = load_vec(in, vb + j, mybytes, al_in);
+        if constexpr (EMU) {
+#pragma unroll
+          for (int p = 0; p < kMaxRanks; ++p)
+            if (p < W) store_stage(ctx.data[p] + off0 + j * 16, v);
+        } else {
+          ptx::multimem_st_v4(ctx.mc_data + off0 + j * 16, *reinterpret_cast<const uint4*>(&v));
+        }
+      }
+      copy_user_to_user(in, reinterpret_cast<T*>(a.out_piece[me]), mybytes, vb, r);
+    }
+    sy.signal_all(0, rd);
+    ok = sy.wait_all(0, rd);
+    if (!ok) break;
+    if (do_work) {
+      const char* mine = sy.half(me, rd);
+      for (int q = 1; q < W; ++q) {
+        const int p = (me + q) % W;
+        const size_t cnt = a.out_cnt[p];
+        const Range r = sub_slice(clamp_len(ceil_div(cnt, (size_t)16), vb, stride_v));
+        copy_stage_to_user(mine + (size_t)p * stride_v * 16, reinterpret_cast<T*>(a.out_piece[p]), cnt, vb, r);
+      }
+    }
+  }
+  sy.finish(rounds);
+}
+
+// ---------------------------------------------------------------------------------------------
 // reduce_scatter: rank p receives piece p of every rank and reduces. Pieces may have different
 // sizes; TOut may be wider than TIn (bf16 gradients reduced and stored as fp32) and the scale
 // (gradient average) is applied in the same pass.
@@ -989,6 +1101,17 @@ cudaError_t launch_allreduce_nvls(int dtype, const RankCtx* ctx, const CollArgs*
     case kF32: return launch_pair<CollArgs, Launch>(allreduce_nvls_kernel<float, false>, allreduce_nvls_kernel<float, true>, ctx, args, cfg);
     default: return cudaErrorInvalidValue;
   }
+}
+cudaError_t launch_reduce_scatter_nvls(int dtype, const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg) {
+  switch (dtype) {
+    case kBF16: return launch_pair<CollArgs, Launch>(reduce_scatter_nvls_kernel<__nv_bfloat16, false>, reduce_scatter_nvls_kernel<__nv_bfloat16, true>, ctx, args, cfg);
+    case kF16: return launch_pair<CollArgs, Launch>(reduce_scatter_nvls_kernel<__half, false>, reduce_scatter_nvls_kernel<__half, true>, ctx, args, cfg);
+    case kF32: return launch_pair<CollArgs, Launch>(reduce_scatter_nvls_kernel<float, false>, reduce_scatter_nvls_kernel<float, true>, ctx, args, cfg);
+    default: return cudaErrorInvalidValue;
+  }
+}
+cudaError_t launch_all_gather_nvls(const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg) {
+  return launch_pair<CollArgs, Launch>(all_gather_nvls_kernel<false>, all_gather_nvls_kernel<true>, ctx, args, cfg);
 }
 cudaError_t launch_all_gather(const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg) {
   return launch_pair<CollArgs, Launch>(all_gather_kernel<false>, all_gather_kernel<true>, ctx, args, cfg);

@@ -59,6 +59,8 @@ cudaError_t launch_allreduce_oneshot(int dtype, const RankCtx* ctx, const CollAr
 cudaError_t launch_allreduce_twoshot(int dtype, const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg);
 // SUM of bf16 / f16 / f32 through the NVLink multicast mapping (RankCtx::mc_data; emulation plays it in software).
 cudaError_t launch_allreduce_nvls(int dtype, const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg);
+cudaError_t launch_reduce_scatter_nvls(int dtype, const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg);  // in dtype == out dtype
+cudaError_t launch_all_gather_nvls(const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg);
 // out dtype may differ from in dtype only for (bf16|f16) -> f32 (fused FSDP gradient cast).
 cudaError_t launch_reduce_scatter(int in_dtype, int out_dtype, const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg);
 cudaError_t launch_all_gather(const RankCtx* ctx, const CollArgs* args, const LaunchCfg& cfg);

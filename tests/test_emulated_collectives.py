@@ -474,3 +474,40 @@ def test_allreduce_switch_reduction_multi_round_scale_and_fallback(comms):
     ys = [rand(1000, torch.float32, 50 + r).cuda() for r in range(world)]
     tag = c.allreduce(ys, ys, MAX, 1.0, 0, 3)
     assert not tag.startswith("nvls")
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_reduce_scatter_switch_reduction_emulated(comms, world, dtype):
+    c = comms(world)
+    cnt = [1000 + 37 * p for p in range(world)]  # uneven pieces
+    xs = [[rand(cnt[p], dtype, 10 * r + p) for p in range(world)] for r in range(world)]
+    ins = [[t.cuda() for t in row] for row in xs]
+    outs = [torch.empty(cnt[r], dtype=dtype, device="cuda") for r in range(world)]
+    for _ in range(2):
+        c.reduce_scatter(ins, outs, SUM, 1.0, 0, True)
+    torch.cuda.synchronize()
+    assert c.last_used_nvls and c.status()[0] == 0
+    for r in range(world):
+        close(outs[r], oracle_reduce([xs[q][r] for q in range(world)], SUM, dtype), dtype, world)
+    # the widened gradient path (bf16 in, fp32 out) keeps the peer-load kernel
+    if dtype == torch.bfloat16:
+        wide = [torch.empty(cnt[r], dtype=torch.float32, device="cuda") for r in range(world)]
+        c.reduce_scatter(ins, wide, SUM, 1.0, 0, True)
+        assert not c.last_used_nvls
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_all_gather_switch_multicast_emulated(comms, world):
+    c = comms(world, 1 << 20)
+    cnt = [70001 + 13 * p for p in range(world)]  # uneven, several rounds through 1 MB halves at world 8
+    xs = [rand(cnt[r], torch.float32, 77 + r) for r in range(world)]
+    ins = [x.cuda() for x in xs]
+    outs = [[torch.empty(cnt[p], device="cuda") for p in range(world)] for _ in range(world)]
+    for _ in range(2):
+        c.all_gather(ins, outs, True)
+    torch.cuda.synchronize()
+    assert c.last_used_nvls and c.status()[0] == 0
+    for r in range(world):
+        for p in range(world):
+            assert torch.equal(outs[r][p].cpu(), xs[p])

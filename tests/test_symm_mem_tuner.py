@@ -103,6 +103,16 @@ def _nvls(rank, world):
             dist.all_reduce(t)
             want = ((torch.arange(n, device="cuda") % 13) * world + world * (world - 1) // 2).to(dtype)
             assert torch.equal(t, want), (dtype, n, (t != want).sum().item())
+        # reduce_scatter and all_gather through the same object (sizes above the 4 MB switch-over)
+        n = 3 << 20
+        full = ((torch.arange(n * world, device="cuda") % 11) + rank).to(torch.bfloat16)
+        part = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+        dist.reduce_scatter_tensor(part, full)
+        want = ((torch.arange(n * world, device="cuda") % 11) * world + world * (world - 1) // 2).to(torch.bfloat16)
+        assert torch.equal(part, want[rank * n:(rank + 1) * n])
+        gathered = torch.empty(n * world, device="cuda", dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(gathered, part)
+        assert torch.equal(gathered, want)
         t = torch.full((4 << 20,), float(rank + 1), device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.AVG)
         assert torch.allclose(t, torch.full_like(t, (world + 1) / 2))
