@@ -1,3 +1,8 @@
+// The element loops of this file want the vectoriser at full strength whatever the build's
+// global level is (the rest of the host code stays at -O2).
+#if defined(__GNUC__) && !defined(__clang__)
+#pragma GCC optimize("O3")
+#endif
 #include "cpu/CpuCollectives.h"
 
 #include <c10/util/BFloat16.h>

@@ -53,7 +53,7 @@ sources = sorted(
 )
 sources = [s for s in sources if "/standalone/" not in s]
 debug = os.environ.get("DEBUG", "0") == "1"
-cxx_flags = ["-std=c++17", "-O0" if debug else "-O3", "-g" if debug else "-g0", "-fvisibility=hidden",
+cxx_flags = ["-std=c++17", "-O0" if debug else "-O2", "-g" if debug else "-g0", "-fvisibility=hidden",
              "-Wno-deprecated-declarations", "-fstack-protector", "-Wformat-security"]
 nvcc_flags = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fvisibility=hidden"]
