@@ -133,6 +133,17 @@ void ProcessGroupCCL::AsyncWorkCCL::finishOk() {
     if (future_ && !future_->completed()) completeFutureNow();
   }
   finish();
+  finished_.store(true, std::memory_order_release);
+}
+
+bool ProcessGroupCCL::AsyncWorkCCL::wait(std::chrono::milliseconds timeout) {
+  const auto t0 = std::chrono::steady_clock::now();
+  while (!finished_.load(std::memory_order_acquire) && std::chrono::steady_clock::now() - t0 < std::chrono::microseconds(60)) {
+#if defined(__x86_64__)
+    __builtin_ia32_pause();
+#endif
+  }
+  return Work::wait(timeout);
 }
 
 void ProcessGroupCCL::AsyncWorkCCL::finishError(std::exception_ptr e) {
@@ -142,6 +153,7 @@ void ProcessGroupCCL::AsyncWorkCCL::finishError(std::exception_ptr e) {
     if (future_ && !future_->completed()) future_->setError(e);
   }
   finish(e);
+  finished_.store(true, std::memory_order_release);
 }
 
 void ProcessGroupCCL::AsyncWorkCCL::abort() { aborted_.store(true); }

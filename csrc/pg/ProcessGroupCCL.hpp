@@ -50,6 +50,9 @@ class ProcessGroupCCL : public Backend {
     float getDuration() const override { return duration_ms_; }
     void abort() override;
     bool isAborted() const { return aborted_.load(); }
+    // Polls for completion for a few tens of microseconds before blocking on the condition
+    // variable: a small CPU collective finishes sooner than a sleeping thread wakes up.
+    bool wait(std::chrono::milliseconds timeout = kNoTimeout) override;
 
     // Output tensors: a flat list or (gather-type ops) a list of lists.
     void setOutputs(std::vector<at::Tensor> outs);
@@ -73,6 +76,7 @@ class ProcessGroupCCL : public Backend {
     uint64_t seq_;
     float duration_ms_ = -1.f;
     std::atomic<bool> aborted_{false};
+    std::atomic<bool> finished_{false};
   };
 
   struct Options : Backend::Options {
