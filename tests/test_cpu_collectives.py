@@ -160,3 +160,32 @@ def _dtype_matrix(rank, world):
 
 def test_cpu_dtypes_and_large_world3():
     run_ranks(_dtype_matrix, world=3)
+
+
+def _edge_cases(rank, world):
+    """Empty tensors, scalars, bool, non-contiguous input (refused like the reference:
+    "input dense tensor has to be contiguous", src/utils.h check_tensor), object collectives."""
+    t = torch.empty(0)
+    dist.all_reduce(t)
+    dist.all_gather([torch.empty(0) for _ in range(world)], t)
+    dist.broadcast(t, 0)
+    dist.all_to_all_single(torch.empty(0), t)
+    dist.reduce_scatter_tensor(torch.empty(0), torch.empty(0))
+    with pytest.raises(RuntimeError, match="contiguous"):
+        dist.all_reduce(torch.ones(4, 4).t()[:, :2])
+    s = torch.tensor(float(rank + 1))
+    dist.all_reduce(s)
+    assert s.item() == world * (world + 1) / 2
+    b = torch.tensor([rank == 0, False])
+    dist.all_reduce(b, op=dist.ReduceOp.MAX)
+    assert b.tolist() == [True, False]
+    objs = [None] * world
+    dist.all_gather_object(objs, {"r": rank})
+    assert [o["r"] for o in objs] == list(range(world))
+    lst = [{"cfg": 7}] if rank == 0 else [None]
+    dist.broadcast_object_list(lst, 0)
+    assert lst == [{"cfg": 7}]
+
+
+def test_edge_cases_world3():
+    run_ranks(_edge_cases, world=3)
