@@ -37,3 +37,8 @@ def test_trace_replay_cpu_async_bf16_world3():
 @pytest.mark.parametrize("dtype_name", ["float16", "bfloat16"])
 def test_trace_replay_cuda(dtype_name):
     run_ranks(_replay, world=min(torch.cuda.device_count(), 8), device="cuda", args=("cuda", 3, dtype_name, False))
+
+
+def test_trace_replay_cpu_world8_bf16():
+    """Eight CPU ranks (the reference's own stress runs 12 local processes, testccl_cpu.py:8)."""
+    run_ranks(_replay, world=8, args=("cpu", 1, "bfloat16", False), timeout=300)
