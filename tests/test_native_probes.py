@@ -103,3 +103,18 @@ def test_epoch_protocol_model_under_tsan():
     assert "ThreadSanitizer" not in r.stderr, r.stderr[-4000:]
     r = subprocess.run([exe, "norelease"], capture_output=True, text=True, timeout=120)
     assert r.returncode == 3, "the model must detect the hazard when the release step is removed: " + r.stdout
+
+
+def test_worker_thread_under_tsan():
+    """The polling FIFO worker (csrc/pg/TaskThread.h): posts that land while it polls, while it goes to sleep and
+    while it sleeps all run once and in order, race-free under ThreadSanitizer."""
+    root = os.path.dirname(os.path.dirname(HERE))
+    src = os.path.join(HERE, "task_thread_stress.cpp")
+    hdr = os.path.join(root, "csrc", "pg", "TaskThread.h")
+    exe = os.path.join(HERE, "task_thread_tsan")
+    if not (os.path.exists(exe) and os.path.getmtime(exe) >= max(os.path.getmtime(src), os.path.getmtime(hdr))):
+        subprocess.run(["g++", "-std=c++17", "-O1", "-g", "-fsanitize=thread", "-I" + os.path.join(root, "csrc"), src, "-o", exe, "-lpthread"],
+                       check=True)
+    for _ in range(3):
+        r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0 and "PASS" in r.stdout and "ThreadSanitizer" not in r.stderr, r.stdout + r.stderr[-3000:]
