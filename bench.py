@@ -31,6 +31,8 @@ def parse():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ccl", choices=["ccl", "reference"])
+    ap.add_argument("--collective", default="ccl", choices=["ccl", "nccl"],
+                    help="nccl: same model and kernels, all_reduce through torch's NCCL backend + a separate add/norm kernel (comparison arm)")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=32, help="testing only; the headline config has 32")
@@ -137,7 +139,7 @@ def main():
     B, S, K, W = args.batch, args.prompt, args.steps, args.warmup
     max_seq = S + W + 2 * K + 16
     max_seq = (max_seq + 255) // 256 * 256
-    model = TPLlamaDecoder(cfg, max_batch=B, max_seq=max_seq, seed=0)
+    model = TPLlamaDecoder(cfg, max_batch=B, max_seq=max_seq, seed=0, collective=args.collective)
 
     g = torch.Generator().manual_seed(1234)
     prompt = torch.randint(0, cfg.vocab, (B, S), generator=g)
@@ -206,7 +208,7 @@ def main():
             "metric": METRIC, "value": round(tokens_per_s, 2), "unit": "tokens/s", "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
-            "impl": "ccl",
+            "impl": "ccl" if args.collective == "ccl" else "ccl kernels + nccl all_reduce",
             "config": {"model": "llama-7b-arch (32L, h4096, 32x128 heads, ffn 11008, vocab 32000)" if args.layers == 32 else f"llama-7b-arch truncated to {args.layers} layers (NOT the headline config)",
                        "global_batch": B, "seq_len": S, "new_tokens_timed": K, "parallelism": f"tp{world}",
                        "l2": "inputs larger than L2: every step streams the whole weight shard and KV cache from HBM",

@@ -51,14 +51,23 @@ def _rand(shape, seed, device, std=0.02):
 
 
 class _Comm:
-    """The fused ops of the process group's CUDA communicator, or single-GPU stand-ins."""
+    """The fused ops of the process group's CUDA communicator, or single-GPU stand-ins.
 
-    def __init__(self, group, device):
+    collective="nccl" is the comparison arm: the same model and kernels, but every all_reduce /
+    all_gather goes through a torch.distributed NCCL group and the residual add + RMSNorm runs as a
+    separate local kernel afterwards (what a model on the stock backend does)."""
+
+    def __init__(self, group, device, collective="ccl"):
         self.world = dist.get_world_size(group) if (group is not None or dist.is_initialized()) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         self.direct = None
         self.backend = None
-        if self.world > 1:
+        self.nccl = None
+        if self.world > 1 and collective == "nccl":
+            ranks = dist.get_process_group_ranks(group) if group is not None else list(range(self.world))
+            self.nccl = dist.new_group(ranks=ranks, backend="nccl")
+            self.direct = _C.CudaComm.create(None, 0, 1, 1 << 20, 1000, "ccl/local-norm")
+        elif self.world > 1:
             from .. import get_backend
 
             self.backend = get_backend(group, "cuda")
@@ -70,15 +79,21 @@ class _Comm:
         if self.backend is not None:
             self.backend.fused_allreduce_residual_rmsnorm(x, residual, weight, out, eps)
         else:
+            if self.nccl is not None:
+                dist.all_reduce(x, group=self.nccl)
             self.direct.allreduce_residual_rmsnorm([x], [residual], [weight], [out], eps)
 
     def all_reduce(self, t):
         if self.backend is not None:
             self.backend.fused_allreduce(t, 1.0)
+        elif self.nccl is not None:
+            dist.all_reduce(t, group=self.nccl)
 
     def all_gather(self, shard, out):
         if self.backend is not None:
             self.backend.fused_all_gather_copy_out(shard, list(out.chunk(self.world)))
+        elif self.nccl is not None:
+            dist.all_gather_into_tensor(out.view(-1), shard.contiguous().view(-1), group=self.nccl)
         else:
             out.copy_(shard.view_as(out))
 
@@ -86,10 +101,10 @@ class _Comm:
 class TPLlamaDecoder:
     """Llama decoder sharded `world`-way by attention head and FFN column (Megatron layout)."""
 
-    def __init__(self, cfg: LlamaConfig, max_batch=16, max_seq=2048, group=None, device=None, seed=0):
+    def __init__(self, cfg: LlamaConfig, max_batch=16, max_seq=2048, group=None, device=None, seed=0, collective="ccl"):
         self.cfg = cfg
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
-        self.comm = _Comm(group, self.device)
+        self.comm = _Comm(group, self.device, collective)
         W, r = self.comm.world, self.comm.rank
         self.world, self.rank = W, r
         assert cfg.n_heads % W == 0 and cfg.n_kv_heads % W == 0 and cfg.inter % (8 * W) == 0 and cfg.vocab % W == 0
