@@ -5,11 +5,18 @@ N(0, 0.02) weights), batch 16, 1024-token prompt of uniform random ids, TP = num
     python bench.py --gpus N --steps K --warmup W           (N > 1: launched by torchrun)
 
 A "step" generates one token for each of the 16 sequences (one CUDA-graph replay of the whole
-decode step: tcgen05 GEMMs, fused RoPE/KV-append/attention, one-shot all_reduce fused with
-residual-add + RMSNorm). Rank 0 prints ONE JSON line; `value` is tokens/s of the whole job.
-Timing: CUDA events on the launching stream, barrier + synchronize on both sides, max over ranks.
+decode step: tcgen05 GEMMs, fused RoPE/KV-append/attention, and each row-parallel projection
+fused with its all_reduce + residual-add + RMSNorm in one kernel). Rank 0 prints ONE JSON line;
+`value` is tokens/s of the whole job.
+Timing: a timed region is K steps between CUDA events on the launching stream, with a barrier +
+synchronize on both sides and the max taken over ranks; the region is repeated `--repeats` times
+from the same starting context and the MEDIAN is reported (`spread` gives min / max), so that the
+clock record holds more than a couple of samples and one slow replay does not move the number.
 Each step streams the rank's whole weight shard (13.5 GB / N) and KV cache from HBM, far more
 than the 126 MB L2, so no L2 flush is needed between steps.
+After the repo's arm the same step is measured in plain PyTorch on the stock stack
+(bench/torch_decode_baseline.py: cuBLAS matmul, SDPA, rms_norm, NCCL all_reduce, CUDA graph);
+`vs_baseline` is tokens/s of this repo divided by tokens/s of that arm on the same GPUs.
 """
 import argparse
 import json
@@ -37,6 +44,9 @@ def parse():
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=32, help="testing only; the headline config has 32")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--repeats", type=int, default=7, help="timed regions of --steps steps each; the median is reported")
+    ap.add_argument("--unfused", action="store_true", help="separate GEMM / all_reduce+norm / sampling kernels (A/B of the fused decode kernels)")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the plain-PyTorch + NCCL comparison arm")
     return ap.parse_args()
 
 
@@ -136,90 +146,157 @@ def main():
 
     cfg = LlamaConfig.llama7b()
     cfg.n_layers = args.layers
-    B, S, K, W = args.batch, args.prompt, args.steps, args.warmup
-    max_seq = S + W + 2 * K + 16
-    max_seq = (max_seq + 255) // 256 * 256
-    model = TPLlamaDecoder(cfg, max_batch=B, max_seq=max_seq, seed=0, collective=args.collective)
-
-    g = torch.Generator().manual_seed(1234)
-    prompt = torch.randint(0, cfg.vocab, (B, S), generator=g)
-    t0 = time.time()
-    model.prefill(prompt)
-    prefill_s = time.time() - t0
-    if not args.no_graph:
-        model.capture(B)
+    B, S, K, W, R = args.batch, args.prompt, args.steps, args.warmup, max(1, args.repeats)
+    max_seq = (S + max(K, W) + 16 + 255) // 256 * 256
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    def run_steps(n):
-        for _ in range(n):
-            model.decode_step(B)
-
-    model.decode_step(B)
-    for _ in range(W):
-        run_steps(1)
-
-    def timed(fn):
-        barrier()
+    def measure(run_region, reset):
+        """R timed regions; returns (list of ms per region, max over ranks each; clock record)."""
         sampler = ClockSampler(local_rank) if rank == 0 else None
         if sampler:
             sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        fn()
-        e1.record()
-        torch.cuda.synchronize(dev)
-        barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        out = []
+        for _ in range(R):
+            reset()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            run_region()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            barrier()
+            ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            out.append(float(ms.item()))
         clocks = sampler.stop() if sampler else None
-        return float(ms.item()), clocks
+        return out, clocks
 
-    # ---- device-timed region: K decode steps --------------------------------------------------
+    def summarize(ms_list):
+        med = statistics.median(ms_list)
+        return {"tokens_per_s": B * K / (med * 1e-3), "ms_per_step": med / K, "min_ms_per_step": min(ms_list) / K,
+                "max_ms_per_step": max(ms_list) / K}
+
+    # ---- this repository's arm ----------------------------------------------------------------------
+    model = TPLlamaDecoder(cfg, max_batch=B, max_seq=max_seq, seed=0, collective=args.collective, fused=not args.unfused)
+    g = torch.Generator().manual_seed(1234)
+    prompt = torch.randint(0, cfg.vocab, (B, S), generator=g)
+    barrier()
+    t0 = time.time()
+    model.prefill(prompt)
+    barrier()
+    prefill_s = time.time() - t0
+    if not args.no_graph:
+        model.capture(B)
+    model.decode_step(B)
+    for _ in range(W):
+        model.decode_step(B)
+
+    def reset_model():
+        model.positions[:B] = S  # every region decodes the same K positions after the prompt
+
     C.launch_count_reset()
     # a profiler started with "--profile-from-start off" captures exactly the timed steps
     profile_range = os.environ.get("CCL_BENCH_PROFILE_RANGE") == "1"
     if profile_range:
         torch.cuda.cudart().cudaProfilerStart()
-    ms, clocks = timed(lambda: run_steps(K))
+
+    def region():
+        for _ in range(K):
+            model.decode_step(B)
+
+    ms_list, clocks = measure(region, reset_model)
     if profile_range:
         torch.cuda.cudart().cudaProfilerStop()
-    tokens_per_s = B * K / (ms * 1e-3)
+    dev_res = summarize(ms_list)
 
     # ---- end to end through the public API: ids from pinned host memory, result read back ------
     pin_in = torch.zeros(B, dtype=torch.int64).pin_memory()
     pin_out = torch.zeros(B, dtype=torch.int64).pin_memory()
     pin_in.copy_(model.next_tokens[:B].cpu())
 
-    def e2e_loop():
+    def e2e_region():
         for _ in range(K):
             model.decode_step_host(pin_in, pin_out)
             pin_in.copy_(pin_out)
 
-    ms_e2e, clocks_e2e = timed(e2e_loop)
-    e2e_tokens_per_s = B * K / (ms_e2e * 1e-3)
+    ms_e2e, clocks_e2e = measure(e2e_region, reset_model)
+    e2e_res = summarize(ms_e2e)
+    kernels_per_step = model.kernels_per_step
+    fused = model.fused
+    del model
+    torch.cuda.empty_cache()
+
+    # ---- comparison arm: plain PyTorch (cuBLAS, SDPA, rms_norm) + NCCL, same shapes, CUDA graph --------
+    base = None
+    if not args.no_baseline:
+        import importlib.util
+
+        spec = importlib.util.spec_from_file_location("torch_decode_baseline", os.path.join(ROOT, "bench", "torch_decode_baseline.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        TorchTPDecoder = mod.TorchTPDecoder
+
+        nccl = dist.new_group(backend="nccl") if world > 1 else None
+        kv_len = (S + max(K, W) + 8 + 63) // 64 * 64
+        tm = TorchTPDecoder(cfg, B, S, kv_len, group=nccl, device=dev, seed=1)
+        if not args.no_graph:
+            tm.capture()
+        for _ in range(W + 1):
+            tm.decode_step()
+
+        def reset_tm():
+            tm.positions.fill_(S)
+
+        def tm_region():
+            for _ in range(K):
+                tm.decode_step()
+
+        b_ms, b_clocks = measure(tm_region, reset_tm)
+        pin_in.copy_(tm.next_tokens.cpu())
+
+        def tm_e2e():
+            for _ in range(K):
+                tm.decode_step_host(pin_in, pin_out)
+                pin_in.copy_(pin_out)
+
+        b_e2e_ms, _ = measure(tm_e2e, reset_tm)
+        bd, be = summarize(b_ms), summarize(b_e2e_ms)
+        base = {"impl": "plain PyTorch: torch.matmul (cuBLAS), scaled_dot_product_attention, rms_norm, eager RoPE / KV append, "
+                        "NCCL all_reduce + all_gather, one CUDA graph per step; none of this repository's kernels",
+                "tokens_per_s": round(bd["tokens_per_s"], 2), "ms_per_step": round(bd["ms_per_step"], 4),
+                "e2e_tokens_per_s": round(be["tokens_per_s"], 2),
+                "ratio": round(dev_res["tokens_per_s"] / bd["tokens_per_s"], 4),
+                "e2e_ratio": round(e2e_res["tokens_per_s"] / be["tokens_per_s"], 4),
+                "clocks": {"sm_mhz": b_clocks["sm_mhz"], "reasons": b_clocks["reasons"]} if b_clocks else None}
+        del tm
 
     if rank == 0:
         out = {
-            "metric": METRIC, "value": round(tokens_per_s, 2), "unit": "tokens/s", "n_gpus": world, "steps": K,
-            "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
-            "impl": "ccl" if args.collective == "ccl" else "ccl kernels + nccl all_reduce",
+            "metric": METRIC, "value": round(dev_res["tokens_per_s"], 2), "unit": "tokens/s", "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": round(dev_res["ms_per_step"], 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": base["ratio"] if base else None,
+            "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
+            "impl": ("ccl" if fused else "ccl, unfused decode kernels") if args.collective == "ccl" else "ccl kernels + nccl all_reduce",
+            "repeats": R, "spread": {"min_ms_per_step": round(dev_res["min_ms_per_step"], 4), "max_ms_per_step": round(dev_res["max_ms_per_step"], 4)},
             "config": {"model": "llama-7b-arch (32L, h4096, 32x128 heads, ffn 11008, vocab 32000)" if args.layers == 32 else f"llama-7b-arch truncated to {args.layers} layers (NOT the headline config)",
                        "global_batch": B, "seq_len": S, "new_tokens_timed": K, "parallelism": f"tp{world}",
                        "l2": "inputs larger than L2: every step streams the whole weight shard and KV cache from HBM",
+                       "timing": f"median of {R} regions of {K} steps, each from context {S}",
                        "cuda_graph": not args.no_graph, "prefill_s": round(prefill_s, 2)},
+            "prefill_tokens_per_s": round(B * S / prefill_s, 1),
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
                        "samples": clocks["samples"]},
-            "e2e": {"value": round(e2e_tokens_per_s, 2), "unit": "tokens/s", "h2d_bytes_per_step": B * 8,
-                    "d2h_bytes_per_step": B * 8, "ms_per_step": round(ms_e2e / K, 4),
+            "e2e": {"value": round(e2e_res["tokens_per_s"], 2), "unit": "tokens/s", "h2d_bytes_per_step": B * 8,
+                    "d2h_bytes_per_step": B * 8, "ms_per_step": round(e2e_res["ms_per_step"], 4),
                     "clocks": {"sm_mhz": clocks_e2e["sm_mhz"], "reasons": clocks_e2e["reasons"]}},
-            "gpu_launches": model.kernels_per_step * K,
-            "kernels_per_step": model.kernels_per_step,
+            "gpu_launches": kernels_per_step * K,
+            "kernels_per_step": kernels_per_step,
+            "baseline": base,
         }
         print(json.dumps(out))
     if world > 1:

@@ -73,6 +73,96 @@ void fill_moe_combine(ccl::MoeArgs& a, const at::Tensor& y, const at::Tensor& me
   a.hidden = (int)y.size(1);
 }
 
+ccl::FusedNormArgs make_norm_args(const at::Tensor& x, at::Tensor& residual, const at::Tensor& weight, at::Tensor& out, double eps,
+                                  const c10::optional<at::Tensor>& tokens, int64_t vocab_base, bool zero_residual) {
+  TORCH_CHECK(x.is_cuda() && residual.is_cuda() && weight.is_cuda() && out.is_cuda(), "allreduce_residual_rmsnorm: CUDA tensors required");
+  TORCH_CHECK(x.device() == residual.device() && x.device() == weight.device() && x.device() == out.device(),
+              "allreduce_residual_rmsnorm: tensors must be on one device");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf, "allreduce_residual_rmsnorm: bf16 or f16 tensors required");
+  TORCH_CHECK(residual.scalar_type() == x.scalar_type() && weight.scalar_type() == x.scalar_type() && out.scalar_type() == x.scalar_type(),
+              "allreduce_residual_rmsnorm: x, residual, weight and out must share one dtype");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && residual.is_contiguous() && out.is_contiguous() && weight.is_contiguous(),
+              "allreduce_residual_rmsnorm: contiguous [rows, hidden] tensors required");
+  const int64_t hidden = x.size(1);
+  TORCH_CHECK(hidden % 8 == 0 && weight.numel() == hidden, "allreduce_residual_rmsnorm: hidden must be a multiple of 8 and weight [hidden]");
+  ccl::FusedNormArgs a;
+  a.x = x.data_ptr();
+  a.residual = residual.data_ptr();
+  a.weight = weight.data_ptr();
+  a.out = out.data_ptr();
+  a.hidden = (int)hidden;
+  a.eps = (float)eps;
+  a.zero_residual = zero_residual ? 1 : 0;
+  int64_t rows = x.size(0);
+  if (tokens.has_value()) {
+    const at::Tensor& t = *tokens;
+    TORCH_CHECK(t.is_cuda() && t.device() == x.device() && t.scalar_type() == at::kLong && t.is_contiguous() && t.dim() == 1,
+                "allreduce_residual_rmsnorm: tokens must be a contiguous int64 vector on the same device");
+    a.gather_tokens = reinterpret_cast<const long long*>(t.data_ptr<int64_t>());
+    a.gather_base = vocab_base;
+    a.gather_rows = (int)x.size(0);
+    rows = t.numel();
+  }
+  TORCH_CHECK(residual.dim() == 2 && residual.size(0) == rows && residual.size(1) == hidden && out.sizes() == residual.sizes(),
+              "allreduce_residual_rmsnorm: residual and out must be [rows, hidden]");
+  a.rows = (int)rows;
+  return a;
+}
+
+ccl::GemmArNormArgs make_gemm_ar_norm_args(const at::Tensor& w_packed, const at::Tensor& x, at::Tensor& residual,
+                                           const at::Tensor& weight, at::Tensor& out, double eps, int64_t splitk) {
+  TORCH_CHECK(w_packed.is_cuda() && x.is_cuda() && residual.is_cuda() && weight.is_cuda() && out.is_cuda(), "gemm_ar_norm: CUDA tensors required");
+  TORCH_CHECK(x.device() == w_packed.device() && x.device() == residual.device() && x.device() == weight.device() && x.device() == out.device(),
+              "gemm_ar_norm: tensors must be on one device");
+  TORCH_CHECK(w_packed.scalar_type() == at::kBFloat16 && x.scalar_type() == at::kBFloat16 && residual.scalar_type() == at::kBFloat16 &&
+                  weight.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16, "gemm_ar_norm: bf16 tensors required");
+  TORCH_CHECK(w_packed.dim() == 2 && w_packed.size(1) == 64 && w_packed.is_contiguous() && w_packed.size(0) % 128 == 0,
+              "gemm_ar_norm: weights must be packed with pack_weight ([*, 64])");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.stride(0) % 8 == 0, "gemm_ar_norm: x must be [rows, K] with a contiguous K and a row stride that is a multiple of 8");
+  TORCH_CHECK(residual.dim() == 2 && residual.is_contiguous() && out.is_contiguous() && weight.is_contiguous() && out.sizes() == residual.sizes() &&
+                  residual.size(0) == x.size(0) && weight.numel() == residual.size(1), "gemm_ar_norm: residual / out [rows, hidden], weight [hidden]");
+  ccl::GemmArNormArgs a;
+  a.w = w_packed.data_ptr();
+  a.w_packed_rows = w_packed.size(0);
+  a.x = x.data_ptr();
+  a.ldx = x.stride(0);
+  a.residual = residual.data_ptr();
+  a.weight = weight.data_ptr();
+  a.out = out.data_ptr();
+  a.rows = (int)x.size(0);
+  a.hidden = (int)residual.size(1);
+  a.K = (int)x.size(1);
+  a.eps = (float)eps;
+  a.splitk = (int)splitk;
+  const int64_t k_tiles = (a.K + 63) / 64;
+  TORCH_CHECK(a.hidden % 128 == 0 && w_packed.size(0) >= (int64_t)a.hidden * k_tiles, "gemm_ar_norm: packed weight does not cover [hidden, K]");
+  return a;
+}
+
+ccl::SampleArgs make_sample_args(const at::Tensor& logits, at::Tensor& next_tokens, const c10::optional<at::Tensor>& tokens,
+                                 const c10::optional<at::Tensor>& positions) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1, "sample: logits must be [rows, vocab shard] fp32");
+  TORCH_CHECK(next_tokens.is_cuda() && next_tokens.device() == logits.device() && next_tokens.scalar_type() == at::kLong &&
+                  next_tokens.is_contiguous() && next_tokens.numel() >= logits.size(0), "sample: next_tokens must be int64 [rows]");
+  ccl::SampleArgs a;
+  a.logits = logits.data_ptr<float>();
+  a.ld = logits.stride(0);
+  a.vshard = (int)logits.size(1);
+  a.rows = (int)logits.size(0);
+  a.next_tokens = reinterpret_cast<long long*>(next_tokens.data_ptr<int64_t>());
+  if (tokens.has_value()) {
+    TORCH_CHECK(tokens->is_cuda() && tokens->device() == logits.device() && tokens->scalar_type() == at::kLong && tokens->is_contiguous() &&
+                    tokens->numel() >= logits.size(0), "sample: tokens must be int64 [rows]");
+    a.tokens = reinterpret_cast<long long*>(const_cast<int64_t*>(tokens->data_ptr<int64_t>()));
+  }
+  if (positions.has_value()) {
+    TORCH_CHECK(positions->is_cuda() && positions->device() == logits.device() && positions->scalar_type() == at::kInt &&
+                    positions->is_contiguous() && positions->numel() >= logits.size(0), "sample: positions must be int32 [rows]");
+    a.positions = const_cast<int*>(positions->data_ptr<int>());
+  }
+  return a;
+}
+
 namespace {
 
 void cu(cudaError_t e, const char* what) {
@@ -230,23 +320,39 @@ struct PyComm {
   void barrier() { cu(comm->barrier(stream()), "barrier"); }
 
   void allreduce_residual_rmsnorm(std::vector<at::Tensor> xs, std::vector<at::Tensor> residuals,
-                                  std::vector<at::Tensor> weights, std::vector<at::Tensor> outs, double eps) {
+                                  std::vector<at::Tensor> weights, std::vector<at::Tensor> outs, double eps,
+                                  c10::optional<std::vector<at::Tensor>> tokens, std::vector<int64_t> vocab_base, bool zero_residual) {
     check_n(xs.size());
     std::vector<ccl::FusedNormArgs> args(xs.size());
     for (size_t i = 0; i < xs.size(); ++i) {
-      TORCH_CHECK(xs[i].is_contiguous() && residuals[i].is_contiguous() && outs[i].is_contiguous(),
-                  "contiguous tensors required");
-      TORCH_CHECK(xs[i].dim() == 2, "x must be [rows, hidden]");
-      args[i].x = xs[i].data_ptr();
-      args[i].residual = residuals[i].data_ptr();
-      args[i].weight = weights[i].data_ptr();
-      args[i].out = outs[i].data_ptr();
-      args[i].rows = (int)xs[i].size(0);
-      args[i].hidden = (int)xs[i].size(1);
-      args[i].eps = (float)eps;
+      c10::optional<at::Tensor> tok;
+      if (tokens.has_value()) tok = (*tokens)[i];
+      args[i] = make_norm_args(xs[i], residuals[i], weights[i], outs[i], eps, tok, vocab_base.empty() ? 0 : vocab_base[i], zero_residual);
     }
     cu(comm->allreduce_residual_rmsnorm(to_ccl_dtype(xs[0].scalar_type()), args, stream()),
        "allreduce_residual_rmsnorm");
+  }
+
+  // w[r]: packed [hidden, K_r]; x[r]: [rows, K_r]; residual[r], out[r]: [rows, hidden]
+  void gemm_ar_norm(std::vector<at::Tensor> ws, std::vector<at::Tensor> xs, std::vector<at::Tensor> residuals,
+                    std::vector<at::Tensor> weights, std::vector<at::Tensor> outs, double eps, int64_t splitk) {
+    check_n(xs.size());
+    std::vector<ccl::GemmArNormArgs> args(xs.size());
+    for (size_t i = 0; i < xs.size(); ++i) args[i] = make_gemm_ar_norm_args(ws[i], xs[i], residuals[i], weights[i], outs[i], eps, splitk);
+    cu(comm->gemm_ar_norm(args, stream()), "gemm_ar_norm");
+  }
+
+  void sample_allgather(std::vector<at::Tensor> logits, std::vector<at::Tensor> next_tokens,
+                        c10::optional<std::vector<at::Tensor>> tokens, c10::optional<std::vector<at::Tensor>> positions) {
+    check_n(logits.size());
+    std::vector<ccl::SampleArgs> args(logits.size());
+    for (size_t i = 0; i < logits.size(); ++i) {
+      c10::optional<at::Tensor> t, p;
+      if (tokens.has_value()) t = (*tokens)[i];
+      if (positions.has_value()) p = (*positions)[i];
+      args[i] = make_sample_args(logits[i], next_tokens[i], t, p);
+    }
+    cu(comm->sample_allgather(args, stream()), "sample_allgather");
   }
 
   // a[r]: [M, K_r]; b[r]: [N, K_r]; out[r]: [M/W, N]
@@ -432,7 +538,16 @@ void bind_cuda_comm(py::module& m) {
       .def("gather", &PyComm::gather)
       .def("scatter", &PyComm::scatter)
       .def("barrier", &PyComm::barrier)
-      .def("allreduce_residual_rmsnorm", &PyComm::allreduce_residual_rmsnorm)
+      .def("allreduce_residual_rmsnorm", &PyComm::allreduce_residual_rmsnorm, py::arg("xs"), py::arg("residuals"), py::arg("weights"),
+           py::arg("outs"), py::arg("eps"), py::arg("tokens") = py::none(), py::arg("vocab_base") = std::vector<int64_t>{},
+           py::arg("zero_residual") = false)
+      .def("gemm_ar_norm", &PyComm::gemm_ar_norm, py::arg("ws"), py::arg("xs"), py::arg("residuals"), py::arg("weights"), py::arg("outs"),
+           py::arg("eps"), py::arg("splitk") = 0)
+      .def("fits_gemm_ar_norm", [](PyComm& c, int rows, int hidden, int k) { return c.comm->fits_gemm_ar_norm(rows, hidden, k); })
+      .def("sample_allgather", &PyComm::sample_allgather, py::arg("logits"), py::arg("next_tokens"), py::arg("tokens") = py::none(),
+           py::arg("positions") = py::none())
+      .def("abort", [](PyComm& c) { c.comm->abort(); })
+      .def("clear_abort", [](PyComm& c) { c.comm->clear_abort(); })
       .def("gemm_rs", &PyComm::gemm_rs)
       .def("ag_gemm", &PyComm::ag_gemm)
       .def("moe_dispatch", &PyComm::moe_dispatch)

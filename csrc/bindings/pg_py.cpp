@@ -13,6 +13,7 @@
 #include <torch/extension.h>
 
 #include "bindings/common.h"
+#include "bindings/fused_ops.h"
 #include "cuda/CudaBackend.h"
 #include "pg/Env.h"
 #include "pg/ProcessGroupCCL.hpp"
@@ -61,10 +62,7 @@ namespace ccl_py {
 
 using c10d::ProcessGroupCCL;
 
-static ccl::CudaComm& cuda_comm_of(ProcessGroupCCL& pg, const at::Tensor& t) {
-  TORCH_CHECK(t.is_cuda(), "ccl fused ops need CUDA tensors");
-  return pg.cudaImpl(t.device()).comm(t.device());
-}
+using ccl_ops::cuda_comm_of;
 
 void bind_process_group(py::module& m) {
   ProcessGroupCCL::cclInitOnce();
@@ -90,140 +88,30 @@ void bind_process_group(py::module& m) {
       .def("set_timeout", &ProcessGroupCCL::setTimeout)
       .def("error_state", [](ProcessGroupCCL& pg) { return (int)pg.getError(); })
       // ---- fused ops: run on the CURRENT stream of the tensor's device (capturable) ----
-      .def("fused_allreduce_residual_rmsnorm",
-           [](ProcessGroupCCL& pg, const at::Tensor& x, at::Tensor& residual, const at::Tensor& weight, at::Tensor& out, double eps) {
-             auto& c = cuda_comm_of(pg, x);
-             c10::cuda::CUDAGuard g(x.device());
-             ccl::FusedNormArgs a;
-             a.x = x.data_ptr();
-             a.residual = residual.data_ptr();
-             a.weight = weight.data_ptr();
-             a.out = out.data_ptr();
-             a.rows = (int)(x.numel() / x.size(-1));
-             a.hidden = (int)x.size(-1);
-             a.eps = (float)eps;
-             C10_CUDA_CHECK(c.allreduce_residual_rmsnorm(to_ccl_dtype(x.scalar_type()), {a}, c10::cuda::getCurrentCUDAStream()));
-           })
-      .def("fused_allreduce",
-           [](ProcessGroupCCL& pg, at::Tensor& t, double scale) {
-             auto& c = cuda_comm_of(pg, t);
-             if (c.world() == 1) {
-               if (scale != 1.0) t.mul_(scale);
-               return;
-             }
-             c10::cuda::CUDAGuard g(t.device());
-             ccl::CollArgs a;
-             a.in = t.data_ptr();
-             a.out = t.data_ptr();
-             a.count = t.numel();
-             if (scale != 1.0) {
-               a.has_scale = 1;
-               a.scale = (float)scale;
-             }
-             C10_CUDA_CHECK(c.allreduce(to_ccl_dtype(t.scalar_type()), {a}, c10::cuda::getCurrentCUDAStream()));
-           },
-           py::arg("tensor"), py::arg("scale") = 1.0)
-      .def("fused_reduce_scatter_cast",
-           // out (fp32 or input dtype) = scale * sum over ranks of this rank's piece of `inp`
-           [](ProcessGroupCCL& pg, const at::Tensor& inp, at::Tensor& out, double scale) {
-             auto& c = cuda_comm_of(pg, inp);
-             c10::cuda::CUDAGuard g(inp.device());
-             const int W = c.world();
-             TORCH_CHECK(inp.numel() == out.numel() * W, "input must hold world pieces of the output size");
-             ccl::CollArgs a;
-             const int64_t n = out.numel();
-             for (int p = 0; p < W; ++p) {
-               a.in_piece[p] = static_cast<const char*>(inp.data_ptr()) + (size_t)p * n * inp.element_size();
-               a.in_cnt[p] = n;
-             }
-             a.out = out.data_ptr();
-             if (scale != 1.0) {
-               a.has_scale = 1;
-               a.scale = (float)scale;
-             }
-             if (W == 1) {
-               out.copy_(inp.view_as(out));
-               if (scale != 1.0) out.mul_(scale);
-               return;
-             }
-             C10_CUDA_CHECK(c.reduce_scatter(to_ccl_dtype(inp.scalar_type()), to_ccl_dtype(out.scalar_type()), {a}, c10::cuda::getCurrentCUDAStream()));
-           },
-           py::arg("input"), py::arg("output"), py::arg("scale") = 1.0)
-      .def("fused_all_gather_copy_out",
-           // gathers `shard` from every rank straight into the per-rank destination tensors
-           [](ProcessGroupCCL& pg, const at::Tensor& shard, std::vector<at::Tensor> outs) {
-             auto& c = cuda_comm_of(pg, shard);
-             c10::cuda::CUDAGuard g(shard.device());
-             TORCH_CHECK((int)outs.size() == c.world(), "need one destination per rank");
-             if (c.world() == 1) {
-               outs[0].copy_(shard.view_as(outs[0]));
-               return;
-             }
-             ccl::CollArgs a;
-             a.in = shard.data_ptr();
-             for (int p = 0; p < c.world(); ++p) {
-               a.out_piece[p] = outs[p].data_ptr();
-               a.out_cnt[p] = (uint64_t)outs[p].numel() * outs[p].element_size();
-             }
-             C10_CUDA_CHECK(c.all_gather({a}, c10::cuda::getCurrentCUDAStream()));
-           })
-      .def("fused_gemm_rs",
-           // out[M/W, N] = this rank's rows of sum over ranks of a[M, K_local] @ b[N, K_local]^T
-           [](ProcessGroupCCL& pg, const at::Tensor& a, const at::Tensor& b, at::Tensor& out) {
-             auto& c = cuda_comm_of(pg, a);
-             c10::cuda::CUDAGuard g(a.device());
-             TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16, "bf16 tensors required");
-             TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && out.is_contiguous(), "K-contiguous operands, contiguous output");
-             ccl::GemmRsArgs r;
-             r.a = a.data_ptr();
-             r.b = b.data_ptr();
-             r.out = out.data_ptr();
-             r.M = a.size(0);
-             r.K = a.size(1);
-             r.N = b.size(0);
-             r.lda = a.stride(0);
-             r.ldb = b.stride(0);
-             TORCH_CHECK(out.size(0) * c.world() == r.M && out.size(1) == r.N, "out must be [M/world, N]");
-             C10_CUDA_CHECK(c.gemm_rs({r}, c10::cuda::getCurrentCUDAStream()));
-           })
-      .def("fused_ag_gemm",
-           // out[M, N_local] = all_gather(a_shard)[M, K] @ b[N_local, K]^T
-           [](ProcessGroupCCL& pg, const at::Tensor& a_shard, const at::Tensor& b, at::Tensor& out) {
-             auto& c = cuda_comm_of(pg, a_shard);
-             c10::cuda::CUDAGuard g(a_shard.device());
-             TORCH_CHECK(a_shard.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16, "bf16 tensors required");
-             TORCH_CHECK(a_shard.is_contiguous() && b.stride(1) == 1 && out.stride(1) == 1, "packed A shard, K-contiguous B");
-             ccl::AgGemmArgs r;
-             r.a_shard = a_shard.data_ptr();
-             r.b = b.data_ptr();
-             r.out = out.data_ptr();
-             r.M = a_shard.size(0) * c.world();
-             r.K = a_shard.size(1);
-             r.N = b.size(0);
-             r.lda = a_shard.stride(0);
-             r.ldb = b.stride(0);
-             r.ldo = out.stride(0);
-             TORCH_CHECK(out.size(0) == r.M && out.size(1) == r.N, "out must be [M, N]");
-             C10_CUDA_CHECK(c.ag_gemm({r}, c10::cuda::getCurrentCUDAStream()));
-           })
-      .def("fused_moe_dispatch",
-           [](ProcessGroupCCL& pg, const at::Tensor& x, const at::Tensor& idx, at::Tensor& out_x, at::Tensor& meta,
-              at::Tensor& count, int experts_per_rank) {
-             auto& c = cuda_comm_of(pg, x);
-             c10::cuda::CUDAGuard g(x.device());
-             ccl::MoeArgs a;
-             fill_moe_dispatch(a, x, idx, out_x, meta, count, experts_per_rank);
-             C10_CUDA_CHECK(c.moe_dispatch({a}, c10::cuda::getCurrentCUDAStream()));
-           })
-      .def("fused_moe_combine",
-           [](ProcessGroupCCL& pg, const at::Tensor& y, const at::Tensor& meta, const at::Tensor& count,
-              const at::Tensor& gate, at::Tensor& out) {
-             auto& c = cuda_comm_of(pg, y);
-             c10::cuda::CUDAGuard g(y.device());
-             ccl::MoeArgs a;
-             fill_moe_combine(a, y, meta, count, gate, out);
-             C10_CUDA_CHECK(c.moe_combine({a}, c10::cuda::getCurrentCUDAStream()));
-           })
+      .def("fused_allreduce_residual_rmsnorm", &ccl_ops::allreduce_residual_rmsnorm, py::arg("x"), py::arg("residual"), py::arg("weight"),
+           py::arg("out"), py::arg("eps"), py::arg("tokens") = py::none(), py::arg("vocab_base") = 0, py::arg("zero_residual") = false)
+      // residual += sum over ranks of x[rows, K_local] @ w[hidden, K_local]^T ; out = rmsnorm(residual) * weight  (one launch)
+      .def("fused_gemm_ar_norm", &ccl_ops::gemm_ar_norm, py::arg("w_packed"), py::arg("x"), py::arg("residual"), py::arg("weight"),
+           py::arg("out"), py::arg("eps"), py::arg("splitk") = 0)
+      .def("fits_gemm_ar_norm", [](ProcessGroupCCL& pg, const at::Tensor& like, int rows, int hidden, int k) {
+        return cuda_comm_of(pg, like).fits_gemm_ar_norm(rows, hidden, k);
+      })
+      // arg-max over the local logits shard + all-gather of the winners; writes the global winner ids
+      .def("fused_sample_allgather", &ccl_ops::sample_allgather, py::arg("logits"), py::arg("next_tokens"), py::arg("tokens") = py::none(),
+           py::arg("positions") = py::none())
+      .def("fused_allreduce", &ccl_ops::all_reduce_scaled, py::arg("tensor"), py::arg("scale") = 1.0)
+      // out (fp32 or input dtype) = scale * sum over ranks of this rank's piece of `inp`
+      .def("fused_reduce_scatter_cast", &ccl_ops::reduce_scatter_cast, py::arg("input"), py::arg("output"), py::arg("scale") = 1.0)
+      // gathers `shard` from every rank straight into the per-rank destination tensors
+      .def("fused_all_gather_copy_out", &ccl_ops::all_gather_copy_out)
+      // out[M/W, N] = this rank's rows of sum over ranks of a[M, K_local] @ b[N, K_local]^T
+      .def("fused_gemm_rs", &ccl_ops::gemm_reduce_scatter)
+      // out[M, N_local] = all_gather(a_shard)[M, K] @ b[N_local, K]^T
+      .def("fused_ag_gemm", &ccl_ops::all_gather_gemm)
+      .def("fused_moe_dispatch", &ccl_ops::moe_dispatch)
+      .def("fused_moe_combine", &ccl_ops::moe_combine)
+      // staging capacity (bytes) of the fused GEMM + collective ops: the whole M x N (gemm_rs) or M x K (ag_gemm) bf16 matrix must fit
+      .def("fused_gemm_capacity_bytes", [](ProcessGroupCCL& pg, const at::Tensor& like) { return (int64_t)cuda_comm_of(pg, like).config().half_bytes; })
       .def("moe_capacity", [](ProcessGroupCCL& pg, const at::Tensor& like) { return cuda_comm_of(pg, like).moe_capacity((int)like.size(-1)); })
       .def("cuda_comm_status", [](ProcessGroupCCL& pg, const at::Tensor& t) {
         auto& c = cuda_comm_of(pg, t);

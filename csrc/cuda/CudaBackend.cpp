@@ -64,6 +64,9 @@ std::string status_message(CudaComm& c) {
   int r = -1, p = -1, ph = -1;
   const int code = c.poll_status(&r, &p, &ph);
   if (code == 0) return "";
+  if (code == kStatusAborted)
+    return "ccl: collective aborted: rank " + std::to_string(r) + " gave up waiting for rank " + std::to_string(p) +
+           " because abort() was called on the process group";
   return "ccl: device-side wait expired (code " + std::to_string(code) + "): rank " + std::to_string(r) +
          " waited for rank " + std::to_string(p) + " in phase " + std::to_string(ph) +
          "; the communicator is unusable, destroy the process group";
@@ -112,6 +115,8 @@ class CudaWork : public AsyncWork {
   void synchronize() override {
     if (!same_stream_ && end_) C10_CUDA_CHECK(cudaStreamWaitEvent(c10::cuda::getCurrentCUDAStream(device_.index()).stream(), end_->ev, 0));
   }
+
+  int cudaDevice() const override { return device_.index(); }
 
   float getDuration() const override {
     if (!start_ || !end_ || !timed_) return -1.f;
@@ -508,6 +513,12 @@ void CudaBackendImpl::shutdown() {
   stream_.reset();
 }
 
-void CudaBackendImpl::abort() {}
+// Raises the communicator's abort word: every kernel that is (or will be) spinning on a peer
+// returns within microseconds instead of after the spin budget, its Work fails with the
+// "aborted" status, and further collectives on this group are refused.
+void CudaBackendImpl::abort() {
+  std::lock_guard<std::mutex> g(mu_);
+  if (comm_) comm_->abort();
+}
 
 }  // namespace ccl

@@ -51,6 +51,7 @@ void fill_ctx(RankCtx& c, int rank, int world, const std::vector<void*>& bases, 
   }
   c.state = reinterpret_cast<uint32_t*>(static_cast<char*>(bases[rank]) + 2 * half + kFlagBytes);
   c.status = status;
+  c.abort_flag = status ? status + 8 : nullptr;  // word 8 of the host-mapped status block
   c.half_bytes = half;
   c.spin_ns = spin_ms * 1000000ull;
   c.mc_data = static_cast<char*>(multicast_base);
@@ -78,6 +79,7 @@ CudaComm::CudaComm(int rank, int world, int device, const CommConfig& cfg, KvSto
   symm_ = std::make_unique<SymmMem>(cfg_.symm, rank_, world_, device_, arena_bytes_, kv_, prefix_,
                                     cfg_.nvls && cfg_.symm == SymmKind::kVmm);
   peer_arenas_ = symm_->bases();
+  check(cudaEventCreateWithFlags(&order_ev_, cudaEventDisableTiming), "cudaEventCreate(order)");
   init_tables();
 }
 
@@ -101,6 +103,7 @@ CudaComm::CudaComm(int world, int device, const CommConfig& cfg)
   std::memset(status_host_, 0, 64);
   check(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev_), status_host_, 0), "cudaHostGetDevicePointer");
   check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+  check(cudaEventCreateWithFlags(&order_ev_, cudaEventDisableTiming), "cudaEventCreate(order)");
   init_tables();
 }
 
@@ -134,6 +137,7 @@ CudaComm::~CudaComm() {
   if (dev_ctx_table_) cudaFree(dev_ctx_table_);
   if (dev_args_table_) cudaFree(dev_args_table_);
   if (status_host_) cudaFreeHost(status_host_);
+  if (order_ev_) cudaEventDestroy(order_ev_);
 }
 
 int CudaComm::poll_status(int* rank, int* peer, int* phase) const {
@@ -150,6 +154,29 @@ void CudaComm::clear_status() {
   volatile int* s = status_host_;
   s[1] = s[2] = s[3] = 0;
   s[0] = 0;
+}
+
+// One launch in flight per communicator: the kernels of a communicator share its epoch, ticket and
+// staging halves, so two of them must never run concurrently. Launches on one stream are ordered
+// by the stream; when the caller moves to another stream (c10d ops run on the backend's
+// communication stream, the fused ops on the caller's current stream) the new stream is made to
+// wait for everything enqueued on the previous one. Costs nothing while the stream stays the
+// same. Streams that are being captured are left alone: inside a CUDA graph the capture's own
+// dependencies order the launches.
+void CudaComm::enter_stream(cudaStream_t s) {
+  std::lock_guard<std::mutex> g(order_mu_);
+  if (has_last_stream_ && last_stream_ != s) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone, cl = cudaStreamCaptureStatusNone;
+    const bool q = cudaStreamIsCapturing(s, &cs) == cudaSuccess && cudaStreamIsCapturing(last_stream_, &cl) == cudaSuccess;
+    if (q && cs == cudaStreamCaptureStatusNone && cl == cudaStreamCaptureStatusNone &&
+        cudaEventRecord(order_ev_, last_stream_) == cudaSuccess) {
+      cudaStreamWaitEvent(s, order_ev_, 0);
+    } else {
+      (void)cudaGetLastError();
+    }
+  }
+  last_stream_ = s;
+  has_last_stream_ = true;
 }
 
 template <typename ArgsT>
@@ -207,6 +234,7 @@ static size_t compact_stride(size_t capacity_stride, size_t needed_vecs) {
 cudaError_t CudaComm::allreduce(int dtype, std::vector<CollArgs> args, cudaStream_t stream, AlgoChoice* chosen) {
   CCL_CHECK_ARGS(args)
   DeviceGuard g(device_);
+  enter_stream(stream);
   const size_t esz = dtype_size(dtype);
   const size_t count = args[0].count;
   const size_t bytes = count * esz;
@@ -253,6 +281,7 @@ cudaError_t CudaComm::allreduce(int dtype, std::vector<CollArgs> args, cudaStrea
 cudaError_t CudaComm::reduce(int dtype, std::vector<CollArgs> args, cudaStream_t stream) {
   CCL_CHECK_ARGS(args)
   DeviceGuard g(device_);
+  enter_stream(stream);
   const size_t nvec = (args[0].count * dtype_size(dtype) + 15) / 16;
   size_t stride = cfg_.half_bytes / (16 * (size_t)(world_ + 1));
   stride = compact_stride(stride / 8 * 8, (nvec + world_ - 1) / world_);
@@ -269,6 +298,7 @@ cudaError_t CudaComm::reduce(int dtype, std::vector<CollArgs> args, cudaStream_t
 cudaError_t CudaComm::reduce_scatter(int in_dtype, int out_dtype, std::vector<CollArgs> args, cudaStream_t stream) {
   CCL_CHECK_ARGS(args)
   DeviceGuard g(device_);
+  enter_stream(stream);
   const size_t esz = dtype_size(in_dtype);
   const size_t per_vec = 16 / esz;
   size_t stride = cfg_.half_bytes / (16 * (size_t)world_);
@@ -304,6 +334,7 @@ cudaError_t CudaComm::reduce_scatter(int in_dtype, int out_dtype, std::vector<Co
 cudaError_t CudaComm::all_gather(std::vector<CollArgs> args, cudaStream_t stream) {
   CCL_CHECK_ARGS(args)
   DeviceGuard g(device_);
+  enter_stream(stream);
   size_t maxb = 0;
   for (auto& a : args)
     for (int p = 0; p < world_; ++p) maxb = std::max(maxb, (size_t)a.out_cnt[p]);
@@ -332,6 +363,7 @@ cudaError_t CudaComm::all_gather(std::vector<CollArgs> args, cudaStream_t stream
 cudaError_t CudaComm::all_to_all(std::vector<CollArgs> args, bool uneven, cudaStream_t stream) {
   CCL_CHECK_ARGS(args)
   DeviceGuard g(device_);
+  enter_stream(stream);
   size_t stride = cfg_.half_bytes / (16 * (size_t)world_);
   stride = stride / 8 * 8;
   size_t maxb = 0;
@@ -357,6 +389,7 @@ cudaError_t CudaComm::all_to_all(std::vector<CollArgs> args, bool uneven, cudaSt
 cudaError_t CudaComm::rooted(std::vector<CollArgs> args, cudaStream_t stream) {
   CCL_CHECK_ARGS(args)
   DeviceGuard g(device_);
+  enter_stream(stream);
   const int mode = args[0].mode;
   size_t stride = (mode == kGather) ? cfg_.half_bytes / (16 * (size_t)world_) : cfg_.half_bytes / 16;
   stride = stride / 8 * 8;
@@ -376,6 +409,7 @@ cudaError_t CudaComm::rooted(std::vector<CollArgs> args, cudaStream_t stream) {
 
 cudaError_t CudaComm::barrier(cudaStream_t stream) {
   DeviceGuard g(device_);
+  enter_stream(stream);
   std::vector<CollArgs> args(nctx());
   for (auto& a : args) a.ablate = kAblateNone;
   LaunchCfg lc = launch_cfg(1, 32, stream);
@@ -387,6 +421,7 @@ cudaError_t CudaComm::barrier(cudaStream_t stream) {
 cudaError_t CudaComm::gemm_rs(const std::vector<GemmRsArgs>& args, cudaStream_t stream) {
   CCL_CHECK_ARGS(args)
   DeviceGuard g(device_);
+  enter_stream(stream);
   // every rank's GEMM only pushes and signals; the reduce kernels wait. Played one rank after
   // the other in emulation, which is safe because the pushes never wait.
   for (int i = 0; i < nctx(); ++i) {
@@ -406,6 +441,7 @@ cudaError_t CudaComm::gemm_rs(const std::vector<GemmRsArgs>& args, cudaStream_t 
 cudaError_t CudaComm::ag_gemm(const std::vector<AgGemmArgs>& args, cudaStream_t stream) {
   CCL_CHECK_ARGS(args)
   DeviceGuard g(device_);
+  enter_stream(stream);
   const int ncomm = 8;
   if (!emulated_) {
     cudaError_t e = launch_ag_gemm(host_ctx_[0], args[0], 0, ncomm, stream);
@@ -432,6 +468,7 @@ int CudaComm::moe_capacity(int hidden) const {
 cudaError_t CudaComm::moe_dispatch(std::vector<MoeArgs> args, cudaStream_t stream) {
   CCL_CHECK_ARGS(args)
   DeviceGuard g(device_);
+  enter_stream(stream);
   const int cap = moe_capacity(args[0].hidden);
   if (cap <= 0 || args[0].hidden % 8 != 0) return cudaErrorInvalidValue;
   for (auto& a : args) {
@@ -451,6 +488,7 @@ cudaError_t CudaComm::moe_dispatch(std::vector<MoeArgs> args, cudaStream_t strea
 cudaError_t CudaComm::moe_combine(std::vector<MoeArgs> args, cudaStream_t stream) {
   CCL_CHECK_ARGS(args)
   DeviceGuard g(device_);
+  enter_stream(stream);
   if ((size_t)args[0].tokens * args[0].topk * args[0].hidden * 2 > cfg_.half_bytes) return cudaErrorInvalidValue;
   LaunchCfg lc = launch_cfg(std::min(64, cfg_.max_blocks), 512, stream);
   cudaError_t e = launch_moe_combine(emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
@@ -460,6 +498,7 @@ cudaError_t CudaComm::moe_combine(std::vector<MoeArgs> args, cudaStream_t stream
 
 cudaError_t CudaComm::barrier_single_rank(int i, cudaStream_t stream) {
   DeviceGuard g(device_);
+  enter_stream(stream);
   if (i < 0 || i >= nctx()) return cudaErrorInvalidValue;
   CollArgs a;
   LaunchCfg lc;
@@ -470,9 +509,46 @@ cudaError_t CudaComm::barrier_single_rank(int i, cudaStream_t stream) {
   return launch_barrier(&host_ctx_[i], &a, lc);
 }
 
+void CudaComm::abort() {
+  volatile int* s = status_host_;
+  s[8] = 1;
+}
+void CudaComm::clear_abort() {
+  volatile int* s = status_host_;
+  s[8] = 0;
+}
+bool CudaComm::aborted() const {
+  volatile int* s = status_host_;
+  return s[8] != 0;
+}
+
+bool CudaComm::fits_gemm_ar_norm(int rows, int hidden, int K) const {
+  return rows > 0 && rows <= gemm_ar_norm_max_rows(hidden) && hidden % 128 == 0 && hidden / 8 <= 192 * 6 && K > 0 && K % 8 == 0 &&
+         cfg_.ablate == kAblateNone;
+}
+
+cudaError_t CudaComm::gemm_ar_norm(const std::vector<GemmArNormArgs>& args, cudaStream_t stream) {
+  CCL_CHECK_ARGS(args)
+  DeviceGuard g(device_);
+  enter_stream(stream);
+  cudaError_t e = launch_gemm_ar_norm(host_ctx_.data(), dev_ctx_table_, args.data(), nctx(), stream);
+  if (e == cudaSuccess) ++launches_;
+  return e;
+}
+
+cudaError_t CudaComm::sample_allgather(const std::vector<SampleArgs>& args, cudaStream_t stream) {
+  CCL_CHECK_ARGS(args)
+  DeviceGuard g(device_);
+  enter_stream(stream);
+  cudaError_t e = launch_sample_allgather(host_ctx_.data(), dev_ctx_table_, args.data(), nctx(), stream);
+  if (e == cudaSuccess) ++launches_;
+  return e;
+}
+
 cudaError_t CudaComm::allreduce_residual_rmsnorm(int dtype, std::vector<FusedNormArgs> args, cudaStream_t stream) {
   CCL_CHECK_ARGS(args)
   DeviceGuard g(device_);
+  enter_stream(stream);
   const FusedNormArgs& a0 = args[0];
   if (a0.hidden % 8 != 0 || a0.rows <= 0) return cudaErrorInvalidValue;
   int threads = std::min(512, std::max(32, ((a0.hidden / 8 + 31) / 32) * 32));  // kernel is compiled for <= 512 threads

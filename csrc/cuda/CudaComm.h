@@ -16,11 +16,13 @@
 
 #include <functional>
 #include <memory>
+#include <mutex>
 #include <string>
 #include <vector>
 
 #include "cuda/SymmMem.h"
 #include "cuda/kernels/collectives.h"
+#include "cuda/kernels/decode_fused.h"
 #include "cuda/kernels/gemm_collective.h"
 #include "cuda/kernels/moe_a2a.h"
 
@@ -96,6 +98,20 @@ class CudaComm {
   cudaError_t barrier_single_rank(int i, cudaStream_t stream);
   cudaError_t allreduce_residual_rmsnorm(int dtype, std::vector<FusedNormArgs> args, cudaStream_t stream);
 
+  // Decode step: row-parallel projection + all_reduce + residual + RMSNorm in one launch, and
+  // arg-max + all-gather of the winners (see decode_fused.h). fits_gemm_ar_norm tells whether the
+  // fused kernel takes the shape (else the caller runs GEMM and allreduce_residual_rmsnorm).
+  bool fits_gemm_ar_norm(int rows, int hidden, int K) const;
+  cudaError_t gemm_ar_norm(const std::vector<GemmArNormArgs>& args, cudaStream_t stream);
+  cudaError_t sample_allgather(const std::vector<SampleArgs>& args, cudaStream_t stream);
+
+  // Asks every kernel of this communicator that is (or will be) waiting for a peer to give up:
+  // sets the host-mapped abort word that all bounded waits poll. The waits return within
+  // microseconds with status kStatusAborted; the communicator stays failed until clear_abort().
+  void abort();
+  void clear_abort();
+  bool aborted() const;
+
   // Fused tensor-parallel GEMMs (one entry per rank context, like the collectives).
   cudaError_t gemm_rs(const std::vector<GemmRsArgs>& args, cudaStream_t stream);
   cudaError_t ag_gemm(const std::vector<AgGemmArgs>& args, cudaStream_t stream);
@@ -115,6 +131,7 @@ class CudaComm {
 
  private:
   void init_tables();
+  void enter_stream(cudaStream_t s);
   template <typename ArgsT>
   const ArgsT* upload(const std::vector<ArgsT>& args, cudaStream_t stream);
   LaunchCfg launch_cfg(int nblocks, int nthreads, cudaStream_t stream) const;
@@ -135,6 +152,10 @@ class CudaComm {
   int* status_host_ = nullptr;        // pinned + mapped
   int* status_dev_ = nullptr;
   uint64_t launches_ = 0;
+  std::mutex order_mu_;
+  cudaEvent_t order_ev_ = nullptr;
+  cudaStream_t last_stream_ = nullptr;
+  bool has_last_stream_ = false;
   Algo last_algo_ = Algo::kAuto;
 };
 

@@ -15,6 +15,7 @@
 // release flag; pulls are system-coherent 16-byte loads from the peer's arena after an acquire.
 #include "collectives.h"
 #include "comm.cuh"
+#include "ll_norm.cuh"
 #include "gemm.h"
 
 #include <cstdio>
@@ -871,10 +872,6 @@ struct LaunchNorm {
   const FusedNormArgs* args_table;
 };
 
-template <typename T> __device__ __forceinline__ T round_to(float v);
-template <> __device__ __forceinline__ __nv_bfloat16 round_to<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
-template <> __device__ __forceinline__ __half round_to<__half>(float v) { return __float2half(v); }
-
 constexpr int kNormMaxVecPerThread = 4;
 
 template <typename T, bool EMU>
@@ -887,11 +884,17 @@ __global__ void __launch_bounds__(512) allreduce_residual_rmsnorm_kernel(const _
   constexpr int N = 8;
   const int W = ctx.world, me = ctx.rank;
   const int hv = a.hidden / N;  // vectors per row
-  const T* x = reinterpret_cast<const T*>(a.x);
-  T* res = reinterpret_cast<T*>(a.residual);
-  const T* wgt = reinterpret_cast<const T*>(a.weight);
-  T* out = reinterpret_cast<T*>(a.out);
-  const size_t slot = round_up((size_t)a.rows * a.hidden * sizeof(T), 128);
+  const char* x = reinterpret_cast<const char*>(a.x);
+  char* res = reinterpret_cast<char*>(a.residual);
+  char* out = reinterpret_cast<char*>(a.out);
+  const size_t row_bytes = (size_t)a.hidden * sizeof(T);
+  const size_t slot = round_up((size_t)a.rows * row_bytes, 128);
+  // this rank's contribution to a row: the row itself, or (embedding lookup) a table row / zeros
+  auto x_row = [&](int row) -> const char* {
+    if (!a.gather_tokens) return x + (size_t)row * row_bytes;
+    const long long idx = a.gather_tokens[row] - a.gather_base;
+    return (idx >= 0 && idx < a.gather_rows) ? x + (size_t)idx * row_bytes : nullptr;
+  };
 
   const bool ll = a.use_ll != 0 && W > 1;
   const uint32_t llflag = sy.epoch + 1;
@@ -899,25 +902,26 @@ __global__ void __launch_bounds__(512) allreduce_residual_rmsnorm_kernel(const _
     // low-latency push: each 16-byte store = {payload, epoch, payload, epoch}; the receiver polls the
     // payload slots themselves, so there is no release fence and no flag round trip
     for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
+      const char* src = x_row(row);
       for (int i = threadIdx.x; i < hv; i += blockDim.x) {
-        const size_t off = ((size_t)row * hv + i) * 16;
-        const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + off);
-        const uint4 s0 = make_uint4(v.x, llflag, v.y, llflag), s1 = make_uint4(v.z, llflag, v.w, llflag);
+        const size_t off = (size_t)row * row_bytes + (size_t)i * 16;
+        const uint4 v = src ? *reinterpret_cast<const uint4*>(src + (size_t)i * 16) : make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int p = 0; p < kMaxRanks; ++p) {
           if (p < W && p != me) {
-            char* dst = ctx.ll[p] + ((size_t)sy.parity(0) * kMaxRanks + me) * kLLSlotBytes + off * 2;
-            ptx::st_v4(dst, s0);
-            ptx::st_v4(dst + 16, s1);
+            char* dst = ll_slot(ctx, p, sy.parity(0), me);
+            ll_store8(dst, off, v.x, v.y, llflag);
+            ll_store8(dst, off + 8, v.z, v.w, llflag);
           }
         }
       }
     }
   } else if (W > 1 && a.ablate != kAblateSyncOnly) {
     for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
+      const char* src = x_row(row);
       for (int i = threadIdx.x; i < hv; i += blockDim.x) {
-        const size_t off = ((size_t)row * hv + i) * 16;
-        const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + off);
+        const size_t off = (size_t)row * row_bytes + (size_t)i * 16;
+        const uint4 v = src ? *reinterpret_cast<const uint4*>(src + (size_t)i * 16) : make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int p = 0; p < kMaxRanks; ++p)
           if (p < W && p != me) ptx::st_v4(sy.half(p, 0) + (size_t)me * slot + off, v);
@@ -930,90 +934,65 @@ __global__ void __launch_bounds__(512) allreduce_residual_rmsnorm_kernel(const _
     ok = sy.wait_all(0, 0);
   }
   if (ok && a.ablate != kAblateSyncOnly) {
-    const char* mine = sy.half(me, 0);
     // the norm weights do not depend on the reduction: fetch them first so that their latency
     // overlaps the peer waits and the block reduction
     Vec<T> wv[kNormMaxVecPerThread];
+    ll_load_norm_weight<T, kNormMaxVecPerThread>(a.weight, a.hidden, wv);
+    if (ll || W == 1) {
+      for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
+        char* rrow = res + (size_t)row * row_bytes;
+        ll_row_residual_norm<T, kNormMaxVecPerThread, 4>(ctx, sy.parity(0), llflag, W == 1 ? kLocalOnly : kOwnPtr, (size_t)row * row_bytes,
+                                                      a.hidden, x_row(row), a.zero_residual ? nullptr : rrow, rrow,
+                                                      out + (size_t)row * row_bytes, wv, a.eps, s_red);
+      }
+    } else {
+      // larger inputs (prefill): the peers' rows were staged in the data half and published by the flag round
+      const char* mine = sy.half(me, 0);
+      for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
+        const char* src = x_row(row);
+        float h[kNormMaxVecPerThread][N];
+        float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < kNormMaxVecPerThread; ++k) {
-      const int i = threadIdx.x + k * blockDim.x;
-      if (i < hv) *reinterpret_cast<uint4*>(&wv[k]) = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(wgt) + (size_t)i * 16);
-    }
-    for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
-      float h[kNormMaxVecPerThread][N];
-      float ss = 0.f;
+        for (int k = 0; k < kNormMaxVecPerThread; ++k) {
+          const int i = threadIdx.x + k * blockDim.x;
+          if (i < hv) {
+            const size_t off = (size_t)row * row_bytes + (size_t)i * 16;
+            float acc[N];
 #pragma unroll
-      for (int k = 0; k < kNormMaxVecPerThread; ++k) {
-        const int i = threadIdx.x + k * blockDim.x;
-        if (i < hv) {
-          const size_t off = ((size_t)row * hv + i) * 16;
-          float acc[N];
+            for (int p = 0; p < kMaxRanks; ++p) {
+              if (p < W) {
+                Vec<T> v;
+                if (p == me)
+                  *reinterpret_cast<uint4*>(&v) = src ? *reinterpret_cast<const uint4*>(src + (size_t)i * 16) : make_uint4(0, 0, 0, 0);
+                else
+                  v = load_stage<T>(mine + (size_t)p * slot + off);
 #pragma unroll
-          for (int p = 0; p < kMaxRanks; ++p) {
-            if (p < W) {
-              Vec<T> v;
-              if (p == me) {
-                *reinterpret_cast<uint4*>(&v) = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + off);
-              } else if (ll) {
-                const char* src = ctx.ll[me] + ((size_t)sy.parity(0) * kMaxRanks + p) * kLLSlotBytes + off * 2;
-                uint4 s0 = ptx::ld_volatile_v4(src), s1 = ptx::ld_volatile_v4(src + 16);
-                if (!(s0.y == llflag && s0.w == llflag && s1.y == llflag && s1.w == llflag)) {
-                  const uint64_t t0 = ptx::globaltimer_ns();
-                  uint32_t it = 0;
-                  while (true) {
-                    s0 = ptx::ld_volatile_v4(src);
-                    s1 = ptx::ld_volatile_v4(src + 16);
-                    if (s0.y == llflag && s0.w == llflag && s1.y == llflag && s1.w == llflag) break;
-                    if ((++it & 63u) == 0 && ptx::globaltimer_ns() - t0 > ctx.spin_ns) {
-                      sy.report(p, 0);
-                      break;
-                    }
-                  }
-                }
-                *reinterpret_cast<uint4*>(&v) = make_uint4(s0.x, s0.z, s1.x, s1.z);
-              } else {
-                v = load_stage<T>(mine + (size_t)p * slot + off);
+                for (int t = 0; t < N; ++t) acc[t] = (p == 0) ? to_acc(v.v[t]) : acc[t] + to_acc(v.v[t]);
               }
-#pragma unroll
-              for (int t = 0; t < N; ++t) acc[t] = (p == 0) ? to_acc(v.v[t]) : acc[t] + to_acc(v.v[t]);
             }
-          }
-          Vec<T> r;
-          *reinterpret_cast<uint4*>(&r) = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(res) + off);
-          Vec<T> hn;
+            Vec<T> r, hn;
+            if (!a.zero_residual) *reinterpret_cast<uint4*>(&r) = *reinterpret_cast<const uint4*>(res + off);
 #pragma unroll
-          for (int t = 0; t < N; ++t) {
-            const float s = to_acc(round_to<T>(acc[t]));        // all_reduce output, rounded
-            const T hr = round_to<T>(s + to_acc(r.v[t]));       // residual add, rounded
-            hn.v[t] = hr;
-            h[k][t] = to_acc(hr);
-            ss += h[k][t] * h[k][t];
+            for (int t = 0; t < N; ++t) {
+              const float s = to_acc(ll_round_to<T>(acc[t]));                                        // all_reduce output, rounded
+              const T hr = a.zero_residual ? ll_round_to<T>(s) : ll_round_to<T>(s + to_acc(r.v[t]));  // residual add, rounded
+              hn.v[t] = hr;
+              h[k][t] = to_acc(hr);
+              ss += h[k][t] * h[k][t];
+            }
+            *reinterpret_cast<uint4*>(res + off) = *reinterpret_cast<const uint4*>(&hn);
           }
-          *reinterpret_cast<uint4*>(reinterpret_cast<char*>(res) + off) = *reinterpret_cast<const uint4*>(&hn);
         }
-      }
-      // block reduction of the sum of squares
+        const float rstd = rsqrtf(block_sum(ss, s_red) / (float)a.hidden + a.eps);
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      __syncthreads();
-      if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = ss;
-      __syncthreads();
-      if (threadIdx.x < 32) {
-        float t = (threadIdx.x < (blockDim.x + 31) / 32) ? s_red[threadIdx.x] : 0.f;
+        for (int k = 0; k < kNormMaxVecPerThread; ++k) {
+          const int i = threadIdx.x + k * blockDim.x;
+          if (i < hv) {
+            Vec<T> o;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-        if (threadIdx.x == 0) s_red[32] = t;
-      }
-      __syncthreads();
-      const float rstd = rsqrtf(s_red[32] / (float)a.hidden + a.eps);
-#pragma unroll
-      for (int k = 0; k < kNormMaxVecPerThread; ++k) {
-        const int i = threadIdx.x + k * blockDim.x;
-        if (i < hv) {
-          Vec<T> o;
-#pragma unroll
-          for (int t = 0; t < N; ++t) o.v[t] = round_to<T>(to_acc(round_to<T>(h[k][t] * rstd)) * to_acc(wv[k].v[t]));
-          *reinterpret_cast<uint4*>(reinterpret_cast<char*>(out) + ((size_t)row * hv + i) * 16) = *reinterpret_cast<const uint4*>(&o);
+            for (int t = 0; t < N; ++t) o.v[t] = ll_round_to<T>(to_acc(ll_round_to<T>(h[k][t] * rstd)) * to_acc(wv[k].v[t]));
+            *reinterpret_cast<uint4*>(out + (size_t)row * row_bytes + (size_t)i * 16) = *reinterpret_cast<const uint4*>(&o);
+          }
         }
       }
     }

@@ -80,6 +80,14 @@ struct FusedNormArgs {
   float eps = 1e-5f;
   int ablate = kAblateNone;
   int use_ll = 0;   // 1: low-latency protocol (rows * hidden * 4 bytes must fit kLLSlotBytes)
+  // Vocabulary-parallel embedding lookup fused in front (decode step start): when gather_tokens
+  // is set, `x` is this rank's shard [gather_rows, hidden] of the embedding table and the
+  // contribution of row i is x[gather_tokens[i] - gather_base] if that index falls inside the
+  // shard, else zeros.
+  const long long* gather_tokens = nullptr;
+  long long gather_base = 0;
+  int gather_rows = 0;
+  int zero_residual = 0;   // 1: the incoming residual counts as zero and is not read
 };
 cudaError_t launch_allreduce_residual_rmsnorm(int dtype, const RankCtx* ctx, const FusedNormArgs* args, const LaunchCfg& cfg);
 

@@ -65,6 +65,11 @@ __device__ __forceinline__ bool dbg_in_bounds(const void* ptr, int is_store) {
 #define CCL_BOUNDS_CHECKED 0
 #endif
 
+// True once the host has asked the communicator's kernels to give up (ProcessGroup abort()).
+__device__ __forceinline__ bool comm_aborted(const RankCtx& c) {
+  return c.abort_flag != nullptr && *reinterpret_cast<const volatile int*>(c.abort_flag) != 0;
+}
+
 // Per-CTA protocol helper.
 struct Sync {
   const RankCtx& ctx;
@@ -113,7 +118,7 @@ struct Sync {
   __device__ __forceinline__ bool wait_all(int phase, int round) {
     if (sync_enabled && threadIdx.x < ctx.world && (int)threadIdx.x != ctx.rank && *failed == 0) {
       const uint32_t* f = flag_ptr(ctx.flags[ctx.rank], phase, threadIdx.x, blk);
-      if (!ptx::spin_until_epoch(f, epoch + round + 1, ctx.spin_ns)) report(threadIdx.x, phase);
+      if (!ptx::spin_until_epoch(f, epoch + round + 1, ctx.spin_ns, ctx.abort_flag)) report(threadIdx.x, phase);
     }
     __syncthreads();
     return *failed == 0;
@@ -121,14 +126,15 @@ struct Sync {
   __device__ __forceinline__ bool wait_one(int peer, int phase, int round) {
     if (sync_enabled && threadIdx.x == 0 && peer != ctx.rank && *failed == 0) {
       const uint32_t* f = flag_ptr(ctx.flags[ctx.rank], phase, peer, blk);
-      if (!ptx::spin_until_epoch(f, epoch + round + 1, ctx.spin_ns)) report(peer, phase);
+      if (!ptx::spin_until_epoch(f, epoch + round + 1, ctx.spin_ns, ctx.abort_flag)) report(peer, phase);
     }
     __syncthreads();
     return *failed == 0;
   }
   __device__ void report(int peer, int phase) {
     *failed = 1;
-    if (ctx.status && atomicCAS(ctx.status, kStatusOk, kStatusTimeout) == kStatusOk) {
+    const int code = comm_aborted(ctx) ? kStatusAborted : kStatusTimeout;
+    if (ctx.status && atomicCAS(ctx.status, kStatusOk, code) == kStatusOk) {
       ctx.status[1] = ctx.rank;
       ctx.status[2] = peer;
       ctx.status[3] = phase;

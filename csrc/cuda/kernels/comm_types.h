@@ -18,13 +18,14 @@ constexpr size_t kLLSlotBytes = 512 << 10;
 constexpr size_t kLLBytes = 2 * kMaxRanks * kLLSlotBytes;  // epoch, ticket, scratch tables (all-to-all counts, ...)
 
 // Status codes written to RankCtx::status[0]; status[1..3] = rank, peer, phase.
-enum : int { kStatusOk = 0, kStatusTimeout = 1, kStatusBounds = 2 };
+enum : int { kStatusOk = 0, kStatusTimeout = 1, kStatusBounds = 2, kStatusAborted = 3 };
 
 struct RankCtx {
   char* data[kMaxRanks];        // peers' arena base addresses as mapped in this rank
   uint32_t* flags[kMaxRanks];   // peers' flag areas
   uint32_t* state;              // own state words: [0] epoch, [1] ticket, [16..] scratch
   int* status;                  // host-visible error record (4 ints)
+  int* abort_flag;              // host-written word (mapped host memory): non-zero makes every bounded wait give up
   unsigned long long half_bytes;  // size of one data half
   unsigned long long spin_ns;     // wait budget
   char* ll[kMaxRanks];          // peers' low-latency regions

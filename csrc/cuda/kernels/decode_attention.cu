@@ -90,6 +90,14 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const Decode
   const int j = tid & 7;   // dim slice within the head
   const int kvh = h / (p.n_heads / p.n_kv_heads);
   const int pos = p.positions[b];  // the new token's position; attends over [0, pos]
+  if (pos < 0 || pos >= p.max_seq) {
+    // a position outside the cache would index the cache and the rotary tables out of bounds:
+    // record it, write nothing to the cache and emit a zero row (uniform for the whole CTA, and
+    // every split of this (sequence, head) takes the same exit, so the arrival counter stays 0)
+    if (tid == 0 && p.status) atomicExch(p.status, 201);
+    if (split == 0) p.out[(size_t)b * p.out_stride + (size_t)h * kHD + tid] = __float2bfloat16(0.f);
+    return;
+  }
   const int total = pos + 1;
   const int per = (total + nsplit - 1) / nsplit;
   const int t0 = split * per;
@@ -291,17 +299,30 @@ int decode_attention_default_splits(int batch, int n_heads, int max_context) {
   return s;
 }
 
+// The kernel moves q/k/v, the cache rows and the output with 16-byte accesses and bulk copies:
+// every base pointer must be 16-byte aligned, both row strides multiples of 8 elements, and a
+// row must not overlap the next one.
+bool decode_attention_layout_ok(const DecodeAttnParams& p) {
+  auto aligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (!aligned(p.qkv) || !aligned(p.k_cache) || !aligned(p.v_cache) || !aligned(p.out)) return false;
+  if (p.qkv_stride % 8 != 0 || p.out_stride % 8 != 0) return false;
+  if (p.qkv_stride < (long long)(p.n_heads + 2 * p.n_kv_heads) * kHD) return false;
+  if (p.out_stride < (long long)p.n_heads * kHD) return false;
+  return true;
+}
+
 cudaError_t decode_attention(const DecodeAttnParams& p, int batch, int nsplit, cudaStream_t stream) {
   if (p.head_dim != kHD) return cudaErrorInvalidValue;
   if (nsplit > 1 && (!p.scratch || !p.counters)) return cudaErrorInvalidValue;
+  if (!decode_attention_layout_ok(p)) return cudaErrorInvalidValue;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(nsplit, p.n_heads, batch);
   cfg.blockDim = dim3(kThreads, 1, 1);
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;  // the shared-memory opt-in is a per-device attribute
+  if (configured.pending()) {
     cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDynSmem);
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured.done();
   }
   cfg.dynamicSmemBytes = kDynSmem;
   cfg.stream = stream;
@@ -362,6 +383,20 @@ extern "C" __attribute__((visibility("default"))) int ccl_decode_attention_noall
     return noalloc_fail(1, "ccl_decode_attention_noalloc: batch * n_heads * nsplit = " + std::to_string(partials) +
                                " exceeds the built-in scratch of " + std::to_string(CCL_NOALLOC_MAX_PARTIALS) +
                                " partial results; lower nsplit or use the entry point that takes a caller-provided scratch buffer");
+  {
+    ccl::DecodeAttnParams chk{};
+    chk.qkv = static_cast<const __nv_bfloat16*>(qkv);
+    chk.qkv_stride = qkv_stride;
+    chk.k_cache = static_cast<__nv_bfloat16*>(k_cache);
+    chk.v_cache = static_cast<__nv_bfloat16*>(v_cache);
+    chk.out = static_cast<__nv_bfloat16*>(out);
+    chk.out_stride = out_stride;
+    chk.n_heads = n_heads;
+    chk.n_kv_heads = n_kv_heads;
+    if (!ccl::decode_attention_layout_ok(chk))
+      return noalloc_fail(2, "ccl_decode_attention_noalloc: qkv, k_cache, v_cache and out must be 16-byte aligned, qkv_stride and "
+                             "out_stride multiples of 8 elements and at least (n_heads + 2 * n_kv_heads) * 128 and n_heads * 128");
+  }
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return noalloc_fail(3, std::string("cudaGetDevice: ") + cudaGetErrorString(e));

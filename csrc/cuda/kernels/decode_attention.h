@@ -25,6 +25,11 @@ struct DecodeAttnParams {
 
 size_t decode_attention_scratch_bytes(int batch, int n_heads, int nsplit);
 int decode_attention_default_splits(int batch, int n_heads, int max_context);
+// Pointer alignment (16 bytes) and row-stride rules of the kernel; decode_attention() refuses a
+// launch that breaks them with cudaErrorInvalidValue. A position outside [0, max_seq) is caught on
+// the device: that sequence's output row is zero, its cache is untouched and `status` (if given)
+// is set to 201.
+bool decode_attention_layout_ok(const DecodeAttnParams& p);
 cudaError_t decode_attention(const DecodeAttnParams& p, int batch, int nsplit, cudaStream_t stream);
 
 }  // namespace ccl

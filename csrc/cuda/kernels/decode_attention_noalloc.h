@@ -22,7 +22,12 @@
 //     left there. The entry point clears the part that has to start at zero (the arrival
 //     counters) on the caller's stream before launching. Two calls that overlap on the same GPU
 //     (different streams, or different threads) race on the array: serialise them.
-//   * Inputs and outputs are the caller's, exactly as for the regular entry point.
+//   * Inputs and outputs are the caller's, exactly as for the regular entry point: qkv, the two
+//     caches and out 16-byte aligned, both row strides multiples of 8 elements and no shorter
+//     than a row. A call that breaks this returns 2 and launches nothing. A position outside
+//     [0, max_seq) gives a zero output row and leaves the caches alone.
+//   * Several GPUs in one process: each device resolves the array and configures the kernel on
+//     its own first call, with that device current.
 #pragma once
 #include <stddef.h>
 

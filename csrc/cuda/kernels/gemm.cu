@@ -70,11 +70,11 @@ cudaError_t launch_persistent(const GemmDesc& d, cudaStream_t stream) {
   p.splitk = 1;
   p.status = d.status;
   auto kern = gemm_persistent_kernel<BN, OutT>;
-  static thread_local bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;
+  if (configured.pending()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax + 2048);
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured.done();
   }
   int sms = 148;
   const int total = m_tiles * n_tiles;
@@ -106,14 +106,14 @@ cudaError_t launch(const GemmDesc& d, int splitk, cudaStream_t stream) {
 
   constexpr size_t kSmemMax = 200 * 1024;
   auto kern = gemm_kernel<BN, DUAL, OutT>;
-  static thread_local size_t configured = 0;
-  if (configured == 0) {
+  static DeviceOnce configured;
+  if (configured.pending()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax + 2048);
     if (e != cudaSuccess) return e;
     // the kernel keeps nothing in L1: give shared memory the whole array so that two CTAs fit
     e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
-    configured = kSmemMax + 2048;
+    configured.done();
   }
   // split-K: bounded by the portable cluster size and by the amount of K work per CTA
   if (splitk > 8) splitk = 8;

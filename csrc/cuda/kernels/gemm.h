@@ -3,7 +3,29 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace ccl {
+
+// Kernel attributes (cudaFuncSetAttribute) are per device. A launcher keeps one DeviceOnce per
+// kernel instantiation: `pending()` is true until `done()` was called with the calling thread's
+// current device, so a process that drives several GPUs configures each of them exactly once.
+class DeviceOnce {
+ public:
+  bool pending() const {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return (mask_.load(std::memory_order_acquire) & (1ull << (dev & 63))) == 0;
+  }
+  void done() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    mask_.fetch_or(1ull << (dev & 63), std::memory_order_release);
+  }
+
+ private:
+  std::atomic<uint64_t> mask_{0};
+};
 
 // D[M, N] = A[M, K] · B[N, K]^T with bf16 operands (K contiguous) and fp32 accumulation.
 // A occupies the 128-row UMMA M side, B the UMMA N side (tile width `bn`, a multiple of 16).

@@ -23,6 +23,7 @@
 #include "gemm_collective.h"
 
 #include "comm.cuh"
+#include "gemm.h"
 #include "gemm_tcgen05.cuh"
 #include "tma_desc.h"
 
@@ -100,7 +101,7 @@ __global__ void __launch_bounds__(1024) gemm_rs_reduce_kernel(const __grid_const
   const int W = ctx.world, me = ctx.rank;
   if ((int)threadIdx.x < W) {
     const uint32_t target = ctx.state[kRsStateBase + threadIdx.x] + a.tiles_per_src;
-    if (!ptx::spin_until_epoch(flag_ptr(ctx.flags[me], 4, threadIdx.x, kRsCounterBlk), target, ctx.spin_ns))
+    if (!ptx::spin_until_epoch(flag_ptr(ctx.flags[me], 4, threadIdx.x, kRsCounterBlk), target, ctx.spin_ns, ctx.abort_flag))
       sy.report(threadIdx.x, 4);
   }
   __syncthreads();
@@ -195,7 +196,7 @@ __global__ void __launch_bounds__(gemm::kThreads, 1)
       int ok = 1;
       if (s != me) {
         const uint32_t target = ctx.state[kAgStateBase + s] + (uint32_t)info.ncomm;
-        if (!ptx::spin_until_epoch(flag_ptr(ctx.flags[me], 4, s, kAgCounterBlk), target, ctx.spin_ns)) {
+        if (!ptx::spin_until_epoch(flag_ptr(ctx.flags[me], 4, s, kAgCounterBlk), target, ctx.spin_ns, ctx.abort_flag)) {
           ok = 0;
           if (ctx.status && atomicCAS(ctx.status, kStatusOk, kStatusTimeout) == kStatusOk) {
             ctx.status[1] = me;
@@ -229,9 +230,14 @@ __global__ void __launch_bounds__(gemm::kThreads, 1)
   }
 }
 
+// Opts one kernel instantiation into large dynamic shared memory, once per device.
 template <typename K>
 cudaError_t set_smem(K kern, size_t smem) {
-  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static DeviceOnce configured;  // one per instantiation of this template, i.e. per kernel
+  if (!configured.pending()) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e == cudaSuccess) configured.done();
+  return e;
 }
 
 int pick_stages(int bn, int k_iters, size_t* smem_out) {

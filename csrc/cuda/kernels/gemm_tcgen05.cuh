@@ -286,6 +286,10 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const C
       if (p.status) atomicExch(p.status, 103);
     }
     ptx::tc_fence_after();
+    // the producer already waited for the predecessor grid before it fetched B; the epilogue
+    // threads repeat the (by now satisfied) wait so that whatever they read or overwrite from an
+    // earlier kernel is ordered for them too
+    ptx::griddep_wait();
     if (p.splitk > 1) {
       // reduce-scatter: send this row's partial to the CTA that owns the row
       // (buffer layout at the owner: [source slot][column group of 4][local row] float4)

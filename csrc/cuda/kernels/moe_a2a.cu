@@ -45,7 +45,7 @@ __device__ __forceinline__ bool wait_all_blocks(Sync& sy, int phase, int nblk) {
     const int src = i / nblk, b = i - src * nblk;
     if (*sy.failed) continue;  // the own rank's CTAs are waited for too: they fill the local segment
     const uint32_t* f = flag_ptr(sy.ctx.flags[sy.ctx.rank], phase, src, b);
-    if (!ptx::spin_until_epoch(f, sy.epoch + 1, sy.ctx.spin_ns)) sy.report(src, phase);
+    if (!ptx::spin_until_epoch(f, sy.epoch + 1, sy.ctx.spin_ns, sy.ctx.abort_flag)) sy.report(src, phase);
   }
   __syncthreads();
   return *sy.failed == 0;
@@ -143,7 +143,9 @@ __global__ void __launch_bounds__(512) moe_dispatch_kernel(const __grid_constant
       uint4* dst = reinterpret_cast<uint4*>(a.out_x) + (size_t)r * hv;
       for (int v = lane; v < hv; v += 32) dst[v] = ptx::ld_relaxed_sys_v4(src + (size_t)v * 16);
       if (lane == 0) {
-        const int2 rec = *reinterpret_cast<const int2*>(slot + meta_off(a) + (size_t)i * 8);
+        // written by the source GPU: same system-coherent load as the rows above
+        const uint32_t* recp = reinterpret_cast<const uint32_t*>(slot + meta_off(a) + (size_t)i * 8);
+        const int2 rec = make_int2((int)ptx::ld_relaxed_sys(recp), (int)ptx::ld_relaxed_sys(recp + 1));
         a.out_meta[3 * r] = s;        // source rank
         a.out_meta[3 * r + 1] = rec.x;  // slot t*K+k at the source
         a.out_meta[3 * r + 2] = rec.y;  // local expert

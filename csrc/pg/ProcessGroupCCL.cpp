@@ -395,6 +395,24 @@ c10::intrusive_ptr<Work> ProcessGroupCCL::endCoalescing() {
   }
   auto works = std::move(coalesced_works_);
   coalesced_works_.clear();
+  int cuda_dev = -1;
+  std::vector<c10::intrusive_ptr<Work>> host_works;
+  for (auto& w : works) {
+    auto* aw = dynamic_cast<AsyncWorkCCL*>(w.get());
+    const int d = aw ? aw->cudaDevice() : -1;
+    if (d >= 0) cuda_dev = d;
+    else host_works.push_back(w);
+  }
+  if (cuda_dev >= 0) {
+    // CUDA collectives were issued in the window: the returned Work must order the CALLER's
+    // stream after them. A marker launch on the communication stream does exactly that: its end
+    // event is recorded after the last inner op, wait() / synchronize() make the current stream
+    // wait for it, and the watchdog retires it. Host-side work of a mixed window is finished first.
+    for (auto& w : host_works) w->wait();
+    const at::Device dev(at::kCUDA, (c10::DeviceIndex)cuda_dev);
+    return cudaImpl(dev).run(OpType::COALESCED, "oneccl_bindings_for_pytorch::end_coalescing", dev,
+                             [](ccl::CudaComm&, cudaStream_t) { return std::string("marker"); }, {}, {}, {}, false, 0);
+  }
   const uint64_t seq = nextSeq();
   auto work = c10::make_intrusive<AsyncWorkCCL>(rank_, OpType::COALESCED, "oneccl_bindings_for_pytorch::end_coalescing", seq);
   work->setOutputs(std::vector<at::Tensor>{});
@@ -402,15 +420,32 @@ c10::intrusive_ptr<Work> ProcessGroupCCL::endCoalescing() {
     work->finishOk();
     return work;
   }
-  // completes when every work issued inside the coalescing window has completed
-  std::thread([work, works]() {
-    try {
-      for (auto& w : works) w->wait();
-      work->finishOk();
-    } catch (...) {
-      work->finishError(std::current_exception());
-    }
-  }).detach();
+  // Host-side work only: the window's Work completes when the last inner work does, from the
+  // thread that completes it (a callback on each inner future) - no helper thread per call.
+  struct Pending {
+    std::atomic<int> left;
+    std::mutex mu;
+    std::exception_ptr err;
+  };
+  auto pending = std::make_shared<Pending>();
+  pending->left.store((int)works.size());
+  for (auto& w : works) {
+    w->getFuture()->addCallback([work, pending](c10::ivalue::Future& f) {
+      if (f.hasError()) {
+        std::lock_guard<std::mutex> g(pending->mu);
+        if (!pending->err) pending->err = f.exception_ptr();
+      }
+      if (pending->left.fetch_sub(1) == 1) {
+        std::exception_ptr e;
+        {
+          std::lock_guard<std::mutex> g(pending->mu);
+          e = pending->err;
+        }
+        if (e) work->finishError(e);
+        else work->finishOk();
+      }
+    });
+  }
   return work;
 }
 

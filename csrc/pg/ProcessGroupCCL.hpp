@@ -50,6 +50,8 @@ class ProcessGroupCCL : public Backend {
     float getDuration() const override { return duration_ms_; }
     void abort() override;
     bool isAborted() const { return aborted_.load(); }
+    // Index of the CUDA device the work's kernels run on, or -1 for host-side work.
+    virtual int cudaDevice() const { return -1; }
     // Polls for completion for a few tens of microseconds before blocking on the condition
     // variable: a small CPU collective finishes sooner than a sleeping thread wakes up.
     bool wait(std::chrono::milliseconds timeout = kNoTimeout) override;

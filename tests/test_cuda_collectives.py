@@ -283,3 +283,145 @@ def _fsdp_engine(rank, world):
 
 def test_cuda_fsdp_engine_and_moe_ops():
     run_ranks(_fsdp_engine, world=_world(), device="cuda", env={"NCCL_NVLS_ENABLE": "0", "CCL_ARENA_MB": "64", "CCL_SPIN_TIMEOUT_MS": "3000"}, timeout=120)
+
+
+def _tp_decode(rank, world):
+    """Tensor-parallel decode on real peers: the fused step (projection + all_reduce + residual + norm in one
+    kernel, fused sampling) against the fp32 restatement over plain all_reduces, eager and from a CUDA graph,
+    and against the unfused kernels."""
+    from torch_ccl_b200.models.llama import LlamaConfig, TPLlamaDecoder
+
+    cfg = LlamaConfig(vocab=1024, hidden=512, n_layers=2, n_heads=8, n_kv_heads=8, inter=1408 if world != 8 else 2048)
+    B = 4
+    m = TPLlamaDecoder(cfg, max_batch=B, max_seq=256, seed=3)
+    u = TPLlamaDecoder(cfg, max_batch=B, max_seq=256, seed=3, fused=False)
+    assert m.fused and not u.fused
+    prompt = torch.randint(0, cfg.vocab, (B, 40), generator=torch.Generator().manual_seed(5))
+    m.prefill(prompt)
+    u.prefill(prompt)
+    assert torch.equal(m.tokens, u.tokens)
+    for step in range(3):
+        u.tokens.copy_(m.tokens)
+        ref = m.reference_decode_step(B)
+        m.decode_step(B)
+        u.decode_step(B)
+        torch.cuda.synchronize()
+        torch.testing.assert_close(m.logits[:B], ref, rtol=3e-2, atol=3e-2)
+        # same rounding points, but the split-K factor (and so the fp32 summation order) may differ
+        torch.testing.assert_close(m.logits[:B], u.logits[:B], rtol=2e-2, atol=2e-2)
+    e = TPLlamaDecoder(cfg, max_batch=B, max_seq=256, seed=3)
+    e.prefill(prompt)
+    for L1, L2 in zip(e.layers, m.layers):  # bring the eager twin to the same state as m
+        L1["k"].copy_(L2["k"])
+        L1["v"].copy_(L2["v"])
+    e.tokens.copy_(m.tokens)
+    e.positions.copy_(m.positions)
+    m.capture(B)
+    for step in range(4):
+        a = m.decode_step(B).clone()
+        b = e.decode_step(B).clone()
+        assert torch.equal(a, b), "graph replay and eager launches of the fused step must agree bit for bit"
+    assert int(m.positions[0]) == 40 + 7
+    # every rank holds the same sampled ids
+    g = [torch.empty_like(a) for _ in range(world)]
+    dist.all_gather(g, a)
+    for t in g:
+        assert torch.equal(t, g[0])
+    be = dist.group.WORLD._get_backend(torch.device("cuda"))
+    assert be.cuda_comm_status(a)[0] == 0
+    dist.barrier()
+
+
+def test_cuda_tp_decode_fused():
+    run_ranks(_tp_decode, world=_world(), device="cuda", env={"NCCL_NVLS_ENABLE": "0", "CCL_ARENA_MB": "64", "CCL_SPIN_TIMEOUT_MS": "5000"}, timeout=300)
+
+
+def _streams_and_coalescing(rank, world):
+    """Ordering across streams: a coalescing window of CUDA collectives issued from a side stream must order that
+    stream after them, and a fused op on the caller's stream must not overlap a c10d op still in flight on the
+    backend's communication stream (both use the same communicator state)."""
+    from torch.distributed.distributed_c10d import _coalescing_manager
+
+    from torch_ccl_b200 import ops
+
+    side = torch.cuda.Stream()
+    n = 1 << 20
+    for it in range(5):
+        with torch.cuda.stream(side):
+            a = torch.full((n,), float(rank + it), device="cuda")
+            b = torch.full((n,), float(rank), device="cuda")
+            with _coalescing_manager(device=torch.device("cuda"), async_ops=True) as cm:
+                dist.all_reduce(a)
+                dist.broadcast(b, src=world - 1)
+            cm.wait()
+            # consumers on the side stream: must see the finished collectives
+            sa, sb = a.sum(), b.sum()
+        side.synchronize()
+        assert float(sa) == float(n) * (sum(range(world)) + world * it), (float(sa), it)
+        assert float(sb) == float(n) * (world - 1)
+    # async c10d op followed at once by a fused op on the current stream
+    for it in range(5):
+        big = torch.ones(4 << 20, device="cuda")
+        w = dist.all_reduce(big, async_op=True)
+        small = torch.full((1000,), 2.0, device="cuda")
+        ops.all_reduce_scaled(small, 0.5)
+        w.wait()
+        torch.cuda.synchronize()
+        assert float(big[-1]) == world and float(small[0]) == world
+    be = dist.group.WORLD._get_backend(torch.device("cuda"))
+    assert be.cuda_comm_status(big)[0] == 0
+    dist.barrier()
+
+
+def test_cuda_streams_and_coalescing():
+    run_ranks(_streams_and_coalescing, world=_world(), device="cuda", env={"NCCL_NVLS_ENABLE": "0", "CCL_ARENA_MB": "64", "CCL_SPIN_TIMEOUT_MS": "5000"}, timeout=300)
+
+
+def test_kernels_configure_each_device():
+    """One process, two GPUs: the shared-memory opt-in of a kernel is a per-device attribute, so the GEMM, the
+    attention and the allocation-free attention entry point must work on device 1 after they ran on device 0."""
+    import ctypes
+    import glob
+
+    import torch_ccl_b200._C as C
+    from torch_ccl_b200.ops import gemm_bf16_tn
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib = ctypes.CDLL(glob.glob(os.path.join(root, "torch_ccl_b200", "_C*.so"))[0])
+    fn = lib.ccl_decode_attention_noalloc
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                   ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong] + [ctypes.c_int] * 6 + [ctypes.c_void_p]
+    results = []
+    for d in (0, 1):
+        with torch.cuda.device(d):
+            dev = torch.device("cuda", d)
+            g = torch.Generator(device=dev).manual_seed(1)
+            a = torch.randn(256, 4096, device=dev, generator=g).to(torch.bfloat16)
+            b = torch.randn(16, 4096, device=dev, generator=g).to(torch.bfloat16)
+            out = gemm_bf16_tn(a, b, trans_out=True, splitk=4, bn=16)       # > 48 KB of dynamic shared memory
+            big = gemm_bf16_tn(torch.randn(4096, 512, device=dev, generator=g).to(torch.bfloat16),
+                               torch.randn(4096, 512, device=dev, generator=g).to(torch.bfloat16))  # persistent kernel
+            torch.testing.assert_close(out.float(), b.float() @ a.float().t(), rtol=2e-2, atol=2.0)
+            B, nh, nkv, hd, S, ns = 2, 4, 2, 128, 512, 3
+            qkv = torch.randn(B, (nh + 2 * nkv) * hd, device=dev, generator=g).to(torch.bfloat16)
+            kc = torch.randn(B, nkv, S, hd, device=dev, generator=g).to(torch.bfloat16)
+            vc = torch.randn(B, nkv, S, hd, device=dev, generator=g).to(torch.bfloat16)
+            pos = torch.tensor([100, 400], device=dev, dtype=torch.int32)
+            tab = torch.zeros(S, hd // 2, device=dev)
+            o1 = torch.empty(B, nh * hd, device=dev, dtype=torch.bfloat16)
+            o2 = torch.empty_like(o1)
+            scratch = torch.zeros(C.decode_attention_scratch_bytes(B, nh, ns) // 4 + 1, device=dev)
+            counters = torch.zeros(B * nh, device=dev, dtype=torch.int32)
+            k1, v1 = kc.clone(), vc.clone()
+            C.decode_attention(qkv, k1, v1, pos, tab + 1.0, tab, o1, scratch, counters, nh, nkv, ns)
+            k2, v2 = kc.clone(), vc.clone()
+            cos = tab + 1.0
+            rc = fn(qkv.data_ptr(), qkv.stride(0), k2.data_ptr(), v2.data_ptr(), pos.data_ptr(), cos.data_ptr(), tab.data_ptr(),
+                    o2.data_ptr(), o2.stride(0), B, nh, nkv, hd, S, ns, torch.cuda.current_stream(dev).cuda_stream)
+            assert rc == 0, lib.ccl_noalloc_last_error()
+            torch.cuda.synchronize(dev)
+            torch.testing.assert_close(o1.float(), o2.float(), rtol=2e-2, atol=2e-2)
+            results.append((out.float().cpu(), o1.float().cpu(), big.float().cpu()))
+    for x, y in zip(results[0], results[1]):
+        torch.testing.assert_close(x, y, rtol=2e-2, atol=2.0)

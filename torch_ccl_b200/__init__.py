@@ -3,14 +3,33 @@
 Layout:
   _C          compiled extension: ProcessGroupCCL (C++), CPU shared-memory collectives, the
               sm_100a collective / GEMM / attention kernels and their launchers
-  ops         fused collective + compute ops on a process group
-  parallel    tensor-parallel layers, FSDP communication hooks, expert-parallel dispatch
-  models      Llama-architecture decoder used by the benchmarks
-  utils       environment, tuner table, statistics
+  ops         fused collective + compute ops on a process group (also registered as torch.ops.ccl.*)
+  parallel    full-shard (ZeRO-3) engine, sequence-parallel tensor-parallel linear layers
+  models      tensor-parallel Llama-architecture decoder used by the benchmarks
+  utils       collective trace replay with value checks
+Environment knobs, the tuning table and statistics live in the extension: see env(), stats(),
+flight_recorder() below and torch_ccl_b200._C.
 """
 import torch  # noqa: F401
 
-from . import _C  # registers backend "ccl" with torch.distributed
+from . import _C  # registers backend "ccl" with torch.distributed and the torch.ops.ccl.* ops
+
+
+def _check_c10d_cuda_keys():
+    """torch.distributed reaches this backend for CUDA tensors through torch's own `c10d::*` CUDA
+    dispatcher entries (they call the Backend object of the process group). The reference has to
+    register those entries itself for its device (src/ProcessGroupCCL.cpp:86-738 of intel/torch-ccl);
+    here they must already exist - a torch build without them could not route a CUDA collective."""
+    names = ["allreduce_", "broadcast_", "reduce_", "allgather_", "_allgather_base_", "reduce_scatter_",
+             "_reduce_scatter_base_", "alltoall_", "alltoall_base_", "gather_", "scatter_", "barrier", "send", "recv_"]
+    has = torch._C._dispatch_has_kernel_for_dispatch_key
+    missing = [n for n in names if not has("c10d::" + n, "CUDA")]
+    if missing:
+        raise ImportError("this torch build has no CUDA dispatcher entries for c10d ops " + ", ".join(missing) +
+                          "; the 'ccl' backend cannot serve CUDA tensors with it")
+
+
+_check_c10d_cuda_keys()
 
 
 def stats():

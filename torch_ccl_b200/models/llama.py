@@ -83,6 +83,36 @@ class _Comm:
                 dist.all_reduce(x, group=self.nccl)
             self.direct.allreduce_residual_rmsnorm([x], [residual], [weight], [out], eps)
 
+    def embed_norm(self, tokens, table, vocab_base, residual, weight, out, eps):
+        """residual <- all_reduce(vocab-parallel embedding of `tokens`); out = rmsnorm(residual) * weight.
+        One kernel: the lookup is the producer side of the fused all_reduce + norm."""
+        if self.backend is not None:
+            self.backend.fused_allreduce_residual_rmsnorm(table, residual, weight, out, eps, tokens, vocab_base, True)
+        else:
+            self.direct.allreduce_residual_rmsnorm([table], [residual], [weight], [out], eps, [tokens], [vocab_base], True)
+
+    def fits_gemm_ar_norm(self, like, rows, hidden, k):
+        if self.nccl is not None:
+            return False
+        if self.backend is not None:
+            return self.backend.fits_gemm_ar_norm(like, rows, hidden, k)
+        return self.direct.fits_gemm_ar_norm(rows, hidden, k)
+
+    def gemm_ar_norm(self, w_packed, x, residual, weight, out, eps, splitk=0):
+        """residual += all_reduce(x @ w^T); out = rmsnorm(residual) * weight, in ONE kernel."""
+        if self.backend is not None:
+            self.backend.fused_gemm_ar_norm(w_packed, x, residual, weight, out, eps, splitk)
+        else:
+            self.direct.gemm_ar_norm([w_packed], [x], [residual], [weight], [out], eps, splitk)
+
+    def sample(self, logits, next_tokens, tokens, positions):
+        """Greedy sampling over the vocabulary shards: arg-max, all-gather of the per-rank winners
+        and the bookkeeping for the next step (tokens <- winner, positions += 1) in one kernel."""
+        if self.backend is not None:
+            self.backend.fused_sample_allgather(logits, next_tokens, tokens, positions)
+        else:
+            self.direct.sample_allgather([logits], [next_tokens], [tokens], [positions])
+
     def all_reduce(self, t):
         if self.backend is not None:
             self.backend.fused_allreduce(t, 1.0)
@@ -101,10 +131,17 @@ class _Comm:
 class TPLlamaDecoder:
     """Llama decoder sharded `world`-way by attention head and FFN column (Megatron layout)."""
 
-    def __init__(self, cfg: LlamaConfig, max_batch=16, max_seq=2048, group=None, device=None, seed=0, collective="ccl"):
+    def __init__(self, cfg: LlamaConfig, max_batch=16, max_seq=2048, group=None, device=None, seed=0, collective="ccl",
+                 fused=True):
+        """fused=True (default): 5 kernels per layer - qkv GEMM, attention, o_proj GEMM + all_reduce +
+        residual + norm in one launch, gate/up GEMM + SwiGLU, down_proj GEMM + all_reduce + residual +
+        norm in one launch - plus embedding + first norm, lm_head and the sampling kernel per step.
+        fused=False: the projections, the all_reduce + norm and the sampling run as separate kernels
+        (7 per layer); kept for A/B measurements. collective="nccl" implies fused=False."""
         self.cfg = cfg
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
         self.comm = _Comm(group, self.device, collective)
+        self.fused = bool(fused) and collective == "ccl"
         W, r = self.comm.world, self.comm.rank
         self.world, self.rank = W, r
         assert cfg.n_heads % W == 0 and cfg.n_kv_heads % W == 0 and cfg.inter % (8 * W) == 0 and cfg.vocab % W == 0
@@ -164,7 +201,8 @@ class TPLlamaDecoder:
         self.my_best = torch.zeros(B, 2, device=dev, dtype=torch.float32)
         self.graph = None
         self.graph_batch = None
-        self.kernels_per_step = cfg.n_layers * 7 + 2 + (1 if W > 1 else 0)
+        # (the unfused path also runs ~20 small torch kernels per step that are not counted here)
+        self.kernels_per_step = cfg.n_layers * 5 + 3 if self.fused else cfg.n_layers * 7 + 2 + (1 if W > 1 else 0)
         self._pin_in = None
         self._pin_out = None
 
@@ -191,6 +229,28 @@ class TPLlamaDecoder:
         out.copy_(rows * ok[:, None].to(rows.dtype))
 
     def _decode_body(self, B):
+        if self.fused and self.comm.fits_gemm_ar_norm(self.h, B, self.cfg.hidden, self.inter):
+            return self._decode_body_fused(B)
+        return self._decode_body_unfused(B)
+
+    def _decode_body_fused(self, B):
+        cfg = self.cfg
+        tokens, h, xn = self.tokens[:B], self.h[:B], self.xn[:B]
+        qkv, attn, act = self.qkv[:B], self.attn[:B], self.act[:B]
+        self.comm.embed_norm(tokens, self.embed, self.rank * self.vshard, h, self.layers[0]["attn_norm"], xn, cfg.eps)
+        for li, L in enumerate(self.layers):
+            self._gemm_t(L["wqkv"], xn, qkv, self.qkv_rows)
+            _C.decode_attention(qkv, L["k"], L["v"], self.positions[:B], self.cos, self.sin, attn, self.scratch,
+                                self.counters, self.nh, self.nkv, self.nsplit)
+            self.comm.gemm_ar_norm(L["wo"], attn, h, L["mlp_norm"], xn, cfg.eps)
+            self._gemm_t(L["wgu"], xn, act, self.inter, dual=self.inter_pad)
+            nw = self.layers[li + 1]["attn_norm"] if li + 1 < cfg.n_layers else self.final_norm
+            self.comm.gemm_ar_norm(L["wd"], act, h, nw, xn, cfg.eps)
+        self._gemm_t(self.lm_head, xn, self.logits[:B], self.vshard)
+        # feeds the sampled ids back into self.tokens and advances the positions: steady state is a pure replay
+        self.comm.sample(self.logits[:B], self.next_tokens[:B], tokens, self.positions[:B])
+
+    def _decode_body_unfused(self, B):
         cfg = self.cfg
         tokens, h, x, xn = self.tokens[:B], self.h[:B], self.x[:B], self.xn[:B]
         qkv, attn, act = self.qkv[:B], self.attn[:B], self.act[:B]

@@ -1,8 +1,19 @@
-"""Fused collective + compute ops. Each runs on the CURRENT CUDA stream of the tensor's device
-(so it can be captured in a CUDA graph) through the process group's peer-memory communicator."""
+"""Fused collective + compute ops of the `ccl` backend.
+
+Every op is registered with the dispatcher as `torch.ops.ccl.<name>` (schema + CUDA kernel + Meta
+kernel for shape inference), so it can be traced with fake tensors, exported and used under
+`torch.compile`; the functions below are thin Python faces that pass the process group by name.
+Each op runs on the CURRENT CUDA stream of the tensor's device (so it can be captured in a CUDA
+graph) through the process group's peer-memory communicator."""
 import torch
+import torch.distributed as dist
 
 from .. import _C
+
+
+def _name(group):
+    group = group if group is not None else dist.group.WORLD
+    return group.group_name
 
 
 def _backend(group, tensor):
@@ -13,14 +24,27 @@ def _backend(group, tensor):
 
 def allreduce_residual_rmsnorm(x, residual, weight, eps=1e-5, group=None, out=None):
     """residual <- residual + all_reduce(x); returns rmsnorm(residual) * weight, in one kernel."""
-    out = torch.empty_like(x) if out is None else out
+    if out is None:
+        return torch.ops.ccl.allreduce_residual_rmsnorm(x, residual, weight, eps, _name(group))
     _backend(group, x).fused_allreduce_residual_rmsnorm(x, residual, weight, out, eps)
+    return out
+
+
+def gemm_allreduce_residual_rmsnorm(w_packed, x, residual, weight, eps=1e-5, group=None, out=None):
+    """Row-parallel linear + all_reduce + residual add + RMSNorm in ONE kernel (tensor-parallel decode):
+    residual <- residual + sum over ranks of x[rows, K_local] @ w[hidden, K_local].T; returns
+    rmsnorm(residual) * weight. `w_packed` is pack_weight(w). Rows are limited (see
+    `gemm_allreduce_residual_rmsnorm_max_rows`); larger inputs run the GEMM and
+    allreduce_residual_rmsnorm separately."""
+    if out is None:
+        return torch.ops.ccl.gemm_ar_norm(w_packed, x, residual, weight, eps, _name(group))
+    _backend(group, x).fused_gemm_ar_norm(w_packed, x, residual, weight, out, eps)
     return out
 
 
 def all_reduce_scaled(tensor, scale=1.0, group=None):
     """In-place SUM all_reduce with the result multiplied by `scale` in the same pass."""
-    _backend(group, tensor).fused_allreduce(tensor, scale)
+    torch.ops.ccl.all_reduce_scaled(tensor, scale, _name(group))
     return tensor
 
 
@@ -32,30 +56,39 @@ def reduce_scatter_cast(inp, out, scale=1.0, group=None):
 
 def all_gather_copy_out(shard, outs, group=None):
     """All-gather `shard` with rank p's piece written directly into outs[p]."""
-    _backend(group, shard).fused_all_gather_copy_out(shard, list(outs))
+    torch.ops.ccl.all_gather_copy_out(shard, list(outs), _name(group))
     return outs
 
 
 def gemm_reduce_scatter(a, b, group=None, out=None):
     """Row-parallel linear fused with its reduce-scatter: returns this rank's rows [M/W, N] of
     sum_ranks(a_rank[M, K_local] @ b_rank[N, K_local].T); tiles cross NVLink from the GEMM epilogue."""
-    be = _backend(group, a)
-    world = torch.distributed.get_world_size(group)
     if out is None:
-        out = torch.empty(a.shape[0] // world, b.shape[0], device=a.device, dtype=torch.bfloat16)
-    be.fused_gemm_rs(a, b, out)
+        return torch.ops.ccl.gemm_reduce_scatter(a, b, _name(group))
+    _backend(group, a).fused_gemm_rs(a, b, out)
     return out
 
 
 def all_gather_gemm(a_shard, b, group=None, out=None):
     """All-gather fused with a column-parallel linear: returns all_gather(a_shard)[M, K] @ b[N, K].T;
     tiles of a shard start as soon as that shard has arrived."""
-    be = _backend(group, a_shard)
-    world = torch.distributed.get_world_size(group)
     if out is None:
-        out = torch.empty(a_shard.shape[0] * world, b.shape[0], device=a_shard.device, dtype=torch.bfloat16)
-    be.fused_ag_gemm(a_shard, b, out)
+        return torch.ops.ccl.all_gather_gemm(a_shard, b, _name(group))
+    _backend(group, a_shard).fused_ag_gemm(a_shard, b, out)
     return out
+
+
+def moe_dispatch(x, expert_idx, experts_per_rank, max_rows, group=None):
+    """Expert-parallel dispatch: sends every (token, k) row of x to the rank that owns its expert.
+    Returns (rows [max_rows, hidden], meta [max_rows, 3] = {source rank, source slot, local expert},
+    count int32 [16]: count[0] = rows received). The order of the received rows of one source is
+    not deterministic from run to run (positions come from an atomic counter); `meta` says which is which."""
+    return torch.ops.ccl.moe_dispatch(x, expert_idx, experts_per_rank, max_rows, _name(group))
+
+
+def moe_combine(y, meta, count, gate, group=None):
+    """Expert-parallel combine: returns out[t] = sum_k gate[t, k] * (row of y that came from slot (t, k))."""
+    return torch.ops.ccl.moe_combine(y, meta, count, gate, _name(group))
 
 
 def pack_weight(w):
