@@ -44,6 +44,10 @@ struct CommConfig {
   // route SUM all_reduces of bf16 / f16 / f32 of at least nvls_min_bytes through the switch.
   bool nvls = false;                  // CCL_NVLS
   size_t nvls_min_bytes = 4u << 20;
+  // Symmetric heap: memory for user tensors that every rank maps (allocate through the backend's
+  // allocateTensor / symm_empty). Collectives on such tensors run zero-copy: no staging through the
+  // arena. Created at the first allocation; bound to a multicast object when `nvls` is set.
+  size_t heap_bytes = 1ull << 30;     // CCL_SYMM_HEAP_MB
 };
 
 // One-shot all_reduce moves (W-1)*S bytes into every GPU, two-shot 2*S*(W-1)/W: with two ranks
@@ -105,6 +109,30 @@ class CudaComm {
   cudaError_t gemm_ar_norm(const std::vector<GemmArNormArgs>& args, cudaStream_t stream);
   cudaError_t sample_allgather(const std::vector<SampleArgs>& args, cudaStream_t stream);
 
+  // ---- symmetric heap ----------------------------------------------------------------------
+  // Allocation is COLLECTIVE IN ORDER: every rank must allocate (and release) the same sizes in the
+  // same order, so that a tensor sits at the same heap offset on every rank; kernels then address
+  // a peer's copy as that peer's heap base + the local offset, with no per-tensor handle exchange.
+  // The first call creates the heap (collective over the communicator, blocks on the store).
+  // Returns nullptr when the heap is exhausted.
+  void* symm_alloc(size_t bytes);
+  void symm_free(void* p);
+  // Offset of [p, p + bytes) inside this rank's heap, or false if it is not (wholly) symmetric memory.
+  bool symm_offset(const void* p, size_t bytes, size_t* off, int ctx_index = 0) const;
+  bool heap_multicast() const { return heap_ && heap_->multicast_base() != nullptr; }
+  size_t heap_in_use() const;
+  // Zero-copy collectives on symmetric tensors (no staging through the arena). `in_off` / `out_off`
+  // are heap offsets (symm_offset); buffers that are plain local memory are passed as pointers.
+  // all_reduce: in and out symmetric (may be the same); SUM through the switch when the heap is
+  // bound to a multicast object and `use_nvls`, else peer loads/stores. count * elem size % 16 == 0.
+  cudaError_t allreduce_symm(int dtype, size_t in_off, size_t out_off, size_t count, int op, float scale, int has_scale,
+                             bool use_nvls, cudaStream_t stream);
+  // reduce_scatter: in symmetric [world * count], out[r] local [count] (out dtype may be fp32 for bf16/f16 input).
+  cudaError_t reduce_scatter_symm(int in_dtype, int out_dtype, size_t in_off, std::vector<void*> outs, size_t count, int op,
+                                  float scale, int has_scale, bool use_nvls, cudaStream_t stream);
+  // all_gather: in[r] local [bytes], out symmetric [world * bytes].
+  cudaError_t all_gather_symm(std::vector<const void*> ins, size_t out_off, size_t bytes, bool use_nvls, cudaStream_t stream);
+
   // Asks every kernel of this communicator that is (or will be) waiting for a peer to give up:
   // sets the host-mapped abort word that all bounded waits poll. The waits return within
   // microseconds with status kStatusAborted; the communicator stays failed until clear_abort().
@@ -152,6 +180,13 @@ class CudaComm {
   int* status_host_ = nullptr;        // pinned + mapped
   int* status_dev_ = nullptr;
   uint64_t launches_ = 0;
+  void ensure_heap();
+  std::unique_ptr<SymmMem> heap_;          // real communicators
+  std::vector<void*> emu_heaps_;           // emulated communicators: one region per played rank
+  std::vector<void*> heap_bases_;          // per rank (own at [rank] / all local in emulation)
+  mutable std::mutex heap_mu_;
+  std::vector<std::pair<size_t, size_t>> heap_free_;   // sorted (offset, size) holes
+  std::vector<std::pair<size_t, size_t>> heap_used_;   // (offset, size) of live blocks
   std::mutex order_mu_;
   cudaEvent_t order_ev_ = nullptr;
   cudaStream_t last_stream_ = nullptr;

@@ -937,7 +937,7 @@ __global__ void __launch_bounds__(512) allreduce_residual_rmsnorm_kernel(const _
     // the norm weights do not depend on the reduction: fetch them first so that their latency
     // overlaps the peer waits and the block reduction
     Vec<T> wv[kNormMaxVecPerThread];
-    ll_load_norm_weight<T, kNormMaxVecPerThread>(a.weight, a.hidden, wv);
+    ll_load_norm_weight<T, kNormMaxVecPerThread>(a.weight, 0, hv, wv);
     if (ll || W == 1) {
       for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
         char* rrow = res + (size_t)row * row_bytes;

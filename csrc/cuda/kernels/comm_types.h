@@ -30,6 +30,8 @@ struct RankCtx {
   unsigned long long spin_ns;     // wait budget
   char* ll[kMaxRanks];          // peers' low-latency regions
   char* mc_data;                // NVLS multicast mapping of the arenas (nullptr if unavailable)
+  char* heap[kMaxRanks];        // peers' symmetric heaps (user tensors allocated through the backend; null until the first one)
+  char* mc_heap;                // NVLS multicast mapping of the heaps (nullptr if unavailable)
   int rank;
   int world;
 };

@@ -13,9 +13,11 @@
 //   [parity][this rank] of EVERY rank's low-latency region (peer stores over NVLink, own rank
 //   included), so the partial sums never make the round trip through HBM that a separate
 //   all_reduce kernel needs.
-//   Norm part: CTA i < rows then owns row i: it polls the W slots of its rank until every unit of
-//   the row carries the epoch, sums in rank order (fp32), adds the residual, normalises and writes
-//   the new residual and the normalised row. Rounding points are those of the unfused sequence
+//   Norm part: split-K cluster i < rows then owns row i, each of its CTAs an equal share of the
+//   row's features: it polls the W slots of its rank until every unit of its share carries the
+//   epoch, sums in rank order (fp32), adds the residual, exchanges its partial sum of squares
+//   with the other CTAs of the cluster over distributed shared memory, normalises and writes the
+//   new residual and the normalised output. Rounding points are those of the unfused sequence
 //   GEMM -> all_reduce -> add -> rmsnorm, so results are bit-identical to it.
 //   No CTA's GEMM part ever waits for another rank, and a row owner only waits for data that GEMM
 //   parts push, so the kernel needs no co-residency guarantee across GPUs; all waits are bounded.
@@ -98,20 +100,29 @@ struct LLPushEpilogue {
   }
 };
 
-template <int BN, bool EMU>
-__global__ void __launch_bounds__(gemm::kThreads, 2)
+// MV: 16-byte vectors of a row per thread in the norm part (the row is split over the CTAs of the
+// split-K cluster, so MV = 1 covers hidden <= 8 * 192 * splitk).
+template <int BN, int MV, bool EMU>
+__global__ void __launch_bounds__(gemm::kThreads, 3)
     gemm_ar_norm_kernel(const __grid_constant__ ArNormPack<EMU ? kMaxRanks : 1> pk, const gemm::Params p,
                         const __grid_constant__ RankCtx ctx1, const RankCtx* ctx_table, const ArNormShape sh) {
   const int ri = EMU ? blockIdx.y : 0;
   const RankCtx& ctx = EMU ? ctx_table[ri] : ctx1;
   const ArNormRank& rk = pk.r[ri];
   __shared__ float s_red[33];
+  __shared__ float s_part[2][8];   // per-CTA partial sums of squares of the cluster, double-buffered over rows
   const int n_ctas = gridDim.x * gridDim.z;
-  const int cta = blockIdx.z * gridDim.x + blockIdx.x;
+  const int nz = gridDim.z;                      // CTAs per cluster = split-K factor
+  const int z = p.splitk > 1 ? (int)ptx::cluster_ctarank() : 0;
+  // norm part: cluster c < rows owns row c (then c + gridDim.x, ...); CTA z of the cluster owns
+  // vectors [z * hvc, (z + 1) * hvc) of the row
+  const int hvc = sh.hidden / 8 / nz;
+  const int v0 = z * hvc, v1 = v0 + hvc;
+  const bool has_row = (int)blockIdx.x < sh.rows;
 
   // the norm weights are constants: fetch them before anything that waits
-  Vec<__nv_bfloat16> wv[kLLNormMaxVec];
-  if (cta < sh.rows) ll_load_norm_weight<__nv_bfloat16, kLLNormMaxVec>(rk.weight, sh.hidden, wv);
+  Vec<__nv_bfloat16> wv[MV];
+  if (has_row) ll_load_norm_weight<__nv_bfloat16, MV>(rk.weight, v0, v1, wv);
 
   const int m0 = blockIdx.x * kBM;
   gemm::gemm_tile_body<BN, false>(&pk.a[ri], &pk.b[ri], p, LLPushEpilogue{&ctx, sh.rows, sh.hidden},
@@ -119,10 +130,25 @@ __global__ void __launch_bounds__(gemm::kThreads, 2)
   ptx::griddep_wait();
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(ctx.state);
   const size_t row_bytes = (size_t)sh.hidden * 2;
-  for (int row = cta; row < sh.rows; row += n_ctas) {
+  int it = 0;
+  for (int row = blockIdx.x; row < sh.rows; row += gridDim.x, ++it) {
     char* res = static_cast<char*>(rk.residual) + (size_t)row * row_bytes;
-    ll_row_residual_norm<__nv_bfloat16, kLLNormMaxVec>(ctx, (int)(epoch & 1), epoch + 1, kOwnInSlot, (size_t)row * row_bytes, sh.hidden, nullptr,
-                                        res, res, static_cast<char*>(rk.out) + (size_t)row * row_bytes, wv, sh.eps, s_red);
+    Vec<__nv_bfloat16> hn[MV];
+    const float ss = ll_row_gather_add<__nv_bfloat16, MV, 4>(ctx, (int)(epoch & 1), epoch + 1, kOwnInSlot, (size_t)row * row_bytes,
+                                                             v0, v1, nullptr, res, res, hn, nullptr);
+    float total = block_sum(ss, s_red);
+    if (nz > 1) {
+      // every CTA of the cluster hands its partial to every other one over distributed shared
+      // memory; all of them then add the partials in the same (rank) order
+      float* buf = s_part[it & 1];
+      if ((int)threadIdx.x < nz) ptx::st_cluster_f32(ptx::mapa(ptx::smem_u32(buf + z), threadIdx.x), total);
+      ptx::cluster_arrive();
+      ptx::cluster_wait();
+      total = 0.f;
+      for (int q = 0; q < nz; ++q) total += buf[q];
+    }
+    const float rstd = rsqrtf(total / (float)sh.hidden + sh.eps);
+    ll_row_write_norm<__nv_bfloat16, MV>(hn, wv, rstd, v0, v1, static_cast<char*>(rk.out) + (size_t)row * row_bytes);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -241,7 +267,7 @@ cudaError_t configure_once(K kern, DeviceOnce& once) {
   return cudaSuccess;
 }
 
-template <int BN, bool EMU>
+template <int BN, int MV, bool EMU>
 cudaError_t launch_ar_norm_bn(const RankCtx* ctx, const RankCtx* dev_ctx_table, const GemmArNormArgs* args, int nctx,
                               int splitk, cudaStream_t stream) {
   constexpr int NR = EMU ? kMaxRanks : 1;
@@ -285,7 +311,7 @@ cudaError_t launch_ar_norm_bn(const RankCtx* ctx, const RankCtx* dev_ctx_table, 
   p.k_tiles = k_iters;
   ArNormShape sh{a0.rows, a0.hidden, a0.eps};
 
-  auto kern = gemm_ar_norm_kernel<BN, EMU>;
+  auto kern = gemm_ar_norm_kernel<BN, MV, EMU>;
   static DeviceOnce configured;
   cudaError_t e = configure_once(kern, configured);
   if (e != cudaSuccess) return e;
@@ -320,7 +346,6 @@ cudaError_t launch_gemm_ar_norm(const RankCtx* ctx, const RankCtx* dev_ctx_table
   const GemmArNormArgs& a0 = args[0];
   if (a0.hidden <= 0 || a0.hidden % kBM != 0 || a0.rows <= 0 || a0.K <= 0 || a0.K % 8 != 0) return cudaErrorInvalidValue;
   if (a0.rows > gemm_ar_norm_max_rows(a0.hidden)) return cudaErrorInvalidValue;
-  if (a0.hidden / 8 > gemm::kThreads * kLLNormMaxVec) return cudaErrorInvalidValue;
   for (int i = 0; i < nctx; ++i) {
     const GemmArNormArgs& a = args[i];
     if (!a.w || !a.x || !a.residual || !a.weight || !a.out) return cudaErrorInvalidValue;
@@ -344,10 +369,18 @@ cudaError_t launch_gemm_ar_norm(const RankCtx* ctx, const RankCtx* dev_ctx_table
   while (splitk > 1 && k_iters / splitk < 1) splitk >>= 1;
   const bool emu = nctx > 1;
   const int bn = a0.rows <= 16 ? 16 : (a0.rows <= 32 ? 32 : 64);
+  // vectors of a row per thread in the norm part: the row is split over the split-K cluster
+  const int per_cta = a0.hidden / 8 / splitk;
+  const int mv = per_cta <= gemm::kThreads ? 1 : (per_cta <= 3 * gemm::kThreads ? 3 : kLLNormMaxVec);
+  if (per_cta > kLLNormMaxVec * gemm::kThreads || (a0.hidden / 8) % splitk != 0) return cudaErrorInvalidValue;
+#define CCL_ARNORM_MV(BN, MV)                                                                                 \
+  return emu ? launch_ar_norm_bn<BN, MV, true>(ctx, dev_ctx_table, args, nctx, splitk, stream)                \
+             : launch_ar_norm_bn<BN, MV, false>(ctx, dev_ctx_table, args, nctx, splitk, stream);
 #define CCL_ARNORM_CASE(BN)                                                                                   \
   case BN:                                                                                                    \
-    return emu ? launch_ar_norm_bn<BN, true>(ctx, dev_ctx_table, args, nctx, splitk, stream)                  \
-               : launch_ar_norm_bn<BN, false>(ctx, dev_ctx_table, args, nctx, splitk, stream);
+    if (mv == 1) { CCL_ARNORM_MV(BN, 1) }                                                                     \
+    if (mv == 3) { CCL_ARNORM_MV(BN, 3) }                                                                     \
+    CCL_ARNORM_MV(BN, kLLNormMaxVec)
   switch (bn) {
     CCL_ARNORM_CASE(16)
     CCL_ARNORM_CASE(32)
@@ -355,6 +388,7 @@ cudaError_t launch_gemm_ar_norm(const RankCtx* ctx, const RankCtx* dev_ctx_table
     default: return cudaErrorInvalidValue;
   }
 #undef CCL_ARNORM_CASE
+#undef CCL_ARNORM_MV
 }
 
 cudaError_t launch_sample_allgather(const RankCtx* ctx, const RankCtx* dev_ctx_table, const SampleArgs* args, int nctx,

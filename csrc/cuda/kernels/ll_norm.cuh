@@ -131,29 +131,30 @@ __device__ __forceinline__ float block_sum(float v, float* s_red) {
   return s_red[32];
 }
 
-// One CTA finishes one row: h = round(round(sum over ranks) + residual); residual <- h;
-// out = round(round(h * rstd) * weight). The rounding points are those of the unfused sequence
-// all_reduce -> add -> rmsnorm in the tensor dtype. `mode` / `x_row`: see LLOwn. `res_in_row`
-// null means a zero residual that is not read. `wv` holds this thread's vectors of the norm
-// weight (fetched by the caller ahead of the wait). MV bounds the vectors per thread.
+// A row is finished in three steps so that the caller can choose how wide the sum of squares is
+// reduced (one CTA, or the CTAs of a cluster that share the row):
+//   1. ll_row_gather_add:  h = round(round(sum over ranks) + residual); residual <- h; returns this
+//      thread's part of sum(h^2). Vectors [v0, v1) of the row, vector v0 + threadIdx.x + k * blockDim.x
+//      in slot k of `hn`.
+//   2. the caller reduces the partial sums and forms rstd = rsqrt(mean(h^2) + eps);
+//   3. ll_row_write_norm:  out = round(round(h * rstd) * weight).
+// The rounding points are those of the unfused sequence all_reduce -> add -> rmsnorm in the tensor
+// dtype. `mode` / `x_row`: see LLOwn. `res_in_row` null means a zero residual that is not read.
 template <typename T, int MV, int BATCH = kMaxRanks>
-__device__ __forceinline__ bool ll_row_residual_norm(const RankCtx& ctx, int parity, uint32_t flag, int mode,
-                                                     size_t row_off /* byte offset of the row in the payload */,
-                                                     int hidden, const char* x_row, const char* res_in_row,
-                                                     char* res_out_row, char* out_row, const Vec<T> (&wv)[MV],
-                                                     float eps, float* s_red) {
-  const int hv = hidden / 8;
-  Vec<T> hn[MV];   // the new residual row, kept in the tensor dtype (half the registers of fp32)
+__device__ __forceinline__ float ll_row_gather_add(const RankCtx& ctx, int parity, uint32_t flag, int mode,
+                                                   size_t row_off /* byte offset of the row in the payload */, int v0, int v1,
+                                                   const char* x_row, const char* res_in_row, char* res_out_row,
+                                                   Vec<T> (&hn)[MV], bool* ok_out) {
   float ss = 0.f;
   bool ok = true;
 #pragma unroll
   for (int k = 0; k < MV; ++k) {
-    const int i = threadIdx.x + k * blockDim.x;
-    if (i < hv) {
+    const int i = v0 + threadIdx.x + k * blockDim.x;
+    if (i < v1) {
       float acc[8];
       if (mode != kLocalOnly) {
         ok = ll_gather_sum<T, BATCH>(ctx, parity, flag, row_off + (size_t)i * 16, mode == kOwnInSlot,
-                              x_row ? x_row + (size_t)i * 16 : nullptr, acc) && ok;
+                                     x_row ? x_row + (size_t)i * 16 : nullptr, acc) && ok;
       } else {
         Vec<T> v;
         *reinterpret_cast<uint4*>(&v) = x_row ? *reinterpret_cast<const uint4*>(x_row + (size_t)i * 16) : make_uint4(0, 0, 0, 0);
@@ -173,28 +174,46 @@ __device__ __forceinline__ bool ll_row_residual_norm(const RankCtx& ctx, int par
       *reinterpret_cast<uint4*>(res_out_row + (size_t)i * 16) = *reinterpret_cast<const uint4*>(&hn[k]);
     }
   }
-  const float total = block_sum(ss, s_red);
-  const float rstd = rsqrtf(total / (float)hidden + eps);
+  if (ok_out) *ok_out = ok;
+  return ss;
+}
+
+template <typename T, int MV>
+__device__ __forceinline__ void ll_row_write_norm(const Vec<T> (&hn)[MV], const Vec<T> (&wv)[MV], float rstd, int v0, int v1,
+                                                  char* out_row) {
 #pragma unroll
   for (int k = 0; k < MV; ++k) {
-    const int i = threadIdx.x + k * blockDim.x;
-    if (i < hv) {
+    const int i = v0 + threadIdx.x + k * blockDim.x;
+    if (i < v1) {
       Vec<T> o;
 #pragma unroll
       for (int t = 0; t < 8; ++t) o.v[t] = ll_round_to<T>(to_acc(ll_round_to<T>(to_acc(hn[k].v[t]) * rstd)) * to_acc(wv[k].v[t]));
       *reinterpret_cast<uint4*>(out_row + (size_t)i * 16) = *reinterpret_cast<const uint4*>(&o);
     }
   }
+}
+
+// One CTA finishes one whole row.
+template <typename T, int MV, int BATCH = kMaxRanks>
+__device__ __forceinline__ bool ll_row_residual_norm(const RankCtx& ctx, int parity, uint32_t flag, int mode, size_t row_off,
+                                                     int hidden, const char* x_row, const char* res_in_row,
+                                                     char* res_out_row, char* out_row, const Vec<T> (&wv)[MV],
+                                                     float eps, float* s_red) {
+  Vec<T> hn[MV];   // the new residual row, kept in the tensor dtype (half the registers of fp32)
+  bool ok = true;
+  const float ss = ll_row_gather_add<T, MV, BATCH>(ctx, parity, flag, mode, row_off, 0, hidden / 8, x_row, res_in_row, res_out_row, hn, &ok);
+  const float rstd = rsqrtf(block_sum(ss, s_red) / (float)hidden + eps);
+  ll_row_write_norm<T, MV>(hn, wv, rstd, 0, hidden / 8, out_row);
   return ok;
 }
 
+// Vectors [v0, v1) of the norm weight, laid out like `hn` above.
 template <typename T, int MV>
-__device__ __forceinline__ void ll_load_norm_weight(const void* wgt, int hidden, Vec<T> (&wv)[MV]) {
-  const int hv = hidden / 8;
+__device__ __forceinline__ void ll_load_norm_weight(const void* wgt, int v0, int v1, Vec<T> (&wv)[MV]) {
 #pragma unroll
   for (int k = 0; k < MV; ++k) {
-    const int i = threadIdx.x + k * blockDim.x;
-    if (i < hv) *reinterpret_cast<uint4*>(&wv[k]) = *reinterpret_cast<const uint4*>(static_cast<const char*>(wgt) + (size_t)i * 16);
+    const int i = v0 + threadIdx.x + k * blockDim.x;
+    if (i < v1) *reinterpret_cast<uint4*>(&wv[k]) = *reinterpret_cast<const uint4*>(static_cast<const char*>(wgt) + (size_t)i * 16);
   }
 }
 

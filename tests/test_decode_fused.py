@@ -131,7 +131,7 @@ def test_sample_allgather(comms, world):
     rows, vs = 16, 1000
     torch.manual_seed(11)
     logits = torch.randn(rows, vs * world)
-    logits[3, 17] = logits[3, vs * (world - 1) + 5] = 9.0  # a tie across the first and the last shard: lowest id wins
+    logits[3, 17] = logits[3, vs * (world - 1) + 25] = 9.0  # a tie (across the first and the last shard): lowest id wins
     shards = [logits[:, r * vs:(r + 1) * vs].contiguous().cuda() for r in range(world)]
     nxt = [torch.zeros(rows, dtype=torch.int64, device="cuda") for _ in range(world)]
     tok = [torch.zeros(rows, dtype=torch.int64, device="cuda") for _ in range(world)]
