@@ -179,7 +179,7 @@ def main():
     def summarize(ms_list):
         med = statistics.median(ms_list)
         return {"tokens_per_s": B * K / (med * 1e-3), "ms_per_step": med / K, "min_ms_per_step": min(ms_list) / K,
-                "max_ms_per_step": max(ms_list) / K}
+                "max_ms_per_step": max(ms_list) / K, "regions": [round(m / K, 4) for m in ms_list]}
 
     # ---- this repository's arm ----------------------------------------------------------------------
     model = TPLlamaDecoder(cfg, max_batch=B, max_seq=max_seq, seed=0, collective=args.collective, fused=not args.unfused)
@@ -282,7 +282,8 @@ def main():
             "vs_baseline": base["ratio"] if base else None,
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
             "impl": ("ccl" if fused else "ccl, unfused decode kernels") if args.collective == "ccl" else "ccl kernels + nccl all_reduce",
-            "repeats": R, "spread": {"min_ms_per_step": round(dev_res["min_ms_per_step"], 4), "max_ms_per_step": round(dev_res["max_ms_per_step"], 4)},
+            "repeats": R, "spread": {"min_ms_per_step": round(dev_res["min_ms_per_step"], 4), "max_ms_per_step": round(dev_res["max_ms_per_step"], 4),
+                                     "ms_per_step_of_each_region": dev_res["regions"]},
             "config": {"model": "llama-7b-arch (32L, h4096, 32x128 heads, ffn 11008, vocab 32000)" if args.layers == 32 else f"llama-7b-arch truncated to {args.layers} layers (NOT the headline config)",
                        "global_batch": B, "seq_len": S, "new_tokens_timed": K, "parallelism": f"tp{world}",
                        "l2": "inputs larger than L2: every step streams the whole weight shard and KV cache from HBM",
@@ -293,6 +294,7 @@ def main():
                        "samples": clocks["samples"]},
             "e2e": {"value": round(e2e_res["tokens_per_s"], 2), "unit": "tokens/s", "h2d_bytes_per_step": B * 8,
                     "d2h_bytes_per_step": B * 8, "ms_per_step": round(e2e_res["ms_per_step"], 4),
+                    "ms_per_step_of_each_region": e2e_res["regions"],
                     "clocks": {"sm_mhz": clocks_e2e["sm_mhz"], "reasons": clocks_e2e["reasons"]}},
             "gpu_launches": kernels_per_step * K,
             "kernels_per_step": kernels_per_step,

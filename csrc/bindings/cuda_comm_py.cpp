@@ -413,6 +413,24 @@ struct PyComm {
   }
   int moe_capacity(int hidden) { return comm->moe_capacity(hidden); }
 
+  // One symmetric block of `nbytes`: a uint8 tensor per played rank, all at the same heap offset. The block returns to
+  // the heap when the FIRST tensor of the list is released.
+  std::vector<at::Tensor> symm_empty(int64_t nbytes) {
+    void* p0 = comm->symm_alloc((size_t)nbytes);
+    TORCH_CHECK(p0 != nullptr, "symmetric heap exhausted");
+    const size_t off = static_cast<char*>(p0) - static_cast<char*>(comm->heap_base(0));
+    std::vector<at::Tensor> out;
+    auto opts = at::TensorOptions().dtype(at::kByte).device(at::kCUDA, comm->device());
+    CudaComm* c = comm.get();
+    for (int i = 0; i < comm->nctx(); ++i) {
+      void* pi = static_cast<char*>(comm->heap_base(i)) + off;
+      if (i == 0) out.push_back(at::from_blob(pi, {nbytes}, [c, p0](void*) { c->symm_free(p0); }, opts));
+      else out.push_back(at::from_blob(pi, {nbytes}, opts));
+    }
+    return out;
+  }
+  int64_t heap_in_use() { return (int64_t)comm->heap_in_use(); }
+
   std::vector<int> status() {
     int r = 0, p = 0, ph = 0;
     int code = comm->poll_status(&r, &p, &ph);
@@ -494,6 +512,7 @@ void bind_cuda_comm(py::module& m) {
             cfg.max_blocks = max_blocks;
             cfg.threads = 512;
             cfg.oneshot_max_bytes = 512 << 10;
+            cfg.heap_bytes = 64u << 20;
             auto p = std::make_unique<PyComm>();
             p->comm = std::make_unique<CudaComm>(world, (int)c10::cuda::current_device(), cfg);
             return p;
@@ -546,6 +565,10 @@ void bind_cuda_comm(py::module& m) {
       .def("fits_gemm_ar_norm", [](PyComm& c, int rows, int hidden, int k) { return c.comm->fits_gemm_ar_norm(rows, hidden, k); })
       .def("sample_allgather", &PyComm::sample_allgather, py::arg("logits"), py::arg("next_tokens"), py::arg("tokens") = py::none(),
            py::arg("positions") = py::none())
+      .def("symm_empty", &PyComm::symm_empty)
+      .def("heap_in_use", &PyComm::heap_in_use)
+      .def("set_symm_min_bytes", [](PyComm& c, int64_t b) { c.comm->mutable_config().symm_min_bytes = (size_t)b; })
+      .def("set_algo", [](PyComm& c, int a) { c.comm->mutable_config().algo = static_cast<ccl::Algo>(a); })
       .def("abort", [](PyComm& c) { c.comm->abort(); })
       .def("clear_abort", [](PyComm& c) { c.comm->clear_abort(); })
       .def("gemm_rs", &PyComm::gemm_rs)

@@ -112,6 +112,24 @@ void bind_process_group(py::module& m) {
       .def("fused_moe_combine", &ccl_ops::moe_combine)
       // staging capacity (bytes) of the fused GEMM + collective ops: the whole M x N (gemm_rs) or M x K (ag_gemm) bf16 matrix must fit
       .def("fused_gemm_capacity_bytes", [](ProcessGroupCCL& pg, const at::Tensor& like) { return (int64_t)cuda_comm_of(pg, like).config().half_bytes; })
+      // symmetric tensor of `numel` elements from the group's heap (collective in order; see ProcessGroupCCL::allocateTensor)
+      .def("symm_empty", [](ProcessGroupCCL& pg, int64_t numel, at::ScalarType dtype, c10::optional<at::Device> device) {
+        at::TensorOptions o = at::TensorOptions().dtype(dtype);
+        if (device.has_value()) o = o.device(*device);
+        return pg.allocateTensor((long)numel, o);
+      }, py::arg("numel"), py::arg("dtype"), py::arg("device") = py::none())
+      .def("is_symmetric", [](ProcessGroupCCL& pg, const at::Tensor& t) {
+        return t.is_cuda() && cuda_comm_of(pg, t).symm_offset(t.data_ptr(), t.nbytes(), nullptr);
+      })
+      .def("symm_heap_info", [](ProcessGroupCCL& pg, const at::Tensor& like) {
+        auto& c = cuda_comm_of(pg, like);
+        py::dict d;
+        d["bytes"] = c.config().heap_bytes;
+        d["in_use"] = c.heap_in_use();
+        d["multicast"] = c.heap_multicast();
+        d["symm_min_bytes"] = c.config().symm_min_bytes;
+        return d;
+      })
       .def("moe_capacity", [](ProcessGroupCCL& pg, const at::Tensor& like) { return cuda_comm_of(pg, like).moe_capacity((int)like.size(-1)); })
       .def("cuda_comm_status", [](ProcessGroupCCL& pg, const at::Tensor& t) {
         auto& c = cuda_comm_of(pg, t);
@@ -131,6 +149,8 @@ void bind_process_group(py::module& m) {
         d["symm_mem"] = c.symm == ccl::SymmKind::kVmm ? "vmm" : "ipc";
         d["nvls"] = c.nvls;
         d["nvls_available"] = cuda_comm_of(pg, t).nvls_available();
+        d["nvls_min_bytes"] = c.nvls_min_bytes;
+        d["symm_min_bytes"] = c.symm_min_bytes;
         return d;
       })
       .def("set_cuda_tuning", [](ProcessGroupCCL& pg, const at::Tensor& t, const py::dict& kv) {
@@ -144,6 +164,9 @@ void bind_process_group(py::module& m) {
           else if (k == "ag_push_max_bytes") c.ag_push_max_bytes = (size_t)v;
           else if (k == "max_blocks") { TORCH_CHECK(v >= 1 && v <= ccl::kMaxBlocks, "max_blocks out of range"); c.max_blocks = (int)v; }
           else if (k == "threads") { TORCH_CHECK(v >= 32 && v <= 512 && v % 32 == 0, "threads out of range"); c.threads = (int)v; }
+          else if (k == "nvls_min_bytes") c.nvls_min_bytes = (size_t)v;
+          else if (k == "symm_min_bytes") c.symm_min_bytes = (size_t)v;
+          else if (k == "algo") { TORCH_CHECK(v >= 0 && v <= 3, "algo: 0 auto, 1 oneshot, 2 twoshot, 3 nvls"); c.algo = static_cast<ccl::Algo>(v); }
           else TORCH_CHECK(false, "unknown tuning key '", k, "'");
         }
       })
@@ -161,6 +184,9 @@ void bind_process_group(py::module& m) {
     d["oneshot_max_bytes"] = e.oneshot_max_bytes;
     d["spin_timeout_ms"] = e.spin_timeout_ms;
     d["arena_mb"] = e.arena_mb;
+    d["symm_heap_mb"] = e.symm_heap_mb;
+    d["symm_min_bytes"] = e.symm_min_bytes;
+    d["nvls_min_bytes"] = e.nvls_min_bytes;
     d["shm_slot_mb"] = e.shm_slot_mb;
     d["max_blocks"] = e.max_blocks;
     d["threads"] = e.threads;

@@ -316,6 +316,9 @@ CudaComm& CudaBackendImpl::comm(const at::Device& device) {
     if (env.oneshot_max_bytes >= 0) cfg.oneshot_max_bytes = (size_t)env.oneshot_max_bytes;
     if (env.max_blocks > 0) cfg.max_blocks = std::min(env.max_blocks, (int)kMaxBlocks);
     if (env.threads > 0) cfg.threads = std::max(32, std::min(512, env.threads / 32 * 32));
+    if (env.symm_heap_mb > 0) cfg.heap_bytes = (size_t)env.symm_heap_mb << 20;
+    if (env.symm_min_bytes >= 0) cfg.symm_min_bytes = (size_t)env.symm_min_bytes;
+    if (env.nvls_min_bytes >= 0) cfg.nvls_min_bytes = (size_t)env.nvls_min_bytes;
     cfg.symm = parse_symm_kind(env.symm_mem);
     if (env.nvls || env.algo == "nvls") {
       // the multicast object binds driver virtual-memory allocations only
@@ -332,6 +335,47 @@ CudaComm& CudaBackendImpl::comm(const at::Device& device) {
       std::cout << "Allreduce goes to the peer-memory kernel path (arena " << env.arena_mb << " MB per half)." << std::endl;
   }
   return *comm_;
+}
+
+std::shared_ptr<CudaComm> CudaBackendImpl::comm_ptr(const at::Device& device) {
+  (void)comm(device);
+  std::lock_guard<std::mutex> g(mu_);
+  return comm_;
+}
+
+namespace {
+struct SymmBlock {
+  std::shared_ptr<CudaComm> comm;  // keeps the heap mapped while the tensor lives
+  void* ptr;
+};
+void release_symm_block(void* ctx) {
+  auto* b = static_cast<SymmBlock*>(ctx);
+  b->comm->symm_free(b->ptr);
+  delete b;
+}
+}  // namespace
+
+c10::DataPtr CudaBackendImpl::symm_allocate(size_t bytes, const at::Device& device) {
+  std::shared_ptr<CudaComm> c = comm_ptr(device);
+  void* p = c->symm_alloc(bytes);
+  TORCH_CHECK(p != nullptr, "ccl: symmetric heap exhausted (", c->heap_in_use() >> 20, " MB of ", c->config().heap_bytes >> 20,
+              " MB in use, ", bytes >> 20, " MB requested); raise CCL_SYMM_HEAP_MB");
+  auto* blk = new SymmBlock{c, p};
+  return c10::DataPtr(p, blk, &release_symm_block, at::Device(at::kCUDA, (c10::DeviceIndex)c->device()));
+}
+
+at::Tensor CudaBackendImpl::symm_empty(int64_t numel, at::TensorOptions options) {
+  const at::Device dev = options.has_device() && options.device().is_cuda() && options.device().has_index()
+                             ? options.device() : at::Device(at::kCUDA, c10::cuda::current_device());
+  const auto dtype = options.has_dtype() ? c10::typeMetaToScalarType(options.dtype()) : at::kFloat;
+  const size_t bytes = (size_t)numel * c10::elementSize(dtype);
+  c10::DataPtr dp = symm_allocate(bytes, dev);
+  auto storage = c10::make_intrusive<c10::StorageImpl>(c10::StorageImpl::use_byte_size_t(), bytes, std::move(dp), /*allocator=*/nullptr,
+                                                        /*resizable=*/false);
+  at::Tensor t = at::detail::make_tensor<at::TensorImpl>(std::move(storage), c10::DispatchKeySet(c10::DispatchKey::CUDA),
+                                                         c10::scalarTypeToTypeMeta(dtype));
+  t.unsafeGetTensorImpl()->set_sizes_contiguous({numel});
+  return t;
 }
 
 c10::cuda::CUDAStream CudaBackendImpl::comm_stream(const at::Device& device) {
@@ -514,7 +558,7 @@ void CudaBackendImpl::shutdown() {
 }
 
 // Raises the communicator's abort word: every kernel that is (or will be) spinning on a peer
-// returns within microseconds instead of after the spin budget, its Work fails with the
+// returns within about a millisecond instead of after the spin budget, its Work fails with the
 // "aborted" status, and further collectives on this group are refused.
 void CudaBackendImpl::abort() {
   std::lock_guard<std::mutex> g(mu_);

@@ -52,6 +52,11 @@ class CudaBackendImpl {
   bool p2p_batch_active() const { return p2p_batch_ops_ > 0; }
 
   CudaComm& comm(const at::Device& device);
+  std::shared_ptr<CudaComm> comm_ptr(const at::Device& device);
+  // Memory from the communicator's symmetric heap (see CudaComm::symm_alloc: collective in order).
+  // The block goes back to the heap when the DataPtr / tensor dies; it keeps the communicator alive.
+  c10::DataPtr symm_allocate(size_t bytes, const at::Device& device);
+  at::Tensor symm_empty(int64_t numel, at::TensorOptions options);
   bool has_comm() const { return comm_ != nullptr; }
   c10::cuda::CUDAStream comm_stream(const at::Device& device);
   void shutdown();

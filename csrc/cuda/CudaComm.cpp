@@ -132,6 +132,8 @@ CudaComm::~CudaComm() {
     } catch (...) {
     }
   }
+  heap_.reset();
+  for (void* h : emu_heaps_) cudaFree(h);
   symm_.reset();
   for (void* a : local_arenas_) cudaFree(a);
   if (dev_ctx_table_) cudaFree(dev_ctx_table_);
@@ -240,6 +242,23 @@ cudaError_t CudaComm::allreduce(int dtype, std::vector<CollArgs> args, cudaStrea
   const size_t bytes = count * esz;
   const size_t nvec = (bytes + 15) / 16;
   Algo algo = cfg_.algo;
+  // symmetric tensors (allocated from the communicator's heap) skip the staging arena altogether
+  if (world_ > 1 && !heap_bases_.empty() && cfg_.ablate == kAblateNone && bytes >= cfg_.symm_min_bytes && bytes % 16 == 0 &&
+      (algo == Algo::kAuto || algo == Algo::kNvls)) {
+    size_t in_off = 0, out_off = 0;
+    bool symm = true;
+    for (int i = 0; i < nctx() && symm; ++i) {
+      size_t io = 0, oo = 0;
+      symm = symm_offset(args[i].in, bytes, &io, i) && symm_offset(args[i].out, bytes, &oo, i) && (i == 0 || (io == in_off && oo == out_off));
+      in_off = io;
+      out_off = oo;
+    }
+    if (symm && in_off % 16 == 0 && out_off % 16 == 0) {
+      cudaError_t es = allreduce_symm(dtype, in_off, out_off, count, args[0].op, args[0].scale, args[0].has_scale, true, stream);
+      if (chosen) *chosen = AlgoChoice{last_algo_, 0, 0};
+      return es;
+    }
+  }
   const size_t slot = round_up(nvec * 16, 128);
   const bool fits_oneshot = slot * world_ <= cfg_.half_bytes;
   // the switch reduces SUMs of bf16 / f16 / f32 only; the emulation plays it in software when forced
@@ -300,6 +319,24 @@ cudaError_t CudaComm::reduce_scatter(int in_dtype, int out_dtype, std::vector<Co
   DeviceGuard g(device_);
   enter_stream(stream);
   const size_t esz = dtype_size(in_dtype);
+  // flat symmetric input (equal pieces, back to back, inside the heap): reduce straight out of the peers' buffers
+  if (world_ > 1 && !heap_bases_.empty() && cfg_.ablate == kAblateNone && (cfg_.algo == Algo::kAuto || cfg_.algo == Algo::kNvls)) {
+    const size_t cnt = args[0].in_cnt[0];
+    const size_t pb = cnt * esz;
+    bool symm = pb >= cfg_.symm_min_bytes / world_ && pb % 16 == 0;
+    size_t in_off = 0;
+    std::vector<void*> outs;
+    for (int i = 0; i < nctx() && symm; ++i) {
+      const char* base = static_cast<const char*>(args[i].in_piece[0]);
+      for (int p = 0; p < world_ && symm; ++p) symm = args[i].in_cnt[p] == cnt && args[i].in_piece[p] == base + (size_t)p * pb;
+      size_t io = 0;
+      symm = symm && symm_offset(base, pb * world_, &io, i) && (i == 0 || io == in_off) && io % 16 == 0 &&
+             (reinterpret_cast<uintptr_t>(args[i].out) & 15) == 0;
+      in_off = io;
+      outs.push_back(args[i].out);
+    }
+    if (symm) return reduce_scatter_symm(in_dtype, out_dtype, in_off, outs, cnt, args[0].op, args[0].scale, args[0].has_scale, true, stream);
+  }
   const size_t per_vec = 16 / esz;
   size_t stride = cfg_.half_bytes / (16 * (size_t)world_);
   stride = stride / 8 * 8;
@@ -335,6 +372,23 @@ cudaError_t CudaComm::all_gather(std::vector<CollArgs> args, cudaStream_t stream
   CCL_CHECK_ARGS(args)
   DeviceGuard g(device_);
   enter_stream(stream);
+  // flat symmetric output (equal pieces, back to back, inside the heap): write straight into the peers' buffers
+  if (world_ > 1 && !heap_bases_.empty() && cfg_.ablate == kAblateNone && (cfg_.algo == Algo::kAuto || cfg_.algo == Algo::kNvls)) {
+    const size_t pb = args[0].out_cnt[0];
+    bool symm = pb >= cfg_.symm_min_bytes / world_ && pb % 16 == 0;
+    size_t out_off = 0;
+    std::vector<const void*> ins;
+    for (int i = 0; i < nctx() && symm; ++i) {
+      const char* base = static_cast<const char*>(args[i].out_piece[0]);
+      for (int p = 0; p < world_ && symm; ++p) symm = args[i].out_cnt[p] == pb && args[i].out_piece[p] == base + (size_t)p * pb;
+      size_t oo = 0;
+      symm = symm && symm_offset(base, pb * world_, &oo, i) && (i == 0 || oo == out_off) && oo % 16 == 0 &&
+             (reinterpret_cast<uintptr_t>(args[i].in) & 15) == 0;
+      out_off = oo;
+      ins.push_back(args[i].in);
+    }
+    if (symm) return all_gather_symm(ins, out_off, pb, true, stream);
+  }
   size_t maxb = 0;
   for (auto& a : args)
     for (int p = 0; p < world_; ++p) maxb = std::max(maxb, (size_t)a.out_cnt[p]);
@@ -507,6 +561,166 @@ cudaError_t CudaComm::barrier_single_rank(int i, cudaStream_t stream) {
   lc.nctx = 1;
   lc.stream = stream;
   return launch_barrier(&host_ctx_[i], &a, lc);
+}
+
+// ------------------------------------------------------------------------------------------
+// symmetric heap
+// ------------------------------------------------------------------------------------------
+void CudaComm::ensure_heap() {
+  if (!heap_bases_.empty()) return;
+  DeviceGuard g(device_);
+  const size_t bytes = round_up(cfg_.heap_bytes, 2u << 20);
+  if (emulated_) {
+    for (int r = 0; r < world_; ++r) {
+      void* base = nullptr;
+      check(cudaMalloc(&base, bytes), "cudaMalloc(symmetric heap)");
+      emu_heaps_.push_back(base);
+    }
+    heap_bases_ = emu_heaps_;
+  } else {
+    // collective over the communicator: every rank reaches its first symmetric allocation together
+    const bool mc = cfg_.nvls && world_ > 1;
+    heap_ = std::make_unique<SymmMem>(mc ? SymmKind::kVmm : cfg_.symm, rank_, world_, device_, bytes, kv_, prefix_ + "/heap", mc);
+    heap_bases_ = heap_->bases();
+  }
+  cfg_.heap_bytes = bytes;
+  heap_free_.assign(1, {0, bytes});
+  for (int i = 0; i < nctx(); ++i) {
+    for (int p = 0; p < world_; ++p) host_ctx_[i].heap[p] = static_cast<char*>(heap_bases_[p]);
+    host_ctx_[i].mc_heap = heap_ ? static_cast<char*>(heap_->multicast_base()) : nullptr;
+  }
+  if (emulated_)
+    check(cudaMemcpy(dev_ctx_table_, host_ctx_.data(), sizeof(RankCtx) * nctx(), cudaMemcpyHostToDevice), "cudaMemcpy(ctx table)");
+}
+
+void* CudaComm::symm_alloc(size_t bytes) {
+  std::lock_guard<std::mutex> g(heap_mu_);
+  ensure_heap();
+  const size_t need = round_up(std::max<size_t>(bytes, 1), 1024);
+  // first fit in address order: the same sequence of calls gives the same offsets on every rank
+  for (size_t i = 0; i < heap_free_.size(); ++i) {
+    if (heap_free_[i].second < need) continue;
+    const size_t off = heap_free_[i].first;
+    if (heap_free_[i].second == need) heap_free_.erase(heap_free_.begin() + i);
+    else heap_free_[i] = {off + need, heap_free_[i].second - need};
+    heap_used_.push_back({off, need});
+    return static_cast<char*>(heap_bases_[emulated_ ? 0 : rank_]) + off;
+  }
+  return nullptr;
+}
+
+void CudaComm::symm_free(void* p) {
+  std::lock_guard<std::mutex> g(heap_mu_);
+  if (heap_bases_.empty() || !p) return;
+  const size_t off = static_cast<char*>(p) - static_cast<char*>(heap_bases_[emulated_ ? 0 : rank_]);
+  for (size_t i = 0; i < heap_used_.size(); ++i) {
+    if (heap_used_[i].first != off) continue;
+    std::pair<size_t, size_t> blk = heap_used_[i];
+    heap_used_.erase(heap_used_.begin() + i);
+    // insert in address order and merge with the neighbours
+    size_t k = 0;
+    while (k < heap_free_.size() && heap_free_[k].first < blk.first) ++k;
+    heap_free_.insert(heap_free_.begin() + k, blk);
+    if (k + 1 < heap_free_.size() && heap_free_[k].first + heap_free_[k].second == heap_free_[k + 1].first) {
+      heap_free_[k].second += heap_free_[k + 1].second;
+      heap_free_.erase(heap_free_.begin() + k + 1);
+    }
+    if (k > 0 && heap_free_[k - 1].first + heap_free_[k - 1].second == heap_free_[k].first) {
+      heap_free_[k - 1].second += heap_free_[k].second;
+      heap_free_.erase(heap_free_.begin() + k);
+    }
+    return;
+  }
+}
+
+size_t CudaComm::heap_in_use() const {
+  std::lock_guard<std::mutex> g(heap_mu_);
+  size_t n = 0;
+  for (auto& b : heap_used_) n += b.second;
+  return n;
+}
+
+bool CudaComm::symm_offset(const void* p, size_t bytes, size_t* off, int ctx_index) const {
+  if (heap_bases_.empty() || !p) return false;
+  const char* base = static_cast<const char*>(heap_bases_[emulated_ ? ctx_index : rank_]);
+  const char* c = static_cast<const char*>(p);
+  if (c < base || c + bytes > base + cfg_.heap_bytes) return false;
+  if (off) *off = (size_t)(c - base);
+  return true;
+}
+
+static bool switch_dtype(int dt) { return dt == kBF16 || dt == kF16 || dt == kF32; }
+
+cudaError_t CudaComm::allreduce_symm(int dtype, size_t in_off, size_t out_off, size_t count, int op, float scale, int has_scale,
+                                     bool use_nvls, cudaStream_t stream) {
+  DeviceGuard g(device_);
+  enter_stream(stream);
+  const size_t bytes = count * dtype_size(dtype);
+  if (bytes % 16 || in_off % 16 || out_off % 16 || heap_bases_.empty()) return cudaErrorInvalidValue;
+  std::vector<SymmArgs> args(nctx());
+  for (auto& a : args) {
+    a.in_off = in_off;
+    a.out_off = out_off;
+    a.count = count;
+    a.op = op;
+    a.scale = scale;
+    a.has_scale = has_scale;
+    a.use_mc = (use_nvls && op == kSum && switch_dtype(dtype) && (emulated_ || heap_multicast())) ? 1 : 0;
+  }
+  const size_t share = ceil_div(bytes / 16, (size_t)world_);
+  LaunchCfg lc = launch_cfg(blocks_for(share, cfg_.max_blocks), threads_for(share, blocks_for(share, cfg_.max_blocks), cfg_.threads), stream);
+  last_algo_ = args[0].use_mc ? Algo::kNvls : Algo::kTwoShot;
+  cudaError_t e = launch_allreduce_symm(dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  if (e == cudaSuccess) ++launches_;
+  return e;
+}
+
+cudaError_t CudaComm::reduce_scatter_symm(int in_dtype, int out_dtype, size_t in_off, std::vector<void*> outs, size_t count, int op,
+                                          float scale, int has_scale, bool use_nvls, cudaStream_t stream) {
+  CCL_CHECK_ARGS(outs)
+  DeviceGuard g(device_);
+  enter_stream(stream);
+  const size_t bytes = count * dtype_size(in_dtype);
+  if (bytes % 16 || in_off % 16 || heap_bases_.empty()) return cudaErrorInvalidValue;
+  std::vector<SymmArgs> args(nctx());
+  for (int i = 0; i < nctx(); ++i) {
+    SymmArgs& a = args[i];
+    a.in_off = in_off;
+    a.out = outs[i];
+    a.count = count;
+    a.op = op;
+    a.scale = scale;
+    a.has_scale = has_scale;
+    a.use_mc = (use_nvls && op == kSum && switch_dtype(in_dtype) && (emulated_ || heap_multicast())) ? 1 : 0;
+  }
+  const size_t pv = bytes / 16;
+  LaunchCfg lc = launch_cfg(blocks_for(pv, cfg_.max_blocks), threads_for(pv, blocks_for(pv, cfg_.max_blocks), cfg_.threads), stream);
+  last_algo_ = args[0].use_mc ? Algo::kNvls : Algo::kTwoShot;
+  cudaError_t e = launch_reduce_scatter_symm(in_dtype, out_dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  if (e == cudaSuccess) ++launches_;
+  return e;
+}
+
+cudaError_t CudaComm::all_gather_symm(std::vector<const void*> ins, size_t out_off, size_t bytes, bool use_nvls, cudaStream_t stream) {
+  CCL_CHECK_ARGS(ins)
+  DeviceGuard g(device_);
+  enter_stream(stream);
+  if (bytes % 16 || out_off % 16 || heap_bases_.empty()) return cudaErrorInvalidValue;
+  std::vector<SymmArgs> args(nctx());
+  for (int i = 0; i < nctx(); ++i) {
+    if (reinterpret_cast<uintptr_t>(ins[i]) & 15) return cudaErrorInvalidValue;
+    SymmArgs& a = args[i];
+    a.in = ins[i];
+    a.out_off = out_off;
+    a.count = bytes;
+    a.use_mc = (use_nvls && (emulated_ || heap_multicast())) ? 1 : 0;
+  }
+  const size_t pv = bytes / 16;
+  LaunchCfg lc = launch_cfg(blocks_for(pv, cfg_.max_blocks), threads_for(pv, blocks_for(pv, cfg_.max_blocks), cfg_.threads), stream);
+  last_algo_ = args[0].use_mc ? Algo::kNvls : Algo::kTwoShot;
+  cudaError_t e = launch_all_gather_symm(emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  if (e == cudaSuccess) ++launches_;
+  return e;
 }
 
 void CudaComm::abort() {

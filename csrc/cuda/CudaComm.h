@@ -22,6 +22,7 @@
 
 #include "cuda/SymmMem.h"
 #include "cuda/kernels/collectives.h"
+#include "cuda/kernels/collectives_symm.h"
 #include "cuda/kernels/decode_fused.h"
 #include "cuda/kernels/gemm_collective.h"
 #include "cuda/kernels/moe_a2a.h"
@@ -48,6 +49,7 @@ struct CommConfig {
   // allocateTensor / symm_empty). Collectives on such tensors run zero-copy: no staging through the
   // arena. Created at the first allocation; bound to a multicast object when `nvls` is set.
   size_t heap_bytes = 1ull << 30;     // CCL_SYMM_HEAP_MB
+  size_t symm_min_bytes = 256u << 10;  // smaller symmetric messages still take the (lower-latency) staged one-shot kernels
 };
 
 // One-shot all_reduce moves (W-1)*S bytes into every GPU, two-shot 2*S*(W-1)/W: with two ranks
@@ -120,6 +122,8 @@ class CudaComm {
   // Offset of [p, p + bytes) inside this rank's heap, or false if it is not (wholly) symmetric memory.
   bool symm_offset(const void* p, size_t bytes, size_t* off, int ctx_index = 0) const;
   bool heap_multicast() const { return heap_ && heap_->multicast_base() != nullptr; }
+  // Base of rank context i's heap (emulation: one per played rank; real: this rank's own at i == 0).
+  void* heap_base(int ctx_index = 0) const { return heap_bases_.empty() ? nullptr : heap_bases_[emulated_ ? ctx_index : rank_]; }
   size_t heap_in_use() const;
   // Zero-copy collectives on symmetric tensors (no staging through the arena). `in_off` / `out_off`
   // are heap offsets (symm_offset); buffers that are plain local memory are passed as pointers.
@@ -134,8 +138,8 @@ class CudaComm {
   cudaError_t all_gather_symm(std::vector<const void*> ins, size_t out_off, size_t bytes, bool use_nvls, cudaStream_t stream);
 
   // Asks every kernel of this communicator that is (or will be) waiting for a peer to give up:
-  // sets the host-mapped abort word that all bounded waits poll. The waits return within
-  // microseconds with status kStatusAborted; the communicator stays failed until clear_abort().
+  // sets the host-mapped abort word that all bounded waits sample. The waits return within about a
+  // millisecond with status kStatusAborted; the communicator stays failed until clear_abort().
   void abort();
   void clear_abort();
   bool aborted() const;

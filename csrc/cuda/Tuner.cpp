@@ -8,7 +8,7 @@ namespace ccl {
 
 namespace {
 
-const char* const kKeys[] = {"oneshot_max_bytes", "ag_push_max_bytes", "max_blocks", "threads"};
+const char* const kKeys[] = {"oneshot_max_bytes", "ag_push_max_bytes", "max_blocks", "threads", "nvls_min_bytes", "symm_min_bytes"};
 
 bool known_key(const std::string& k) {
   for (const char* s : kKeys)
@@ -82,6 +82,8 @@ bool apply_tuning(const std::map<int, TuneEntry>& table, int world, CommConfig* 
     else if (kv.first == "ag_push_max_bytes") cfg->ag_push_max_bytes = (size_t)kv.second;
     else if (kv.first == "max_blocks") cfg->max_blocks = (int)kv.second;
     else if (kv.first == "threads") cfg->threads = (int)kv.second;
+    else if (kv.first == "nvls_min_bytes") cfg->nvls_min_bytes = (size_t)kv.second;
+    else if (kv.first == "symm_min_bytes") cfg->symm_min_bytes = (size_t)kv.second;
   }
   return true;
 }

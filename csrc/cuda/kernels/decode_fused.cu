@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(256) sample_allgather_kernel(const __grid_cons
         while (true) {
           s = ptx::ld_volatile_v4(src);
           if (s.y == flag && s.w == flag) break;
-          if ((++it & 63u) == 0 && (ptx::globaltimer_ns() - t0 > ctx.spin_ns || comm_aborted(ctx))) {
+          if ((++it & 63u) == 0 && (ptx::globaltimer_ns() - t0 > ctx.spin_ns || ((it & 1023u) == 0 && comm_aborted(ctx)))) {
             sy.report(threadIdx.x, 0);
             break;
           }

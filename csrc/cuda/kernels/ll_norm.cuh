@@ -87,7 +87,7 @@ __device__ __forceinline__ bool ll_gather_sum(const RankCtx& ctx, int parity, ui
               s[2 * q] = ptx::ld_volatile_v4(base + (size_t)p * kLLSlotBytes);
               s[2 * q + 1] = ptx::ld_volatile_v4(base + (size_t)p * kLLSlotBytes + 16);
               if (ll_ready(s[2 * q], s[2 * q + 1], flag)) break;
-              if ((++it & 63u) == 0 && (ptx::globaltimer_ns() - t0 > ctx.spin_ns || comm_aborted(ctx))) {
+              if ((++it & 63u) == 0 && (ptx::globaltimer_ns() - t0 > ctx.spin_ns || ((it & 1023u) == 0 && comm_aborted(ctx)))) {
                 report_timeout(ctx, p, 0);
                 ok = false;
                 break;

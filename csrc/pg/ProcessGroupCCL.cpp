@@ -377,6 +377,38 @@ static std::string flow_str(int from, int to) {
 }
 
 // ------------------------------------------------------------------------------------------
+// symmetric tensors
+// ------------------------------------------------------------------------------------------
+at::Tensor ProcessGroupCCL::allocateTensor(long size, at::TensorOptions options) {
+  TORCH_CHECK(size >= 0, "allocateTensor: negative size");
+  const at::Device dev = options.has_device() && options.device().is_cuda() && options.device().has_index()
+                             ? options.device() : at::Device(at::kCUDA, c10::cuda::current_device());
+  return cudaImpl(dev).symm_empty(size, options);
+}
+
+namespace {
+// c10::Allocator over the symmetric heap, for torch.cuda.MemPool-style users.
+class SymmAllocator : public c10::Allocator {
+ public:
+  explicit SymmAllocator(ProcessGroupCCL* pg) : pg_(pg) {}
+  c10::DataPtr allocate(size_t n) override {
+    const at::Device dev(at::kCUDA, c10::cuda::current_device());
+    return pg_->cudaImpl(dev).symm_allocate(n, dev);
+  }
+  void copy_data(void* dest, const void* src, std::size_t count) const override {
+    C10_CUDA_CHECK(cudaMemcpy(dest, src, count, cudaMemcpyDeviceToDevice));
+  }
+
+ private:
+  ProcessGroupCCL* pg_;
+};
+}  // namespace
+
+std::shared_ptr<c10::Allocator> ProcessGroupCCL::getMemAllocator() {
+  return std::make_shared<SymmAllocator>(this);
+}
+
+// ------------------------------------------------------------------------------------------
 // coalescing
 // ------------------------------------------------------------------------------------------
 void ProcessGroupCCL::startCoalescing() {

@@ -6,7 +6,7 @@
 // future and result(). Differences by design: no runtime stub registry (device routing is a
 // switch), no process-global mutex, futures complete when the work completes (CPU) or are
 // stream-ordered (CUDA) instead of at enqueue time, and the optional Backend virtuals
-// setTimeout / abort / shutdown / sequence numbers / allocateTensor are implemented.
+// setTimeout / abort / shutdown / sequence numbers / allocateTensor / getMemAllocator are implemented.
 #pragma once
 #include <torch/csrc/distributed/c10d/Backend.hpp>
 #include <torch/csrc/distributed/c10d/Store.hpp>
@@ -132,7 +132,12 @@ class ProcessGroupCCL : public Backend {
   void abort() override;
   void shutdown() override;
   ErrorType getError() override;
-  bool supportsTensorAlloc(c10::DeviceIndex) override { return false; }
+  // Symmetric ("registered") tensors: memory that every rank of the group maps, so that collectives
+  // on it run zero-copy over NVLink instead of staging through the arena. Allocation is collective
+  // in order: every rank allocates the same sizes in the same order (and drops them in the same order).
+  bool supportsTensorAlloc(c10::DeviceIndex) override { return true; }
+  at::Tensor allocateTensor(long size, at::TensorOptions options = {}) override;
+  std::shared_ptr<c10::Allocator> getMemAllocator() override;
 
   // Extras exposed to Python (fused ops, stats, tuning).
   std::chrono::milliseconds timeout() const { return timeout_; }

@@ -55,4 +55,25 @@ def get_backend(group=None, device="cuda"):
     return group._get_backend(torch.device(device))
 
 
+def symm_empty(shape, dtype=torch.float32, group=None, device=None):
+    """An uninitialised SYMMETRIC tensor: memory from the group's symmetric heap, mapped by every rank, so that
+    all_reduce / reduce_scatter_tensor / all_gather_into_tensor on it run zero-copy over NVLink (through the NVSwitch
+    reduction when the heap is bound to a multicast object, CCL_NVLS=1) instead of staging through the arena.
+    Collective in order: every rank of the group must allocate the same sizes in the same order and drop them in the
+    same order. The heap has CCL_SYMM_HEAP_MB megabytes (default 1024) and is created by the first allocation.
+    Same as `backend.allocate_tensor(...)` of torch's Backend API."""
+    shape = (shape,) if isinstance(shape, int) else tuple(shape)
+    numel = 1
+    for s in shape:
+        numel *= int(s)
+    be = get_backend(group, "cuda")
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    return be.symm_empty(numel, dtype, dev).view(shape)
+
+
+def is_symmetric(tensor, group=None):
+    """True if `tensor` lies wholly inside the group's symmetric heap."""
+    return get_backend(group, "cuda").is_symmetric(tensor)
+
+
 from . import ops  # noqa: E402,F401
