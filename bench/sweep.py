@@ -25,22 +25,35 @@ import oneccl_bindings_for_pytorch  # noqa: E402,F401
 DT = {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}
 
 
-def make_op(name, group, n_elems, dtype, world, dev):
-    """Returns (callable taking a buffer index, number of pooled buffers)."""
+def make_op(name, group, n_elems, dtype, world, dev, symmetric=False):
+    """Returns (callable taking a buffer index, number of pooled buffers). `symmetric`: the buffers a
+    peer touches (all_reduce tensor, reduce_scatter input, all_gather output) come from the group's
+    symmetric heap, so the `ccl` backend runs its zero-copy kernels."""
     pool = max(1, min(8, int(256e6 // max(1, n_elems * dtype.itemsize)) + 1))
     g = torch.Generator(device=dev).manual_seed(7)
+
+    def rand(n, symm):
+        t = torch.randn(n, device=dev, generator=g).to(dtype)
+        if symm:
+            import torch_ccl_b200
+
+            st = torch_ccl_b200.symm_empty(n, dtype, group=group)
+            st.copy_(t)
+            return st
+        return t
+
     if name == "all_reduce":
-        bufs = [torch.randn(n_elems, device=dev, generator=g).to(dtype) for _ in range(pool)]
+        bufs = [rand(n_elems, symmetric) for _ in range(pool)]
         return (lambda i: dist.all_reduce(bufs[i % pool], group=group)), pool
     if name == "reduce_scatter":
         n = n_elems // world * world
-        ins = [torch.randn(n, device=dev, generator=g).to(dtype) for _ in range(pool)]
+        ins = [rand(n, symmetric) for _ in range(pool)]
         out = torch.empty(n // world, device=dev, dtype=dtype)
         return (lambda i: dist.reduce_scatter_tensor(out, ins[i % pool], group=group)), pool
     if name == "all_gather":
         n = n_elems // world * world
-        ins = [torch.randn(n // world, device=dev, generator=g).to(dtype) for _ in range(pool)]
-        out = torch.empty(n, device=dev, dtype=dtype)
+        ins = [rand(n // world, False) for _ in range(pool)]
+        out = rand(n, symmetric)
         return (lambda i: dist.all_gather_into_tensor(out, ins[i % pool], group=group)), pool
     if name == "all_to_all":
         n = n_elems // world * world
@@ -78,6 +91,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--backends", default="ccl,nccl")
     ap.add_argument("--out", default="")
+    ap.add_argument("--symmetric", action="store_true",
+                    help="add a third arm: ccl on tensors from the symmetric heap (zero-copy kernels; set CCL_SYMM_HEAP_MB large enough)")
     args = ap.parse_args()
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -106,8 +121,19 @@ def main():
                     row[b] = {"us": round(t * 1e6, 2), "algbw_GBps": round(alg, 2), "busbw_GBps": round(bus, 2)}
                     del fn
                     torch.cuda.empty_cache()
+                if args.symmetric and op != "all_to_all" and "ccl" in groups:
+                    fn, _ = make_op(op, groups["ccl"], n, dtype, world, dev, symmetric=True)
+                    iters = max(3, min(args.iters, int(2e9 // size) + 3))
+                    t = time_op(fn, iters, args.warmup, groups["ccl"], dev)
+                    alg = size / t / 1e9
+                    bus = alg * (2 * (world - 1) / world if op == "all_reduce" else (world - 1) / world)
+                    row["ccl_symmetric"] = {"us": round(t * 1e6, 2), "algbw_GBps": round(alg, 2), "busbw_GBps": round(bus, 2)}
+                    del fn
+                    torch.cuda.empty_cache()
                 if "ccl" in row and "nccl" in row:
                     row["speedup_vs_nccl"] = round(row["nccl"]["us"] / row["ccl"]["us"], 3)
+                if "ccl_symmetric" in row and "nccl" in row:
+                    row["symmetric_speedup_vs_nccl"] = round(row["nccl"]["us"] / row["ccl_symmetric"]["us"], 3)
                 rows.append(row)
                 if rank == 0:
                     print(json.dumps(row), flush=True)

@@ -153,3 +153,65 @@ def test_single_rank_never_builds_a_multicast_object():
     assert not c.allreduce([x], [out], 0, 1.0, 0, 3).startswith("nvls")
     torch.cuda.synchronize()
     assert torch.equal(out, x)
+
+
+def _symmetric_tensors(rank, world):
+    """Tensors from the group's symmetric heap: collectives on them take the zero-copy kernels (through the
+    switch when the heap is bound to a multicast object), plain tensors keep working next to them."""
+    import time
+
+    import torch.distributed as dist
+    import torch_ccl_b200
+
+    be = dist.distributed_c10d._get_default_group()._get_backend(torch.device("cuda"))
+    try:
+        assert be.supports_tensor_alloc(torch.device("cuda", torch.cuda.current_device()))
+        n = (1 << 20) + 8
+        x = torch_ccl_b200.symm_empty(n, torch.bfloat16)
+        y = torch_ccl_b200.symm_empty((2, n // 2), torch.float32)
+        assert torch_ccl_b200.is_symmetric(x) and torch_ccl_b200.is_symmetric(y) and not torch_ccl_b200.is_symmetric(torch.ones(4, device="cuda"))
+        info = be.symm_heap_info(x)
+        assert info["in_use"] >= x.nbytes + y.nbytes
+        for it in range(3):
+            x.copy_(((torch.arange(n, device="cuda") % 13) + rank + it).to(torch.bfloat16))
+            dist.all_reduce(x)
+            want = ((torch.arange(n, device="cuda") % 13) * world + world * it + world * (world - 1) // 2).to(torch.bfloat16)
+            assert torch.equal(x, want), (it, (x != want).sum().item())
+        y.fill_(float(rank + 1))
+        dist.all_reduce(y, op=dist.ReduceOp.AVG)
+        assert torch.allclose(y, torch.full_like(y, (world + 1) / 2))
+        z = torch.full((n,), float(rank), device="cuda")  # a plain tensor between symmetric ones
+        dist.all_reduce(z)
+        assert float(z[0]) == world * (world - 1) / 2
+        # reduce_scatter from a symmetric input (bf16 -> bf16), all_gather into a symmetric output
+        m = 1 << 18
+        full = torch_ccl_b200.symm_empty(m * world, torch.bfloat16)
+        full.copy_(((torch.arange(m * world, device="cuda") % 11) + rank).to(torch.bfloat16))
+        part = torch.empty(m, device="cuda", dtype=torch.bfloat16)
+        dist.reduce_scatter_tensor(part, full)
+        want = ((torch.arange(m * world, device="cuda") % 11) * world + world * (world - 1) // 2).to(torch.bfloat16)
+        assert torch.equal(part, want[rank * m:(rank + 1) * m])
+        gathered = torch_ccl_b200.symm_empty(m * world, torch.bfloat16)
+        dist.all_gather_into_tensor(gathered, part)
+        assert torch.equal(gathered, want)
+        torch.cuda.synchronize()
+        rec = torch_ccl_b200.flight_recorder()
+        assert ("nvls" in rec) == bool(info["multicast"]), rec[-400:]
+        # release in the same order on every rank; the blocks return to the heap
+        del x, y, full, gathered
+        assert be.symm_heap_info(z)["in_use"] == 0
+    finally:
+        torch.cuda.synchronize()
+        store = dist.distributed_c10d._get_default_store()
+        store.add("symm_done", 1)
+        t0 = time.time()
+        while int(store.add("symm_done", 0)) < world and time.time() - t0 < 20:
+            time.sleep(0.01)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+@pytest.mark.parametrize("nvls", ["0", "1"])
+def test_symmetric_tensors_zero_copy(nvls):
+    run_ranks(_symmetric_tensors, world=min(torch.cuda.device_count(), 8), device="cuda",
+              env={"CCL_NVLS": nvls, "CCL_ARENA_MB": "64", "CCL_SYMM_HEAP_MB": "64", "NCCL_NVLS_ENABLE": "0"})

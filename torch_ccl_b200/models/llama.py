@@ -322,11 +322,13 @@ class TPLlamaDecoder:
         return out_pinned
 
     # ------------------------------------------------------------------------------------
-    def prefill(self, prompt):
-        """Runs the prompt [B, S] through the model one sequence at a time, fills the KV caches
-        and leaves the first generated token in self.tokens. Uses the same GEMM kernel in its
-        row-major form, the two-shot all_reduce and the fused norm; attention over the prompt
-        itself uses torch's scaled_dot_product_attention."""
+    def prefill(self, prompt, chunk_seqs=None):
+        """Runs the prompt [B, S] through the model, fills the KV caches and leaves the first generated
+        token in self.tokens. All sequences of a chunk go through every layer together ([chunk * S]
+        rows per GEMM): the same tcgen05 GEMM in its row-major form, the staged all_reduce fused with
+        residual add + norm (in slices that fit the communicator's staging arena), and torch's
+        scaled_dot_product_attention for the causal attention over the prompt itself.
+        `chunk_seqs` bounds the sequences per pass (default: as many as keep a pass under ~32k rows)."""
         cfg = self.cfg
         B, S = prompt.shape
         hd, H = cfg.head_dim, cfg.hidden
@@ -335,52 +337,58 @@ class TPLlamaDecoder:
         cos = self.cos[:S].to(torch.bfloat16)[None, :, None, :]
         sin = self.sin[:S].to(torch.bfloat16)[None, :, None, :]
 
-        def rope(t):  # [1, S, heads, hd]
+        def rope(t):  # [n, S, heads, hd]
             t1, t2 = t[..., : hd // 2], t[..., hd // 2:]
             return torch.cat([t1 * cos - t2 * sin, t2 * cos + t1 * sin], dim=-1)
 
-        cap_rows = 1024 if self.world > 1 else S  # rows per fused-norm launch (arena capacity)
-        for b in range(B):
-            toks = prompt[b].to(dev)
-            x = torch.empty(S, H, **bf)
+        cap_rows = 1024 if self.world > 1 else 1 << 30  # rows per fused-norm launch (staging capacity)
+        per = chunk_seqs or max(1, 32768 // S)
+        for b0 in range(0, B, per):
+            n = min(per, B - b0)
+            R = n * S
+            toks = prompt[b0:b0 + n].reshape(-1).to(dev)
+            x = torch.empty(R, H, **bf)
             self._embed_partial(toks, x)
-            h = torch.zeros(S, H, **bf)
-            xn = torch.empty(S, H, **bf)
+            h = torch.zeros(R, H, **bf)
+            xn = torch.empty(R, H, **bf)
 
             def norm_step(w):
-                for r0 in range(0, S, cap_rows):
-                    r1 = min(S, r0 + cap_rows)
+                for r0 in range(0, R, cap_rows):
+                    r1 = min(R, r0 + cap_rows)
                     self.comm.ar_res_norm(x[r0:r1], h[r0:r1], w, xn[r0:r1], cfg.eps)
 
             norm_step(self.layers[0]["attn_norm"])
+            qkv = torch.empty(R, (self.nh + 2 * self.nkv) * hd, **bf)
+            attn = torch.empty(R, self.nh * hd, **bf)
+            act = torch.empty(R, self.inter, **bf)
             for li, L in enumerate(self.layers):
-                qkv = torch.empty(S, (self.nh + 2 * self.nkv) * hd, **bf)
                 self._gemm_t(L["wqkv"], xn, qkv, self.qkv_rows)
-                q = rope(qkv[:, : self.nh * hd].view(1, S, self.nh, hd))
-                k = rope(qkv[:, self.nh * hd:(self.nh + self.nkv) * hd].view(1, S, self.nkv, hd))
-                v = qkv[:, (self.nh + self.nkv) * hd:].view(1, S, self.nkv, hd)
-                L["k"][b, :, :S] = k[0].transpose(0, 1)
-                L["v"][b, :, :S] = v[0].transpose(0, 1)
+                q = rope(qkv[:, : self.nh * hd].view(n, S, self.nh, hd))
+                k = rope(qkv[:, self.nh * hd:(self.nh + self.nkv) * hd].view(n, S, self.nkv, hd))
+                v = qkv[:, (self.nh + self.nkv) * hd:].view(n, S, self.nkv, hd)
+                L["k"][b0:b0 + n, :, :S] = k.transpose(1, 2)
+                L["v"][b0:b0 + n, :, :S] = v.transpose(1, 2)
                 o = torch.nn.functional.scaled_dot_product_attention(
                     q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
                     enable_gqa=self.nh != self.nkv)
-                attn = o.transpose(1, 2).reshape(S, self.nh * hd).contiguous()
+                attn.copy_(o.transpose(1, 2).reshape(R, self.nh * hd))
                 self._gemm_t(L["wo"], attn, x, cfg.hidden)
                 norm_step(L["mlp_norm"])
-                act = torch.empty(S, self.inter, **bf)
                 self._gemm_t(L["wgu"], xn, act, self.inter, dual=self.inter_pad)
                 self._gemm_t(L["wd"], act, x, cfg.hidden)
                 nw = self.layers[li + 1]["attn_norm"] if li + 1 < cfg.n_layers else self.final_norm
                 norm_step(nw)
-            logits = torch.empty(1, self.vshard, device=dev, dtype=torch.float32)
-            self._gemm_t(self.lm_head, xn[S - 1:S].contiguous(), logits, self.vshard)
+            last = xn.view(n, S, H)[:, S - 1].contiguous()
+            logits = torch.empty(n, self.vshard, device=dev, dtype=torch.float32)
+            self._gemm_t(self.lm_head, last, logits, self.vshard)
             val, idx = logits.max(dim=-1)
             if self.world > 1:
-                mine = torch.stack([val, (idx + self.rank * self.vshard).float()], dim=-1)
-                allb = torch.empty(self.world, 1, 2, device=dev)
+                mine = torch.stack([val, (idx + self.rank * self.vshard).float()], dim=-1).contiguous()
+                allb = torch.empty(self.world, n, 2, device=dev)
                 self.comm.all_gather(mine, allb)
-                idx = allb[allb[:, 0, 0].argmax(), :, 1].to(torch.int64)
-            self.tokens[b] = idx[0]
+                win = allb[:, :, 0].argmax(dim=0)
+                idx = allb[:, :, 1].gather(0, win[None, :])[0].to(torch.int64)
+            self.tokens[b0:b0 + n] = idx
         self.positions[:B] = S
         torch.cuda.synchronize(dev)
 
