@@ -461,6 +461,25 @@ cudaError_t CudaComm::rooted(std::vector<CollArgs> args, cudaStream_t stream) {
   return e;
 }
 
+bool CudaComm::multi_fits(int dtype, const MultiArgs& a) const {
+  return world_ > 1 && a.n >= 1 && a.n <= kMaxMulti && cfg_.ablate == kAblateNone &&
+         multi_slot_bytes(dtype, a) * (size_t)world_ <= cfg_.half_bytes;
+}
+
+cudaError_t CudaComm::multi(int dtype, std::vector<MultiArgs> args, cudaStream_t stream) {
+  CCL_CHECK_ARGS(args)
+  DeviceGuard g(device_);
+  enter_stream(stream);
+  if (!multi_fits(dtype, args[0])) return cudaErrorInvalidValue;
+  const size_t slot = multi_slot_bytes(dtype, args[0]);
+  for (auto& a : args) a.slot_bytes = slot;
+  const size_t vecs = slot / 16;
+  LaunchCfg lc = launch_cfg(blocks_for(vecs, std::min(cfg_.max_blocks, 64)), threads_for(vecs, blocks_for(vecs, std::min(cfg_.max_blocks, 64)), cfg_.threads), stream);
+  cudaError_t e = launch_multi(dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
+  if (e == cudaSuccess) ++launches_;
+  return e;
+}
+
 cudaError_t CudaComm::barrier(cudaStream_t stream) {
   DeviceGuard g(device_);
   enter_stream(stream);

@@ -22,6 +22,7 @@
 
 #include "cuda/SymmMem.h"
 #include "cuda/kernels/collectives.h"
+#include "cuda/kernels/collectives_multi.h"
 #include "cuda/kernels/collectives_symm.h"
 #include "cuda/kernels/decode_fused.h"
 #include "cuda/kernels/gemm_collective.h"
@@ -103,6 +104,12 @@ class CudaComm {
   // ranks' flags (which nothing sets) runs into the bounded-wait budget and reports a timeout.
   cudaError_t barrier_single_rank(int i, cudaStream_t stream);
   cudaError_t allreduce_residual_rmsnorm(int dtype, std::vector<FusedNormArgs> args, cudaStream_t stream);
+
+  // A list of small tensors in ONE launch (see collectives_multi.h). `args` has nctx() entries with the same
+  // n / mode / counts. Returns cudaErrorInvalidValue when the list does not fit the staging arena (or has more
+  // than kMaxMulti tensors): the caller then issues the tensors one by one. multi_fits tells in advance.
+  bool multi_fits(int dtype, const MultiArgs& a) const;
+  cudaError_t multi(int dtype, std::vector<MultiArgs> args, cudaStream_t stream);
 
   // Decode step: row-parallel projection + all_reduce + residual + RMSNorm in one launch, and
   // arg-max + all-gather of the winners (see decode_fused.h). fits_gemm_ar_norm tells whether the

@@ -66,6 +66,27 @@ ccl::cpu::ReduceDesc cpu_reduce_desc(const ReduceOp& op, at::ScalarType st, int 
   return d;
 }
 
+// Sends `n` tensors through CudaComm::multi in chunks of kMaxMulti (one launch per chunk). `head` carries mode / op /
+// scale, `entry(m, i)` writes tensor i into slot m.n of a chunk. Returns false without launching anything when a chunk
+// does not fit the staging arena; the caller then issues the tensors one by one.
+template <typename Entry>
+bool run_multi(ccl::CudaComm& c, int dtype, size_t n, const ccl::MultiArgs& head, cudaStream_t s, Entry entry) {
+  std::vector<ccl::MultiArgs> chunks;
+  for (size_t i = 0; i < n;) {
+    ccl::MultiArgs m = head;
+    m.n = 0;
+    for (; i < n && m.n < ccl::kMaxMulti; ++i) {
+      entry(m, i);
+      if (m.count[m.n] != 0) ++m.n;   // empty tensors take no slot
+    }
+    if (m.n == 0) continue;
+    if (!c.multi_fits(dtype, m)) return false;
+    chunks.push_back(m);
+  }
+  for (auto& m : chunks) C10_CUDA_CHECK(c.multi(dtype, {m}, s));
+  return true;
+}
+
 void fill_reduce(ccl::CollArgs& a, const ccl::ReduceSpec& s, at::ScalarType st) {
   a.op = s.kind;
   if (s.has_scale) {
@@ -535,6 +556,26 @@ static c10::intrusive_ptr<Work> allreduce_impl(ProcessGroupCCL& pg, std::vector<
     return pg.cudaImpl(ts[0].device()).run(type, "oneccl_bindings_for_pytorch::cuda::allreduce", ts[0].device(),
         [ts, specs, disabled](ccl::CudaComm& c, cudaStream_t s) {
           std::string tag = "noop";
+          // a list of small tensors (DDP buckets, coalesced calls): one launch over a pointer table
+          if (ts.size() > 1 && c.world() > 1 && !disabled) {
+            bool uniform = true;
+            for (size_t i = 1; i < ts.size(); ++i)
+              uniform = uniform && specs[i].kind == specs[0].kind && specs[i].has_scale == specs[0].has_scale &&
+                        specs[i].is_avg == specs[0].is_avg && specs[i].scale == specs[0].scale;
+            ccl::CollArgs proto;
+            fill_reduce(proto, specs[0], ts[0].scalar_type());
+            ccl::MultiArgs head;
+            head.mode = ccl::kMultiAllReduce;
+            head.op = proto.op;
+            head.has_scale = proto.has_scale;
+            head.scale = proto.scale;
+            if (uniform && run_multi(c, ccl_py::to_ccl_dtype(ts[0].scalar_type()), ts.size(), head, s, [&](ccl::MultiArgs& m, size_t i) {
+                  m.in[m.n] = ts[i].data_ptr();
+                  m.out[m.n] = ts[i].data_ptr();
+                  m.count[m.n] = (uint64_t)ts[i].numel();
+                }))
+              return std::string("multi");
+          }
           for (size_t i = 0; i < ts.size(); ++i) {
             const at::Tensor& t = ts[i];
             if (t.numel() == 0 || disabled) continue;
@@ -641,6 +682,24 @@ static c10::intrusive_ptr<Work> allgather_pieces(ProcessGroupCCL& pg, OpType typ
     for (auto& l : outs) keep.insert(keep.end(), l.begin(), l.end());
     return pg.cudaImpl(ins[0].device()).run(type, title_cuda, ins[0].device(),
         [ins, outs](ccl::CudaComm& c, cudaStream_t s) {
+          // several flat gathers (FSDP2 parameter groups, coalesced calls): one launch over a pointer table
+          if (ins.size() > 1 && c.world() > 1) {
+            bool flat = true;
+            for (size_t i = 0; i < ins.size() && flat; ++i) {
+              const size_t pb = (size_t)ins[i].numel() * ins[i].element_size();
+              for (int p = 0; p < c.world() && flat; ++p)
+                flat = (size_t)outs[i][p].numel() * outs[i][p].element_size() == pb &&
+                       outs[i][p].data_ptr() == static_cast<char*>(outs[i][0].data_ptr()) + (size_t)p * pb;
+            }
+            ccl::MultiArgs head;
+            head.mode = ccl::kMultiAllGather;
+            if (flat && run_multi(c, ccl::kU8, ins.size(), head, s, [&](ccl::MultiArgs& m, size_t i) {
+                  m.in[m.n] = ins[i].data_ptr();
+                  m.out[m.n] = outs[i][0].data_ptr();
+                  m.count[m.n] = (uint64_t)ins[i].numel() * ins[i].element_size();
+                }))
+              return std::string("multi");
+          }
           for (size_t i = 0; i < ins.size(); ++i) {
             ccl::CollArgs a;
             a.in = ins[i].data_ptr();
@@ -883,6 +942,31 @@ static c10::intrusive_ptr<Work> reduce_scatter_pieces(ProcessGroupCCL& pg, OpTyp
     for (auto& o : outs) specs.push_back(ccl::make_reduce_spec(rop, o.scalar_type(), W));
     return pg.cudaImpl(outs[0].device()).run(type, title_cuda, outs[0].device(),
         [ins, outs, specs](ccl::CudaComm& c, cudaStream_t s) {
+          // several flat reduce_scatters of one dtype (FSDP2 gradient groups, coalesced calls): one launch over a pointer table
+          if (outs.size() > 1 && c.world() > 1) {
+            bool flat = true;
+            for (size_t i = 0; i < outs.size() && flat; ++i) {
+              const size_t pb = (size_t)outs[i].numel() * outs[i].element_size();
+              flat = outs[i].scalar_type() == outs[0].scalar_type() && specs[i].kind == specs[0].kind && specs[i].has_scale == specs[0].has_scale &&
+                     specs[i].is_avg == specs[0].is_avg && specs[i].scale == specs[0].scale;
+              for (int p = 0; p < c.world() && flat; ++p)
+                flat = ins[i][p].numel() == outs[i].numel() && ins[i][p].scalar_type() == outs[i].scalar_type() &&
+                       ins[i][p].data_ptr() == static_cast<char*>(ins[i][0].data_ptr()) + (size_t)p * pb;
+            }
+            ccl::CollArgs proto;
+            fill_reduce(proto, specs[0], outs[0].scalar_type());
+            ccl::MultiArgs head;
+            head.mode = ccl::kMultiReduceScatter;
+            head.op = proto.op;
+            head.has_scale = proto.has_scale;
+            head.scale = proto.scale;
+            if (flat && run_multi(c, ccl_py::to_ccl_dtype(outs[0].scalar_type()), outs.size(), head, s, [&](ccl::MultiArgs& m, size_t i) {
+                  m.in[m.n] = ins[i][0].data_ptr();
+                  m.out[m.n] = outs[i].data_ptr();
+                  m.count[m.n] = (uint64_t)outs[i].numel();
+                }))
+              return std::string("multi");
+          }
           for (size_t i = 0; i < outs.size(); ++i) {
             ccl::CollArgs a;
             bool any = false;
