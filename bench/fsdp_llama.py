@@ -1,11 +1,17 @@
 """Full-shard (ZeRO-3) training step of a Llama-architecture model: bf16 parameters and compute,
 fp32 gradient reduction and master weights, sequence 2048, micro-batch 1 per GPU, uniform random
-token ids — the fused-collective engine of this repository (`torch_ccl_b200.parallel.fsdp`, comm
-"ccl": all_gather with direct copy-out, reduce_scatter with fused average + fp32 cast) against the
-same schedule on torch's NCCL backend (comm "c10d").
+token ids. Arms (`--arms`, comma separated):
+
+  ccl          the fused-collective engine of this repository (`torch_ccl_b200.parallel.fsdp`: all_gather with
+               direct copy-out, reduce_scatter with fused average + fp32 cast) on the `ccl` backend
+  nccl         the same engine and schedule on plain torch.distributed calls over torch's NCCL backend
+  fsdp2        stock `torch.distributed.fsdp.fully_shard` (bf16 parameters, fp32 reduce, activation
+               checkpointing per layer) over NCCL - what a user of the stock stack runs
+  fsdp2_ccl    the same stock fully_shard model over the `ccl` backend (the usage the reference tests:
+               tests/test_fsdp.py:153 of intel/torch-ccl)
 
     torchrun --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 bench/fsdp_llama.py \
-        [--layers 32] [--hidden 4096] [--ffn 11008] [--seq 2048] [--steps 5]
+        [--layers 32] [--hidden 4096] [--ffn 11008] [--seq 2048] [--steps 5] [--comm-blocks 48]
 
 Device-timed (CUDA events), max over ranks; prints step time and tokens/s of the whole job.
 """
@@ -106,6 +112,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--arms", default="ccl,nccl")
+    ap.add_argument("--comm-blocks", type=int, default=0, help="CTA cap of the ccl collectives while they overlap compute (0: library default)")
     a = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -113,25 +120,55 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("ccl", rank=rank, world_size=world)
     results = {}
+    nccl_group = None
     for arm in a.arms.split(","):
-        group = None if arm == "ccl" else dist.new_group(backend="nccl")
-        # build unit by unit so that only one full layer is ever resident next to the shards
-        engine = None
-        mods = build(a, dev)
-        engine = FullyShardedSequential(mods, group=group, comm="ccl" if arm == "ccl" else "c10d")
-        opt = torch.optim.AdamW(engine.master_params(), lr=1e-4, fused=True)
+        if arm in ("nccl", "fsdp2") and nccl_group is None:
+            nccl_group = dist.new_group(backend="nccl")
         g = torch.Generator().manual_seed(1 + rank)
+        mods = build(a, dev)
+        if arm in ("ccl", "nccl"):
+            engine = FullyShardedSequential(mods, group=None if arm == "ccl" else nccl_group, comm="ccl" if arm == "ccl" else "c10d",
+                                            comm_blocks=a.comm_blocks or None)
+            opt = torch.optim.AdamW(engine.master_params(), lr=1e-4, fused=True)
 
-        def step():
-            ids = torch.randint(0, a.vocab, (1, a.seq), generator=g).to(dev)
-            labels = torch.randint(0, a.vocab, (1, a.seq), generator=g).to(dev)
-            logits = engine(ids)
-            loss = F.cross_entropy(logits.float().view(-1, a.vocab), labels.view(-1))
-            loss.backward()
-            engine.master_params()
-            opt.step()
-            engine.after_step()
-            return loss
+            def step():
+                ids = torch.randint(0, a.vocab, (1, a.seq), generator=g).to(dev)
+                labels = torch.randint(0, a.vocab, (1, a.seq), generator=g).to(dev)
+                logits = engine(ids)
+                loss = F.cross_entropy(logits.float().view(-1, a.vocab), labels.view(-1))
+                loss.backward()
+                engine.master_params()
+                opt.step()
+                engine.after_step()
+                return loss
+        else:
+            from torch.distributed.device_mesh import DeviceMesh
+            from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+            from torch.utils.checkpoint import checkpoint
+
+            grp = nccl_group if arm == "fsdp2" else dist.group.WORLD
+            mesh = DeviceMesh.from_group(grp, "cuda", mesh=list(range(world)))
+            mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+            for m in mods:
+                fully_shard(m, mesh=mesh, mp_policy=mp)
+            engine = nn.ModuleList(mods)
+            opt = torch.optim.AdamW(engine.parameters(), lr=1e-4, fused=True)
+
+            def run_model(ids):
+                x = mods[0](ids)
+                for blk in mods[1:-1]:
+                    x = checkpoint(blk, x, use_reentrant=False)  # recompute activations per layer, like the engine above
+                return mods[-1](x)
+
+            def step():
+                ids = torch.randint(0, a.vocab, (1, a.seq), generator=g).to(dev)
+                labels = torch.randint(0, a.vocab, (1, a.seq), generator=g).to(dev)
+                logits = run_model(ids)
+                loss = F.cross_entropy(logits.float().view(-1, a.vocab), labels.view(-1))
+                loss.backward()
+                opt.step()
+                opt.zero_grad(set_to_none=True)
+                return loss
 
         for _ in range(a.warmup):
             step()
@@ -148,14 +185,17 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         results[arm] = {"ms_per_step": round(float(t), 2), "tokens_per_s": round(world * a.seq / (float(t) * 1e-3), 1),
                         "final_loss": round(float(loss), 4)}
-        del engine, opt, mods
+        del engine, opt, mods, step
         torch.cuda.empty_cache()
     if rank == 0:
         out = {"bench": "fsdp_llama", "world": world, "layers": a.layers, "hidden": a.hidden, "ffn": a.ffn, "seq": a.seq,
                "micro_batch": 1, "dtype": "bf16 params/compute, fp32 reduce + master"}
         out.update(results)
+        out["comm_blocks"] = a.comm_blocks
         if "ccl" in results and "nccl" in results:
             out["speedup_vs_nccl"] = round(results["nccl"]["ms_per_step"] / results["ccl"]["ms_per_step"], 3)
+        if "ccl" in results and "fsdp2" in results:
+            out["speedup_vs_torch_fsdp2_nccl"] = round(results["fsdp2"]["ms_per_step"] / results["ccl"]["ms_per_step"], 3)
         print(json.dumps(out))
     dist.destroy_process_group()
 

@@ -413,6 +413,35 @@ struct PyComm {
   }
   int moe_capacity(int hidden) { return comm->moe_capacity(hidden); }
 
+  // Batched small-tensor collective: ins[r] / outs[r] = the list of tensors of rank r. mode 0 all_reduce, 1 reduce_scatter
+  // (ins[r][t] holds world pieces), 2 all_gather (outs[r][t] holds world pieces). Returns false if the list does not fit.
+  bool multi(int mode, std::vector<std::vector<at::Tensor>> ins, std::vector<std::vector<at::Tensor>> outs, int op, double scale, int has_scale) {
+    check_n(ins.size());
+    std::vector<ccl::MultiArgs> args(ins.size());
+    const int W = comm->world();
+    for (size_t i = 0; i < ins.size(); ++i) {
+      ccl::MultiArgs& m = args[i];
+      m.mode = mode;
+      m.op = op;
+      m.scale = (float)scale;
+      m.has_scale = has_scale;
+      TORCH_CHECK(ins[i].size() == outs[i].size() && (int)ins[i].size() <= ccl::kMaxMulti, "bad tensor lists");
+      for (size_t t = 0; t < ins[i].size(); ++t) {
+        TORCH_CHECK(ins[i][t].is_contiguous() && outs[i][t].is_contiguous(), "contiguous tensors required");
+        m.in[m.n] = ins[i][t].data_ptr();
+        m.out[m.n] = outs[i][t].data_ptr();
+        m.count[m.n] = mode == ccl::kMultiAllReduce ? ins[i][t].numel()
+                       : mode == ccl::kMultiReduceScatter ? ins[i][t].numel() / W
+                                                           : ins[i][t].numel() * ins[i][t].element_size();
+        ++m.n;
+      }
+    }
+    const int dt = mode == ccl::kMultiAllGather ? (int)ccl::kU8 : to_ccl_dtype(ins[0][0].scalar_type());
+    if (!comm->multi_fits(dt, args[0])) return false;
+    cu(comm->multi(dt, args, stream()), "multi");
+    return true;
+  }
+
   // One symmetric block of `nbytes`: a uint8 tensor per played rank, all at the same heap offset. The block returns to
   // the heap when the FIRST tensor of the list is released.
   std::vector<at::Tensor> symm_empty(int64_t nbytes) {
@@ -565,6 +594,8 @@ void bind_cuda_comm(py::module& m) {
       .def("fits_gemm_ar_norm", [](PyComm& c, int rows, int hidden, int k) { return c.comm->fits_gemm_ar_norm(rows, hidden, k); })
       .def("sample_allgather", &PyComm::sample_allgather, py::arg("logits"), py::arg("next_tokens"), py::arg("tokens") = py::none(),
            py::arg("positions") = py::none())
+      .def("multi", &PyComm::multi, py::arg("mode"), py::arg("ins"), py::arg("outs"), py::arg("op") = 0, py::arg("scale") = 1.0,
+           py::arg("has_scale") = 0)
       .def("symm_empty", &PyComm::symm_empty)
       .def("heap_in_use", &PyComm::heap_in_use)
       .def("set_symm_min_bytes", [](PyComm& c, int64_t b) { c.comm->mutable_config().symm_min_bytes = (size_t)b; })

@@ -56,6 +56,14 @@ template <typename T> struct Multimem {
   static __device__ __forceinline__ uint4 ld_reduce(const void*) { return make_uint4(0, 0, 0, 0); }
 };
 
+constexpr int kUnrollMc = 4;   // multicast loads in flight per thread
+
+// N output elements as one aligned store (16 bytes, or 32 when bf16 / f16 is widened to fp32).
+template <typename TOut, int N>
+struct alignas(sizeof(TOut) * N >= 32 ? 32 : 16) OutVec {
+  TOut v[N];
+};
+
 #define CCL_SYMM_CTX                                               \
   const RankCtx& ctx = EMU ? L.ctx_table[blockIdx.y] : L.ctx;      \
   const SymmArgs& a = EMU ? L.args_table[blockIdx.y] : L.args;     \
@@ -120,15 +128,32 @@ __global__ void __launch_bounds__(512) allreduce_symm_kernel(const __grid_consta
   bool ok = sy.wait_all(0, 0);
   if (ok) {
     const bool mc = a.use_mc != 0;
-    for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
-      const size_t v = vb + j;
-      const Vec<T> res = scale_vec<T>(reduce_at<T, EMU>(ctx, a.in_off + v * 16, W, a.op, mc), a);
-      if (mc && !EMU) {
-        ptx::multimem_st_v4(ctx.mc_heap + a.out_off + v * 16, *reinterpret_cast<const uint4*>(&res));
-      } else {
+    const size_t nt = blockDim.x;
+    size_t j = r.j0 + threadIdx.x;
+    if (mc && !EMU) {
+      // through the switch: one reducing load and one multicast store per vector; kUnrollMc of them are
+      // in flight per thread, which is what covers the NVLink round trip at full rate
+      for (; j + (kUnrollMc - 1) * nt < r.j1; j += kUnrollMc * nt) {
+        Vec<T> res[kUnrollMc];
+#pragma unroll
+        for (int u = 0; u < kUnrollMc; ++u) *reinterpret_cast<uint4*>(&res[u]) = Multimem<T>::ld_reduce(ctx.mc_heap + a.in_off + (vb + j + u * nt) * 16);
+#pragma unroll
+        for (int u = 0; u < kUnrollMc; ++u) {
+          res[u] = scale_vec<T>(res[u], a);
+          ptx::multimem_st_v4(ctx.mc_heap + a.out_off + (vb + j + u * nt) * 16, *reinterpret_cast<const uint4*>(&res[u]));
+        }
+      }
+      for (; j < r.j1; j += nt) {
+        const Vec<T> res = scale_vec<T>(reduce_at<T, EMU>(ctx, a.in_off + (vb + j) * 16, W, a.op, true), a);
+        ptx::multimem_st_v4(ctx.mc_heap + a.out_off + (vb + j) * 16, *reinterpret_cast<const uint4*>(&res));
+      }
+    } else {
+      // peer loads: one load per rank is in flight per thread already
+      for (; j < r.j1; j += nt) {
+        const Vec<T> res = scale_vec<T>(reduce_at<T, EMU>(ctx, a.in_off + (vb + j) * 16, W, a.op, false), a);
 #pragma unroll
         for (int p = 0; p < kMaxRanks; ++p)
-          if (p < W) ptx::st_v4(ctx.heap[p] + a.out_off + v * 16, *reinterpret_cast<const uint4*>(&res));
+          if (p < W) ptx::st_v4(ctx.heap[p] + a.out_off + (vb + j) * 16, *reinterpret_cast<const uint4*>(&res));
       }
     }
   }
@@ -153,17 +178,30 @@ __global__ void __launch_bounds__(512) reduce_scatter_symm_kernel(const __grid_c
   if (ok) {
     const bool mc = a.use_mc != 0;
     const size_t base = a.in_off + (size_t)me * pv * 16;
-    for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
-      const Vec<TIn> red = reduce_at<TIn, EMU>(ctx, base + j * 16, W, a.op, mc);
-      // widen (bf16 / f16 gradients kept as fp32) and scale in the same pass
+    const size_t nt = blockDim.x;
+    // widen (bf16 / f16 gradients kept as fp32) and scale in the same pass
+    auto emit = [&](size_t j, const Vec<TIn>& red) {
+      OutVec<TOut, N> o;
 #pragma unroll
       for (int t = 0; t < N; ++t) {
         A x = to_acc(red.v[t]);
         if (a.has_scale == 1) x = static_cast<A>(x * static_cast<A>(a.scale));
         else if (a.has_scale == 2) x = static_cast<A>(x / static_cast<A>(a.scale));
-        out[j * N + t] = static_cast<TOut>(from_acc<TOut, A>(x));
+        o.v[t] = static_cast<TOut>(from_acc<TOut, A>(x));
+      }
+      *reinterpret_cast<OutVec<TOut, N>*>(out + j * N) = o;
+    };
+    size_t j = r.j0 + threadIdx.x;
+    if (mc && !EMU) {
+      for (; j + (kUnrollMc - 1) * nt < r.j1; j += kUnrollMc * nt) {
+        Vec<TIn> red[kUnrollMc];
+#pragma unroll
+        for (int u = 0; u < kUnrollMc; ++u) *reinterpret_cast<uint4*>(&red[u]) = Multimem<TIn>::ld_reduce(ctx.mc_heap + base + (j + u * nt) * 16);
+#pragma unroll
+        for (int u = 0; u < kUnrollMc; ++u) emit(j + u * nt, red[u]);
       }
     }
+    for (; j < r.j1; j += nt) emit(j, reduce_at<TIn, EMU>(ctx, base + j * 16, W, a.op, mc));
   }
   sy.signal_all(1, 0);
   sy.wait_all(1, 0);   // the peers have finished reading this rank's input
@@ -184,7 +222,24 @@ __global__ void __launch_bounds__(512) all_gather_symm_kernel(const __grid_const
   if (ok) {
     const size_t base = a.out_off + (size_t)me * pv * 16;
     const bool mc = a.use_mc != 0 && !EMU;
-    for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
+    const size_t nt = blockDim.x;
+    size_t j = r.j0 + threadIdx.x;
+    for (; j + 3 * nt < r.j1; j += 4 * nt) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const uint4*>(in + (j + u * nt) * 16);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (mc) {
+          ptx::multimem_st_v4(ctx.mc_heap + base + (j + u * nt) * 16, v[u]);
+        } else {
+#pragma unroll
+          for (int p = 0; p < kMaxRanks; ++p)
+            if (p < W) ptx::st_v4(ctx.heap[p] + base + (j + u * nt) * 16, v[u]);
+        }
+      }
+    }
+    for (; j < r.j1; j += nt) {
       const uint4 v = *reinterpret_cast<const uint4*>(in + j * 16);
       if (mc) {
         ptx::multimem_st_v4(ctx.mc_heap + base + j * 16, v);

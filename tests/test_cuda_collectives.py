@@ -61,6 +61,40 @@ def _allreduce(rank, world):
             assert torch.all(t == sum(range(world)) + world * i)
 
 
+def _coalesced(rank, world):
+    """The *_coalesced entry points: a list of small tensors goes out as ONE kernel launch (pointer table)."""
+    import torch_ccl_b200
+
+    be = dist.group.WORLD._get_backend(torch.device("cuda"))
+    sizes = [3, 1000, 17, 40000]
+    ts = [torch.full((n,), float(rank + i), device="cuda") for i, n in enumerate(sizes)]
+    n0 = be.cuda_kernel_launches(ts[0])
+    dist.all_reduce_coalesced(ts)
+    torch.cuda.synchronize()
+    assert be.cuda_kernel_launches(ts[0]) == n0 + 1, "one launch for the whole list"
+    for i, t in enumerate(ts):
+        assert torch.all(t == sum(range(world)) + world * i)
+    assert "multi" in torch_ccl_b200.flight_recorder()
+    ins = [_data(rank, n, torch.bfloat16, salt=i).cuda() for i, n in enumerate(sizes)]
+    outs = [torch.empty(n * world, dtype=torch.bfloat16, device="cuda") for n in sizes]
+    n0 = be.cuda_kernel_launches(ts[0])
+    dist.group.WORLD.allgather_into_tensor_coalesced(outs, ins).wait()
+    torch.cuda.synchronize()
+    assert be.cuda_kernel_launches(ts[0]) == n0 + 1
+    for i, n in enumerate(sizes):
+        assert torch.equal(outs[i].cpu(), torch.cat([_data(r, n, torch.bfloat16, salt=i) for r in range(world)]))
+    full = [_data(rank, n * world, salt=10 + i).cuda() for i, n in enumerate(sizes)]
+    parts = [torch.empty(n, device="cuda") for n in sizes]
+    n0 = be.cuda_kernel_launches(ts[0])
+    dist.group.WORLD.reduce_scatter_tensor_coalesced(parts, full).wait()
+    torch.cuda.synchronize()
+    assert be.cuda_kernel_launches(ts[0]) == n0 + 1
+    for i, n in enumerate(sizes):
+        ref = torch.stack([_data(r, n * world, salt=10 + i) for r in range(world)]).sum(0)[rank * n:(rank + 1) * n]
+        torch.testing.assert_close(parts[i].cpu(), ref, rtol=1e-5, atol=1e-5)
+    dist.barrier()
+
+
 def _rooted(rank, world):
     n = 300001
     xs = [_data(r, n) for r in range(world)]
@@ -176,7 +210,7 @@ def _p2p(rank, world):
     dist.barrier()
 
 
-@pytest.mark.parametrize("fn", [_allreduce, _rooted, _gather_scatter_family, _work_semantics_and_ddp, _p2p],
+@pytest.mark.parametrize("fn", [_allreduce, _coalesced, _rooted, _gather_scatter_family, _work_semantics_and_ddp, _p2p],
                          ids=lambda f: f.__name__.strip("_"))
 def test_cuda_ranks(fn):
     run_ranks(fn, world=_world(), device="cuda", env={"NCCL_NVLS_ENABLE": "0", "CCL_ARENA_MB": "64"}, timeout=300)

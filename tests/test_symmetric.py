@@ -124,3 +124,48 @@ def test_all_gather_zero_copy(comm, world):
     ref = torch.cat(pieces)
     for r in range(world):
         assert torch.equal(outs[r], ref)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.int32])
+def test_batched_small_tensor_collectives(comm, world, dtype):
+    """A list of tensors in ONE launch: all_reduce, reduce_scatter and all_gather over a pointer table."""
+    c = comm(world)
+    torch.manual_seed(world)
+    sizes = [1, 7, 4096, 333, 8, 20003]
+    data = [[(torch.randn(n) * 2).to(dtype) for n in sizes] for _ in range(world)]
+    tol = {torch.bfloat16: 2e-2, torch.float32: 1e-5, torch.int32: 0}[dtype]
+    before = c.launches
+    # all_reduce (in place), averaged
+    bufs = [[t.clone().cuda() for t in data[r]] for r in range(world)]
+    scaled = dtype != torch.int32
+    assert c.multi(0, bufs, bufs, 0, 1.0 / world if scaled else 1.0, 1 if scaled else 0)
+    torch.cuda.synchronize()
+    assert c.status()[0] == 0 and c.launches == before + 1
+    for t, n in enumerate(sizes):
+        ref = torch.stack([data[r][t].double() for r in range(world)]).sum(0) / (world if scaled else 1)
+        for r in range(world):
+            torch.testing.assert_close(bufs[r][t].cpu().double(), ref.to(dtype).double(), rtol=tol, atol=tol * world * 2)
+    # reduce_scatter: every tensor holds `world` pieces
+    full = [[(torch.randn(n * world) * 2).to(dtype) for n in sizes] for _ in range(world)]
+    ins = [[t.cuda() for t in full[r]] for r in range(world)]
+    outs = [[torch.empty(n, dtype=dtype, device="cuda") for n in sizes] for _ in range(world)]
+    assert c.multi(1, ins, outs)
+    torch.cuda.synchronize()
+    for t, n in enumerate(sizes):
+        ref = torch.stack([full[r][t].double() for r in range(world)]).sum(0).to(dtype)
+        for r in range(world):
+            torch.testing.assert_close(outs[r][t].cpu().double(), ref[r * n:(r + 1) * n].double(), rtol=tol, atol=tol * world * 2)
+    # all_gather
+    pieces = [[t.cuda() for t in data[r]] for r in range(world)]
+    gathered = [[torch.empty(n * world, dtype=dtype, device="cuda") for n in sizes] for _ in range(world)]
+    assert c.multi(2, pieces, gathered)
+    torch.cuda.synchronize()
+    assert c.status()[0] == 0
+    for t, n in enumerate(sizes):
+        ref = torch.cat([data[r][t] for r in range(world)])
+        for r in range(world):
+            assert torch.equal(gathered[r][t].cpu(), ref)
+    # a list that is too large for the staging arena is refused, not truncated
+    huge = [[torch.zeros(1 << 20, device="cuda")] * 4 for _ in range(world)]
+    assert not c.multi(0, huge, huge)

@@ -170,8 +170,17 @@ class _UnitFn(torch.autograd.Function):
 class FullyShardedSequential:
     """A chain of modules, each sharded as one unit: y = m_n(...m_1(x))."""
 
-    def __init__(self, modules, group=None, comm="ccl", param_dtype=torch.bfloat16):
+    def __init__(self, modules, group=None, comm="ccl", param_dtype=torch.bfloat16, comm_blocks=None):
+        """comm_blocks: CTA cap of the collective kernels of this group's communicator. The gathers and
+        reduce_scatters of this engine run NEXT TO the units' compute; with the default cap (256 CTAs of
+        512 threads) they take every SM away from the GEMMs they are supposed to hide behind. A cap of
+        32-64 leaves most of the GPU to the compute while the NVLink transfer still runs near full rate.
+        The setting applies to every collective of the group (all ranks must pass the same value)."""
         self.units = [ShardedUnit(m, group, comm, param_dtype) for m in modules]
+        if comm == "ccl" and comm_blocks:
+            from .. import get_backend
+
+            get_backend(group, "cuda").set_cuda_tuning(self.units[0].shard, {"max_blocks": int(comm_blocks)})
         self.comm_stream = torch.cuda.Stream()
         self.anchor = torch.zeros((), device=self.units[0].device, requires_grad=True)
         self.group = group
@@ -224,6 +233,7 @@ class FullyShardedSequential:
     def full_state_dict(self, dst=0):
         """Consolidated fp32 parameters {"<unit>.<name>": tensor} on rank `dst` (None elsewhere):
         one all_gather of the master shards per unit through torch.distributed."""
+        self.finish_backward()  # gradient reduce_scatters may still be running on the communication stream
         out = {} if self.units[0].rank == dst else None
         for i, u in enumerate(self.units):
             full = torch.empty(u.padded, device=u.device, dtype=torch.float32)
