@@ -226,6 +226,24 @@ def main():
 
     ms_e2e, clocks_e2e = measure(e2e_region, reset_model)
     e2e_res = summarize(ms_e2e)
+
+    if os.environ.get("CCL_BENCH_KERNEL_TABLE") and rank == 0:
+        # diagnostic only (never a bench value): per-kernel device time of a few graph replays, as seen by torch's profiler
+        from torch.profiler import ProfilerActivity, profile
+
+        reset_model()
+        torch.cuda.synchronize(dev)
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(3):
+                model.decode_step(B)
+            torch.cuda.synchronize(dev)
+        with open(os.environ["CCL_BENCH_KERNEL_TABLE"], "w") as f:
+            f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=30, max_name_column_width=90))
+    elif os.environ.get("CCL_BENCH_KERNEL_TABLE"):
+        reset_model()
+        for _ in range(3):
+            model.decode_step(B)
+        torch.cuda.synchronize(dev)
     kernels_per_step = model.kernels_per_step
     fused = model.fused
     del model
