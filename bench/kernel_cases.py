@@ -2,6 +2,11 @@
 launches, inputs larger than the 126 MB L2 but only a few hundred MB on the device).
 
     python bench/kernel_cases.py {gemm_decode|gemm_swiglu|gemm_large|attention|addnorm} [--iters N]
+    python bench/kernel_cases.py {tp8_qkv|tp8_gate_up|tp8_attention|tp8_fused_o|tp8_fused_down} [--iters N]
+
+The tp8_* cases are the kernels of one layer of the tensor-parallel decode step at the shapes ONE rank of
+eight sees (Llama-7B, batch 16, 1024-token context), on a one-rank communicator: what a rank computes when
+no time is spent waiting for peers.
 """
 import argparse
 import os
@@ -17,6 +22,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("case")
     ap.add_argument("--iters", type=int, default=6)
+    ap.add_argument("--splitk", type=int, default=0, help="tp8_* GEMM cases: split-K factor (0 = the library's choice)")
     a = ap.parse_args()
     dev = "cuda"
     bf = dict(device=dev, dtype=torch.bfloat16)
@@ -56,6 +62,42 @@ def main():
         w = torch.ones(4096, **bf)
         out = torch.empty(16, 4096, **bf)
         fn = lambda i: comm.allreduce_residual_rmsnorm([x], [res], [w], [out], 1e-5)
+    elif a.case in ("tp8_qkv", "tp8_gate_up", "tp8_fused_o", "tp8_fused_down"):
+        from torch_ccl_b200.ops import pack_weight
+
+        x16 = torch.randn(16, 4096, **bf)
+        if a.case == "tp8_qkv":  # 4 + 4 + 4 heads: 12.6 MB of weights
+            ws = [pack_weight(torch.randn(1536, 4096, **bf) * 0.02) for _ in range(12)]
+            out = torch.empty(16, 1536, **bf)
+            fn = lambda i: C.gemm_bf16_tn(ws[i % 12], x16, out, True, 0, a.splitk, 16, 1536)
+        elif a.case == "tp8_gate_up":  # 1376 + 1376 rows with the SwiGLU epilogue: 22.5 MB of weights
+            pad = (1376 + 127) // 128 * 128
+            ws = [torch.cat([pack_weight(torch.randn(1376, 4096, **bf) * 0.02), pack_weight(torch.randn(1376, 4096, **bf) * 0.02)]) for _ in range(8)]
+            out = torch.empty(16, 1376, **bf)
+            fn = lambda i: C.gemm_bf16_tn(ws[i % 8], x16, out, True, pad, a.splitk, 16, 1376)
+        else:  # row-parallel projection + (one-rank) all_reduce + residual + norm in one launch
+            K = 512 if a.case == "tp8_fused_o" else 1376
+            comm = C.CudaComm.create(None, 0, 1, 1 << 20, 1000, "ccl/case")
+            n = 40 if K == 512 else 16
+            ws = [pack_weight(torch.randn(4096, K, **bf) * 0.02) for _ in range(n)]
+            xk = torch.randn(16, K, **bf)
+            res = torch.randn(16, 4096, **bf)
+            wn = torch.ones(4096, **bf)
+            out = torch.empty(16, 4096, **bf)
+            fn = lambda i: comm.gemm_ar_norm([ws[i % n]], [xk], [res], [wn], [out], 1e-5, a.splitk)
+    elif a.case == "tp8_attention":  # 16 sequences x 4 heads over a 1024-token cache; caches cycled through > L2
+        B, nh, S = 16, 4, 1280
+        qkv = torch.randn(B, 3 * nh * 128, **bf)
+        caches = [(torch.randn(B, nh, S, 128, **bf), torch.randn(B, nh, S, 128, **bf)) for _ in range(5)]
+        pos = torch.full((B,), 1024, device=dev, dtype=torch.int32)
+        inv = 1.0 / (10000.0 ** (torch.arange(0, 128, 2, device=dev).float() / 128))
+        ang = torch.arange(S, device=dev).float()[:, None] * inv[None]
+        cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+        out = torch.empty(B, nh * 128, **bf)
+        ns = C.decode_attention_default_splits(B, nh, S)
+        scratch = torch.zeros(C.decode_attention_scratch_bytes(B, nh, ns) // 4 + 1, device=dev)
+        cnt = torch.zeros(B * nh, device=dev, dtype=torch.int32)
+        fn = lambda i: C.decode_attention(qkv, caches[i % 5][0], caches[i % 5][1], pos, cos, sin, out, scratch, cnt, nh, nh, ns)
     else:
         raise SystemExit("unknown case")
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -67,7 +109,7 @@ def main():
         fn(i)
     e.record()
     torch.cuda.synchronize()
-    print(f"{a.case}: {s.elapsed_time(e) / a.iters * 1e3:.2f} us per launch")
+    print(f"{a.case}{' splitk ' + str(a.splitk) if a.splitk else ''}: {s.elapsed_time(e) / a.iters * 1e3:.2f} us per launch")
 
 
 if __name__ == "__main__":

@@ -29,13 +29,23 @@ struct DeviceGuard {
 
 }  // namespace
 
+// Built-in algorithm thresholds, from bench/tune.py on B200 / NVSwitch (device-timed, max over ranks;
+// a CCL_TUNE_FILE measured on the machine at hand overrides them):
+//   2 ranks: one-shot 9-10 us up to 512 KB, 25 us at 4 MB, 188 us at 64 MB against two-shot 16-20 / 40 / 185 us:
+//            one-shot whenever the tensor fits its staging slot;
+//   8 ranks: one-shot 12.5 us at 32 KB, 18.7 us at 512 KB, 24.5 us at 1 MB, 46.7 us at 2 MB; two-shot 31-38 us up
+//            to 1 MB, 40 us at 2 MB, 50 us at 8 MB, 157 us at 32 MB; through the switch (staged, CCL_NVLS=1) 27 us
+//            at 1 MB, 28 us at 2 MB, 49 us at 8 MB, 114 us at 32 MB: one-shot up to 1 MB, then the switch (from
+//            2 MB) or two-shot.
 size_t default_oneshot_max(int world) {
-  // two ranks: both algorithms move the same bytes and one-shot has one phase less; it was never
-  // slower up to 16 MB (bench/tune.py), so it is used whenever the tensor fits the staging half
   if (world <= 2) return (size_t)1 << 40;
-  if (world <= 4) return 1u << 20;
-  return 512u << 10;
+  return 1u << 20;
 }
+
+// all_gather: push (every rank writes its piece into all peers' arenas) against pull. 2 ranks: push wins up to
+// 2 MB per piece (8 KB 7.8 vs 8.7 us, 1 MB 14.1 vs 16.6); 8 ranks: push wins or ties up to 2 MB per piece
+// (8 KB 14.0 vs 21.5 us, 256 KB 17.5 vs 25.9, 2 MB 42.0 vs 41.5).
+static size_t default_ag_push_max(int /*world*/) { return 2u << 20; }
 
 namespace {
 
@@ -69,7 +79,8 @@ CudaComm::CudaComm(int rank, int world, int device, const CommConfig& cfg, KvSto
   DeviceGuard g(device_);
   cfg_.half_bytes = round_up(cfg_.half_bytes, 1 << 20);
   if (cfg_.oneshot_max_bytes == 0) cfg_.oneshot_max_bytes = default_oneshot_max(world_);
-  if (cfg_.ag_push_max_bytes == 0) cfg_.ag_push_max_bytes = world_ <= 2 ? (2u << 20) : (256u << 10);
+  if (cfg_.ag_push_max_bytes == 0) cfg_.ag_push_max_bytes = default_ag_push_max(world_);
+  if (cfg_.symm_min_bytes == (size_t)-1) cfg_.symm_min_bytes = world_ <= 2 ? (16u << 20) : (512u << 10);
   arena_bytes_ = arena_size(cfg_.half_bytes);
   check(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped | cudaHostAllocPortable),
         "cudaHostAlloc(status)");
@@ -89,7 +100,8 @@ CudaComm::CudaComm(int world, int device, const CommConfig& cfg)
   DeviceGuard g(device_);
   cfg_.half_bytes = round_up(cfg_.half_bytes, 1 << 20);
   if (cfg_.oneshot_max_bytes == 0) cfg_.oneshot_max_bytes = default_oneshot_max(world_);
-  if (cfg_.ag_push_max_bytes == 0) cfg_.ag_push_max_bytes = 256u << 10;
+  if (cfg_.ag_push_max_bytes == 0) cfg_.ag_push_max_bytes = default_ag_push_max(world_);
+  if (cfg_.symm_min_bytes == (size_t)-1) cfg_.symm_min_bytes = world_ <= 2 ? (16u << 20) : (512u << 10);
   arena_bytes_ = arena_size(cfg_.half_bytes);
   for (int r = 0; r < world_; ++r) {
     void* base = nullptr;

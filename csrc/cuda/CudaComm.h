@@ -36,7 +36,7 @@ struct CommConfig {
   size_t half_bytes = 256ull << 20;   // one staging half per rank (arena = 2 halves + flags)
   uint64_t spin_timeout_ms = 30000;   // device-side wait budget
   size_t oneshot_max_bytes = 0;        // 0: pick from the world size (see default_oneshot_max)
-  size_t ag_push_max_bytes = 0;        // per-piece size up to which all_gather pushes (0: 2 MB for 2 ranks, else 256 KB)
+  size_t ag_push_max_bytes = 0;        // per-piece size up to which all_gather pushes (0: built-in, 2 MB)
   int max_blocks = 256;               // CTAs for bandwidth-bound collectives
   int threads = 512;
   Algo algo = Algo::kAuto;
@@ -45,16 +45,19 @@ struct CommConfig {
   // NVLS: bind the arenas to an NVLink multicast object (needs symm = kVmm and device support) and
   // route SUM all_reduces of bf16 / f16 / f32 of at least nvls_min_bytes through the switch.
   bool nvls = false;                  // CCL_NVLS
-  size_t nvls_min_bytes = 4u << 20;
+  size_t nvls_min_bytes = 2u << 20;    // measured at 8 ranks: the staged switch kernel wins from 2 MB (28 vs 40 us)
   // Symmetric heap: memory for user tensors that every rank maps (allocate through the backend's
   // allocateTensor / symm_empty). Collectives on such tensors run zero-copy: no staging through the
   // arena. Created at the first allocation; bound to a multicast object when `nvls` is set.
   size_t heap_bytes = 1ull << 30;     // CCL_SYMM_HEAP_MB
-  size_t symm_min_bytes = 256u << 10;  // smaller symmetric messages still take the (lower-latency) staged one-shot kernels
+  // smaller symmetric messages still take the staged one-shot kernel. Measured at 8 ranks: zero-copy 16.9 us
+  // against 18.7 us at 512 KB, 17.6 against 24.5 us at 1 MB, 36.6 against 48.4 us at 8 MB; below 512 KB a tie.
+  // (2 ranks: the staged one-shot kernel stays ahead up to 16 MB; a tuning file can raise the threshold there.)
+  size_t symm_min_bytes = (size_t)-1;  // -1: built-in (512 KB; 16 MB for two ranks)
 };
 
 // One-shot all_reduce moves (W-1)*S bytes into every GPU, two-shot 2*S*(W-1)/W: with two ranks
-// they move the same, with eight the crossover is a few hundred KB (measured on B200/NVSwitch).
+// they move the same, with eight the measured crossover is 1 MB (see CudaComm.cpp).
 size_t default_oneshot_max(int world);
 
 struct AlgoChoice {

@@ -80,7 +80,6 @@ __device__ __forceinline__ void rope16(float (&own)[16], const float (&partner)[
 
 __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const DecodeAttnParams p) {
   ptx::griddep_launch_dependents();
-  ptx::griddep_wait();  // q/k/v of the new token come from the projection kernel just before
   const int split = blockIdx.x;
   const int h = blockIdx.y;
   const int b = blockIdx.z;
@@ -89,6 +88,25 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const Decode
   const int g = tid >> 3;  // position group within the CTA
   const int j = tid & 7;   // dim slice within the head
   const int kvh = h / (p.n_heads / p.n_kv_heads);
+  if (tid == 0 && p.prefetch_l2) {
+    // While the projection kernel before this one is still running, pull this CTA's range of the
+    // cache towards L2. The cached positions were written by earlier steps; the position read here
+    // may be one step old (the kernel that advances it is not known to have finished yet), which
+    // moves the range by one row at most - it is only a hint, everything is read again below.
+    const int pp = *reinterpret_cast<const volatile int*>(p.positions + b);
+    if (pp >= 0 && pp < p.max_seq) {
+      const int tot = pp + 1;
+      const int pr = (tot + nsplit - 1) / nsplit;
+      const int a0 = split * pr, a1 = min(tot, a0 + pr);
+      if (a1 > a0) {
+        const size_t base = (((size_t)b * p.n_kv_heads + kvh) * p.max_seq + a0) * kHD;
+        const uint32_t bytes = (uint32_t)(a1 - a0) * kRowBytes;
+        ptx::bulk_prefetch_l2(p.k_cache + base, bytes);
+        ptx::bulk_prefetch_l2(p.v_cache + base, bytes);
+      }
+    }
+  }
+  ptx::griddep_wait();  // q/k/v of the new token come from the projection kernel just before
   const int pos = p.positions[b];  // the new token's position; attends over [0, pos]
   if (pos < 0 || pos >= p.max_seq) {
     // a position outside the cache would index the cache and the rotary tables out of bounds:
@@ -292,7 +310,7 @@ int decode_attention_default_splits(int batch, int n_heads, int max_context) {
   // rejected for 512 pairs, where the SMs get 3 or 4 equal CTAs: an uneven two-way split, 7/8 heads
   // dispatched before 1/8 tails, was no faster than no split - 52.1 vs 51.6 us.)
   int s = (4 * 148) / pairs;
-  const int cap = (max_context + 255) / 256;  // at least 256 positions per split
+  const int cap = (max_context + 127) / 128;  // at least 128 positions (four pipeline chunks) per split
   if (s > cap) s = cap;
   if (s < 1) s = 1;
   if (s > 32) s = 32;
@@ -329,7 +347,12 @@ cudaError_t decode_attention(const DecodeAttnParams& p, int batch, int nsplit, c
   cudaLaunchAttribute attr[1];
   cfg.attrs = attr;
   cfg.numAttrs = pdl_launch_attr(&attr[0]);
-  return cudaLaunchKernelEx(&cfg, decode_attention_kernel, p);
+  // Early L2 prefetch only when the K/V of the whole launch is well below the 126 MB L2 (a tensor-parallel
+  // shard): for a full-size cache (268 MB at batch 16 x 32 heads) the hint would only evict itself and was
+  // measured to cost 20 % of the step.
+  DecodeAttnParams q = p;
+  q.prefetch_l2 = pdl_enabled() && (size_t)batch * p.n_kv_heads * p.max_seq * kRowBytes * 2 <= (48u << 20);
+  return cudaLaunchKernelEx(&cfg, decode_attention_kernel, q);
 }
 
 }  // namespace ccl

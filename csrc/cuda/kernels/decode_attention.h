@@ -21,6 +21,8 @@ struct DecodeAttnParams {
   int n_heads, n_kv_heads, head_dim, max_seq;
   float scale;               // 1/sqrt(head_dim)
   int* status = nullptr;     // optional device error word (set if a bounded wait expires)
+  int prefetch_l2 = 0;       // set by decode_attention(): the launch's whole K/V fits L2 comfortably, so every CTA
+                             // pulls its range towards L2 while the kernel before it is still running
 };
 
 size_t decode_attention_scratch_bytes(int batch, int n_heads, int nsplit);

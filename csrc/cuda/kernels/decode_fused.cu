@@ -308,6 +308,7 @@ cudaError_t launch_ar_norm_bn(const RankCtx* ctx, const RankCtx* dev_ctx_table, 
   p.status = ctx[0].status;
   p.a_tiled = 1;
   p.a_static = 1;
+  p.a_packed = a0.w;
   p.k_tiles = k_iters;
   ArNormShape sh{a0.rows, a0.hidden, a0.eps};
 

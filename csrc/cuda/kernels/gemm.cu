@@ -113,11 +113,15 @@ cudaError_t launch(const GemmDesc& d, int splitk, cudaStream_t stream) {
     // the kernel keeps nothing in L1: give shared memory the whole array so that two CTAs fit
     e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
+    // split-K over 16 CTAs is one step beyond the portable cluster size
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return e;
     configured.done();
   }
-  // split-K: bounded by the portable cluster size and by the amount of K work per CTA
-  if (splitk > 8) splitk = 8;
+  // split-K: bounded by the largest cluster and by the amount of K work per CTA
+  if (splitk > 16) splitk = 16;
   while (splitk > 1 && k_iters / splitk < 2) --splitk;
+  if (splitk > 8 && splitk < 16) splitk = 8;   // between the portable limit and 16: stay portable
   if (splitk < 1) splitk = 1;
   const int stages = stages_for<BN, DUAL>((int64_t)m_tiles * n_tiles * splitk, k_iters, splitk);
   const size_t smem = smem_bytes<BN, DUAL>(stages, splitk);
@@ -148,6 +152,7 @@ cudaError_t launch(const GemmDesc& d, int splitk, cudaStream_t stream) {
   p.acquire_a = 0;
   p.a_tiled = d.a_tiled;
   p.a_static = d.a_tiled;  // packed operands are weights: nothing on the stream produces them
+  p.a_packed = d.a_tiled ? d.a : nullptr;
   p.k_tiles = k_iters;
 
   cudaLaunchConfig_t cfg = {};
@@ -208,8 +213,11 @@ cudaError_t gemm_bf16_tn(const GemmDesc& d, cudaStream_t stream) {
       // (e.g. 96 tiles x 3 = 288 CTAs) no longer fits one wave and costs 40 %. At least 4 K-steps
       // stay in every CTA.
       splitk = (int)(264 / tiles);
-      if (splitk > 8) splitk = 8;
-      while (splitk > 1 && k_iters / splitk < 4) --splitk;
+      // few tiles (a tensor-parallel shard of a projection): clusters of 16 keep more SMs streaming weights
+      // (measured at the shapes one rank of eight sees, batch 16: qkv 12 tiles 7.5 -> 6.9 us with 16; the SwiGLU
+      // pair, whose CTAs stream two weight tiles per step, 10.9 -> 11.0 us, so it stays at 8)
+      if (splitk > 8) splitk = (splitk >= 16 && d.dual_off == 0) ? 16 : 8;
+      while (splitk > 1 && k_iters / splitk < 4) splitk = splitk == 16 ? 8 : splitk - 1;
       if (splitk < 1) splitk = 1;
     } else if (bn <= 64 && tiles < 148) {
       splitk = (int)(148 / tiles);

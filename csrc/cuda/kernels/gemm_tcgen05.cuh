@@ -53,6 +53,8 @@ struct Params {
                         //    predecessor kernel on the stream has finished (programmatic dependent launch)
   int acquire_a;        // 1: A was written by another GPU and observed through a flag; order the
                         //    TMA (async proxy) reads after that acquire with a proxy fence
+  const void* a_packed; // base of the packed A (a_tiled only; may be null): lets the producer pull the tiles
+                        //    that do not fit the shared-memory ring towards L2 ahead of the dependency wait
 };
 
 // Where a CTA's tile lives: `a_row` is the TMA row coordinate of the A tile (it differs from the
@@ -229,6 +231,17 @@ __device__ __forceinline__ void gemm_tile_body(const CUtensorMap* tma_a, const C
         // the predecessor kernel is still running, then wait for it and fetch the B tiles.
         const int pre = n_iters < stages ? n_iters : stages;
         for (int i = 0; i < pre; ++i) load_a(i);
+        if (p.a_tiled && p.a_packed != nullptr) {
+          // the rest of this CTA's weight tiles: a hint towards L2 while the predecessor still runs
+          const char* base = static_cast<const char*>(p.a_packed);
+          // (at most four tiles ahead: a CTA with a long K range would otherwise push its neighbours' tiles out of L2)
+          const int ahead = n_iters < pre + 4 ? n_iters : pre + 4;
+          for (int i = pre; i < ahead; ++i) {
+            const size_t kt = (size_t)(it_begin + i);
+            ptx::bulk_prefetch_l2(base + ((size_t)(tc.a_row / kBM) * p.k_tiles + kt) * kABytes, kABytes);
+            if (DUAL) ptx::bulk_prefetch_l2(base + ((size_t)((tc.a_row + p.dual_off) / kBM) * p.k_tiles + kt) * kABytes, kABytes);
+          }
+        }
         ptx::griddep_wait();
         for (int i = 0; i < pre; ++i) load_b(i);
         i0 = pre;

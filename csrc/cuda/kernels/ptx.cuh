@@ -232,6 +232,12 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
                "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
+// Hint: bring [gmem, gmem + bytes) into L2 (address 16-byte aligned, size a multiple of 16). No
+// completion to wait for and no effect on correctness: it may run before the data's final value is
+// known to be needed (or even before a stale index has been re-read), the real loads come later.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gmem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void tma_store_2d(const void* tmap, const void* smem_src, int32_t x,
                                              int32_t y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(

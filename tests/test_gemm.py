@@ -38,7 +38,7 @@ def test_gemm_plain(M, N, K, bn, out_dtype):
 
 
 @pytest.mark.parametrize("batch", [1, 4, 16])
-@pytest.mark.parametrize("splitk", [1, 2, 4, 8, 0])
+@pytest.mark.parametrize("splitk", [1, 2, 4, 8, 16, 0])
 def test_gemm_swap_ab_splitk(batch, splitk):
     """Decode shape: weights on the UMMA M side, the few activation rows on the N side."""
     torch.manual_seed(1)
@@ -51,7 +51,7 @@ def test_gemm_swap_ab_splitk(batch, splitk):
     _check(out, _ref(x, w), K)
 
 
-@pytest.mark.parametrize("splitk", [1, 2, 4])
+@pytest.mark.parametrize("splitk", [1, 2, 4, 16])
 def test_gemm_dual_swiglu(splitk):
     torch.manual_seed(2)
     inter, K, batch = 1376, 4096, 16
@@ -81,7 +81,7 @@ def test_gemm_persistent(M, N, K, bn, out_dtype):
 
 
 @pytest.mark.parametrize("rows,K,batch", [(1536, 4096, 16), (1000, 1376, 5), (4096, 512, 16), (4096, 1376, 130)])
-@pytest.mark.parametrize("splitk", [0, 1, 3])
+@pytest.mark.parametrize("splitk", [0, 1, 3, 16])
 def test_gemm_pretiled_weights(rows, K, batch, splitk):
     """Weights packed as contiguous 128x64 tiles (ops.pack_weight), rows / K padded with zeros."""
     from torch_ccl_b200.ops import pack_weight, unpack_weight

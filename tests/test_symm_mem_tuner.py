@@ -215,4 +215,4 @@ def _symmetric_tensors(rank, world):
 @pytest.mark.parametrize("nvls", ["0", "1"])
 def test_symmetric_tensors_zero_copy(nvls):
     run_ranks(_symmetric_tensors, world=min(torch.cuda.device_count(), 8), device="cuda",
-              env={"CCL_NVLS": nvls, "CCL_ARENA_MB": "64", "CCL_SYMM_HEAP_MB": "64", "NCCL_NVLS_ENABLE": "0"})
+              env={"CCL_NVLS": nvls, "CCL_ARENA_MB": "64", "CCL_SYMM_HEAP_MB": "64", "CCL_SYMM_MIN_BYTES": "0", "NCCL_NVLS_ENABLE": "0"})
