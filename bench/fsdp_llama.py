@@ -112,6 +112,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--arms", default="ccl,nccl")
+    ap.add_argument("--symmetric", action="store_true", help="ccl arm: parameter / gradient buffers from the symmetric heap (zero-copy collectives)")
     ap.add_argument("--comm-blocks", type=int, default=0, help="CTA cap of the ccl collectives while they overlap compute (0: library default)")
     a = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -128,7 +129,8 @@ def main():
         mods = build(a, dev)
         if arm in ("ccl", "nccl"):
             engine = FullyShardedSequential(mods, group=None if arm == "ccl" else nccl_group, comm="ccl" if arm == "ccl" else "c10d",
-                                            comm_blocks=a.comm_blocks or None)
+                                            comm_blocks=(a.comm_blocks or None) if arm == "ccl" else None,
+                                            symmetric=a.symmetric and arm == "ccl")
             opt = torch.optim.AdamW(engine.master_params(), lr=1e-4, fused=True)
 
             def step():
@@ -192,6 +194,7 @@ def main():
                "micro_batch": 1, "dtype": "bf16 params/compute, fp32 reduce + master"}
         out.update(results)
         out["comm_blocks"] = a.comm_blocks
+        out["symmetric"] = a.symmetric
         if "ccl" in results and "nccl" in results:
             out["speedup_vs_nccl"] = round(results["nccl"]["ms_per_step"] / results["ccl"]["ms_per_step"], 3)
         if "ccl" in results and "fsdp2" in results:

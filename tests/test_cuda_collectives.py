@@ -273,8 +273,10 @@ def _fsdp_engine(rank, world):
         return [nn.Sequential(nn.Linear(64, 96), nn.GELU()).cuda(), nn.Linear(96, 64).cuda(), nn.Linear(64, 8).cuda()]
 
     losses = {}
-    for comm in ("c10d", "ccl"):
-        eng = FullyShardedSequential(make(), comm=comm)
+    for comm in ("c10d", "ccl_symmetric", "ccl"):
+        # "ccl_symmetric": parameter / gradient buffers from the symmetric heap, zero-copy collectives
+        eng = FullyShardedSequential(make(), comm="ccl" if comm.startswith("ccl") else comm, symmetric=comm == "ccl_symmetric",
+                                     comm_blocks=16 if comm == "ccl_symmetric" else None)
         opt = torch.optim.SGD(eng.master_params(), lr=0.02)
         out = []
         for it in range(3):
@@ -286,8 +288,9 @@ def _fsdp_engine(rank, world):
             eng.after_step()
             out.append(float(loss))
         losses[comm] = out
-    for a, b in zip(losses["ccl"], losses["c10d"]):
-        assert abs(a - b) <= 2e-2 * max(1.0, abs(b)), (losses)
+    for arm in ("ccl", "ccl_symmetric"):
+        for a, b in zip(losses[arm], losses["c10d"]):
+            assert abs(a - b) <= 2e-2 * max(1.0, abs(b)), (losses)
     assert losses["ccl"][-1] < losses["ccl"][0]
     # sharded checkpoint: save, perturb, reload -> the same loss; consolidated copy on rank 0
     import io
@@ -316,7 +319,8 @@ def _fsdp_engine(rank, world):
 
 
 def test_cuda_fsdp_engine_and_moe_ops():
-    run_ranks(_fsdp_engine, world=_world(), device="cuda", env={"NCCL_NVLS_ENABLE": "0", "CCL_ARENA_MB": "64", "CCL_SPIN_TIMEOUT_MS": "3000"}, timeout=120)
+    run_ranks(_fsdp_engine, world=_world(), device="cuda", env={"NCCL_NVLS_ENABLE": "0", "CCL_ARENA_MB": "64", "CCL_SPIN_TIMEOUT_MS": "3000",
+                                                                   "CCL_SYMM_HEAP_MB": "64", "CCL_SYMM_MIN_BYTES": "0"}, timeout=180)
 
 
 def _tp_decode(rank, world):

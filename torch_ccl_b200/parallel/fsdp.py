@@ -28,6 +28,20 @@ import torch.distributed as dist
 from .. import ops
 
 
+class _SymmPool:
+    """Two symmetric buffers (memory of the group's symmetric heap, mapped by every rank) used in
+    turn by consecutive units, so that the collectives on them run zero-copy: the all_gather writes
+    straight into every rank's parameter buffer and the reduce_scatter reads the peers' gradient
+    buffers in place (through the NVSwitch reduction when the heap is bound to a multicast object).
+    `free[slot]` is the event after which the slot may be overwritten."""
+
+    def __init__(self, numel, dtype, group, slots=2):
+        from .. import symm_empty
+
+        self.bufs = [symm_empty(numel, dtype, group=group) for _ in range(slots)]
+        self.free = [None] * slots
+
+
 class ShardedUnit:
     def __init__(self, module, group=None, comm="ccl", param_dtype=torch.bfloat16):
         self.module = module
@@ -62,6 +76,8 @@ class ShardedUnit:
         self.full = None
         self.gfull = None
         self.ready = None  # event: gathered parameters are complete
+        self.ppool = self.gpool = None  # symmetric buffer pools of the engine (optional)
+        self.slot = 0
 
     # -- parameters ---------------------------------------------------------------------------
     def gather(self, stream):
@@ -71,14 +87,20 @@ class ShardedUnit:
         cur = torch.cuda.current_stream(self.device)
         s = stream
         with torch.cuda.stream(s):
-            full = torch.empty(self.padded, device=self.device, dtype=self.dtype)
+            if self.ppool is not None:
+                if self.ppool.free[self.slot] is not None:
+                    s.wait_event(self.ppool.free[self.slot])  # the unit that used this slot before has finished computing
+                full = self.ppool.bufs[self.slot][: self.padded]
+            else:
+                full = torch.empty(self.padded, device=self.device, dtype=self.dtype)
             if self.comm == "ccl":
                 ops.all_gather_copy_out(self.shard, list(full.chunk(self.world)), group=self.group)
             else:
                 dist.all_gather_into_tensor(full, self.shard, group=self.group)
             self.ready = torch.cuda.Event()
             self.ready.record(s)
-        full.record_stream(cur)
+        if self.ppool is None:
+            full.record_stream(cur)
         self.full = full
         for p, (o, n, shape) in zip(self.params, self.meta):
             p.data = full[o:o + n].view(shape)
@@ -88,6 +110,10 @@ class ShardedUnit:
             torch.cuda.current_stream(self.device).wait_event(self.ready)
 
     def release(self):
+        if self.ppool is not None and self.full is not None:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self.ppool.free[self.slot] = ev
         self.full = None
         self.ready = None
         for p in self.params:
@@ -95,7 +121,13 @@ class ShardedUnit:
 
     # -- gradients ----------------------------------------------------------------------------
     def prepare_grads(self):
-        self.gfull = torch.zeros(self.padded, device=self.device, dtype=self.dtype)
+        if self.gpool is not None:
+            if self.gpool.free[self.slot] is not None:
+                torch.cuda.current_stream(self.device).wait_event(self.gpool.free[self.slot])  # its last reduce_scatter is done
+            self.gfull = self.gpool.bufs[self.slot][: self.padded]
+            self.gfull.zero_()
+        else:
+            self.gfull = torch.zeros(self.padded, device=self.device, dtype=self.dtype)
         for p, (o, n, shape) in zip(self.params, self.meta):
             p.grad = self.gfull[o:o + n].view(shape)
 
@@ -118,7 +150,12 @@ class ShardedUnit:
                 tmp = torch.empty(self.shard_numel, device=self.device, dtype=self.dtype)
                 dist.reduce_scatter_tensor(tmp, gfull, group=self.group)
                 self.grad_shard += tmp.float() / self.world
-        gfull.record_stream(stream)
+            if self.gpool is not None:
+                ev = torch.cuda.Event()
+                ev.record(stream)
+                self.gpool.free[self.slot] = ev
+        if self.gpool is None:
+            gfull.record_stream(stream)
         for p in self.params:
             p.grad = None
         self.gfull = None
@@ -170,13 +207,22 @@ class _UnitFn(torch.autograd.Function):
 class FullyShardedSequential:
     """A chain of modules, each sharded as one unit: y = m_n(...m_1(x))."""
 
-    def __init__(self, modules, group=None, comm="ccl", param_dtype=torch.bfloat16, comm_blocks=None):
+    def __init__(self, modules, group=None, comm="ccl", param_dtype=torch.bfloat16, comm_blocks=None, symmetric=False):
         """comm_blocks: CTA cap of the collective kernels of this group's communicator. The gathers and
         reduce_scatters of this engine run NEXT TO the units' compute; with the default cap (256 CTAs of
         512 threads) they take every SM away from the GEMMs they are supposed to hide behind. A cap of
         32-64 leaves most of the GPU to the compute while the NVLink transfer still runs near full rate.
-        The setting applies to every collective of the group (all ranks must pass the same value)."""
+        The setting applies to every collective of the group (all ranks must pass the same value).
+        symmetric: keep the gathered parameters and the flat gradients in two pairs of buffers from the
+        group's symmetric heap (CCL_SYMM_HEAP_MB must hold four buffers of the largest unit), so that both
+        collectives run zero-copy over NVLink instead of staging through the arena."""
         self.units = [ShardedUnit(m, group, comm, param_dtype) for m in modules]
+        if comm == "ccl" and symmetric and self.units[0].world > 1:
+            biggest = max(u.padded for u in self.units)
+            ppool = _SymmPool(biggest, param_dtype, group)
+            gpool = _SymmPool(biggest, param_dtype, group)
+            for i, u in enumerate(self.units):
+                u.ppool, u.gpool, u.slot = ppool, gpool, i % 2
         if comm == "ccl" and comm_blocks:
             from .. import get_backend
 
