@@ -4,6 +4,12 @@ launches, inputs larger than the 126 MB L2 but only a few hundred MB on the devi
     python bench/kernel_cases.py {gemm_decode|gemm_swiglu|gemm_large|attention|addnorm} [--iters N]
     python bench/kernel_cases.py {tp8_qkv|tp8_gate_up|tp8_attention|tp8_fused_o|tp8_fused_down} [--iters N]
 
+    python bench/kernel_cases.py {emu_oneshot|emu_twoshot|emu_reduce_scatter|emu_all_to_all|emu_symm_allreduce} [--iters N]
+
+The emu_* cases run one collective kernel for EIGHT ranks on one GPU (one cooperative launch with gridDim.y = 8, every
+rank's arena on this device): the only form in which a profiler can look at a collective kernel, since kernels of
+different ranks wait on one another. Traffic that crosses NVLink in a real run shows up as L2 / DRAM traffic here.
+
 The tp8_* cases are the kernels of one layer of the tensor-parallel decode step at the shapes ONE rank of
 eight sees (Llama-7B, batch 16, 1024-token context), on a one-rank communicator: what a rank computes when
 no time is spent waiting for peers.
@@ -85,6 +91,32 @@ def main():
             wn = torch.ones(4096, **bf)
             out = torch.empty(16, 4096, **bf)
             fn = lambda i: comm.gemm_ar_norm([ws[i % n]], [xk], [res], [wn], [out], 1e-5, a.splitk)
+    elif a.case.startswith("emu_"):
+        W = 8
+        comm = C.CudaComm.emulated(W, 64 << 20, 2000, 16)
+        nbytes = (64 << 10) if a.case == "emu_oneshot" else (8 << 20)
+        n = nbytes // 2
+        if a.case in ("emu_oneshot", "emu_twoshot"):
+            comm.set_oneshot_max_bytes((1 << 30) if a.case == "emu_oneshot" else 1)
+            xs = [torch.randn(n, **bf) for _ in range(W)]
+            outs = [torch.empty(n, **bf) for _ in range(W)]
+            fn = lambda i: comm.allreduce(xs, outs)
+        elif a.case == "emu_symm_allreduce":
+            comm.set_symm_min_bytes(0)
+            xs = [t.view(torch.bfloat16) for t in comm.symm_empty(nbytes)]
+            for t in xs:
+                t.normal_()
+            fn = lambda i: comm.allreduce(xs, xs)
+        elif a.case == "emu_reduce_scatter":
+            ins = [list(torch.randn(n, **bf).chunk(W)) for _ in range(W)]
+            outs = [torch.empty(n // W, **bf) for _ in range(W)]
+            fn = lambda i: comm.reduce_scatter(ins, outs)
+        elif a.case == "emu_all_to_all":
+            ins = [list(torch.randn(n, **bf).chunk(W)) for _ in range(W)]
+            outs = [list(torch.empty(n, **bf).chunk(W)) for _ in range(W)]
+            fn = lambda i: comm.all_to_all(ins, outs)
+        else:
+            raise SystemExit("unknown case")
     elif a.case == "tp8_attention":  # 16 sequences x 4 heads over a 1024-token cache; caches cycled through > L2
         B, nh, S = 16, 4, 1280
         qkv = torch.randn(B, 3 * nh * 128, **bf)

@@ -1166,6 +1166,12 @@ c10::intrusive_ptr<Work> ProcessGroupCCL::alltoall_base(at::Tensor& outputTensor
   ccl::check_split_sizes(outputSplitSizes, outputTensor, size_);
   RECORD_FUNCTION("oneccl_bindings_for_pytorch::alltoall_base", std::vector<c10::IValue>({inputTensor}));
   CCL_OP_PROLOGUE("alltoall_base", inputTensor, "", tensors_str(inputTensor), (uint64_t)inputTensor.numel() * inputTensor.element_size())
+  // On CUDA the form of the call selects the device protocol: without split lists the fixed-size exchange, with
+  // them the one that first agrees on sizes. The choice is made from this rank's arguments alone, so either every
+  // rank of the group passes split lists or none does; CCL_DEBUG_CHECKS=1 compares the form across ranks and
+  // names the rank that differs instead of letting the mismatch end in a device-side timeout.
+  if (on_cuda && Env::get().debug_checks)
+    debugConsistencyCheck(uneven ? "alltoall_base[with split lists]" : "alltoall_base[without split lists]", inputTensor.scalar_type(), 0);
   if (on_cuda && !uneven) {
     at::Tensor in = inputTensor, ot2 = outputTensor;
     return cudaImpl(in.device()).run(OpType::ALLTOALL_BASE, "oneccl_bindings_for_pytorch::cuda::alltoall_base", in.device(),
