@@ -275,7 +275,8 @@ struct PyComm {
     cu(comm->all_to_all(args, uneven, stream()), "all_to_all");
   }
 
-  void broadcast(std::vector<at::Tensor> bufs, int root) {
+  void broadcast(std::vector<at::Tensor> bufs, int root, bool nvls) {
+    ForceNvls force(comm.get(), nvls);
     check_n(bufs.size());
     std::vector<CollArgs> args(bufs.size());
     for (size_t i = 0; i < bufs.size(); ++i) {
@@ -582,7 +583,7 @@ void bind_cuda_comm(py::module& m) {
       .def("all_gather", &PyComm::all_gather, py::arg("ins"), py::arg("outs"), py::arg("nvls") = false)
       .def_property_readonly("last_used_nvls", [](PyComm& c) { return c.comm->last_used_nvls(); })
       .def("all_to_all", &PyComm::all_to_all, py::arg("ins"), py::arg("outs"), py::arg("uneven") = false)
-      .def("broadcast", &PyComm::broadcast)
+      .def("broadcast", &PyComm::broadcast, py::arg("bufs"), py::arg("root"), py::arg("nvls") = false)
       .def("gather", &PyComm::gather)
       .def("scatter", &PyComm::scatter)
       .def("barrier", &PyComm::barrier)

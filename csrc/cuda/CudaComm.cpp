@@ -456,7 +456,18 @@ cudaError_t CudaComm::rooted(std::vector<CollArgs> args, cudaStream_t stream) {
   CCL_CHECK_ARGS(args)
   DeviceGuard g(device_);
   enter_stream(stream);
-  const int mode = args[0].mode;
+  int mode = args[0].mode;
+  if (mode == kBroadcast && world_ > 1 && cfg_.ablate == kAblateNone) {
+    // Large broadcasts leave the root once and are replicated by the switch.
+    const bool nvls_ok = emulated_ ? true : nvls_available();
+    const bool use_nvls = nvls_ok && (cfg_.algo == Algo::kNvls || (!emulated_ && cfg_.nvls && cfg_.algo == Algo::kAuto &&
+                                                                    (size_t)args[0].count >= cfg_.nvls_min_bytes));
+    last_algo_ = use_nvls ? Algo::kNvls : Algo::kTwoShot;
+    if (use_nvls) {
+      mode = kBroadcastSwitch;
+      for (auto& a : args) a.mode = kBroadcastSwitch;
+    }
+  }
   size_t stride = (mode == kGather) ? cfg_.half_bytes / (16 * (size_t)world_) : cfg_.half_bytes / 16;
   stride = stride / 8 * 8;
   const size_t maxv = ((size_t)args[0].count + 15) / 16;

@@ -201,29 +201,41 @@ __device__ __forceinline__ Vec<T> finish_vec(const typename Acc<T>::type (&acc)[
   return r;
 }
 
-// acc = v[0] (op) v[1] (op) ... in rank order. The SUM case, by far the most common, avoids the
-// per-element dispatch on the reduce kind.
+// acc = v(0) (op) v(1) (op) ... in rank order, where `load(p)` returns rank p's vector. The loads
+// go out in groups of kReduceBatch ranks (all loads of a group are issued before the first is
+// used): 8 vectors in flight at once cost 32 registers and made the 512-thread kernels spill.
+// The SUM case, by far the most common, avoids the per-element dispatch on the reduce kind.
+// The one-shot kernel, whose whole point is latency, keeps all ranks in flight for the types that
+// fit (one round trip to L2 instead of two).
+constexpr int kReduceBatch = 4;
 template <typename T>
-__device__ __forceinline__ void reduce_ranks(const Vec<T> (&v)[kMaxRanks], int W, int op,
-                                             typename Acc<T>::type (&acc)[Vec<T>::kN]) {
+constexpr int kOneshotBatch = (sizeof(T) >= 4 || std::is_same<T, __nv_bfloat16>::value || std::is_same<T, __half>::value) ? kMaxRanks : kReduceBatch;
+template <typename T, int BATCH = kReduceBatch, typename F>
+__device__ __forceinline__ void reduce_ranks(int W, int op, typename Acc<T>::type (&acc)[Vec<T>::kN], F load) {
   using A = typename Acc<T>::type;
   constexpr int N = Vec<T>::kN;
+  static_assert(kMaxRanks % BATCH == 0, "the batch must divide the rank limit");
 #pragma unroll
-  for (int t = 0; t < N; ++t) acc[t] = to_acc(v[0].v[t]);
-  if (op == kSum) {
+  for (int b0 = 0; b0 < kMaxRanks; b0 += BATCH) {
+    if (b0 < W) {
+      Vec<T> v[BATCH];
 #pragma unroll
-    for (int p = 1; p < kMaxRanks; ++p) {
-      if (p < W) {
+      for (int q = 0; q < BATCH; ++q)
+        if (b0 + q < W) v[q] = load(b0 + q);
 #pragma unroll
-        for (int t = 0; t < N; ++t) acc[t] = acc[t] + to_acc(v[p].v[t]);
-      }
-    }
-  } else {
+      for (int q = 0; q < BATCH; ++q) {
+        if (b0 + q < W) {
+          if (b0 + q == 0) {
 #pragma unroll
-    for (int p = 1; p < kMaxRanks; ++p) {
-      if (p < W) {
+            for (int t = 0; t < N; ++t) acc[t] = to_acc(v[q].v[t]);
+          } else if (op == kSum) {
 #pragma unroll
-        for (int t = 0; t < N; ++t) acc[t] = Combine<A>::apply(op, acc[t], to_acc(v[p].v[t]));
+            for (int t = 0; t < N; ++t) acc[t] = acc[t] + to_acc(v[q].v[t]);
+          } else {
+#pragma unroll
+            for (int t = 0; t < N; ++t) acc[t] = Combine<A>::apply(op, acc[t], to_acc(v[q].v[t]));
+          }
+        }
       }
     }
   }
@@ -269,13 +281,10 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const __grid_con
   if (do_work && ok) {
     const char* mine = sy.half(me, 0);
     for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
-      Vec<T> v[kMaxRanks];
-#pragma unroll
-      for (int p = 0; p < kMaxRanks; ++p) {
-        if (p < W) v[p] = (p == me) ? load_vec(in, j, count, al_in) : load_stage<T>(mine + (size_t)p * slot + j * 16);
-      }
       A acc[N];
-      reduce_ranks<T>(v, W, a.op, acc);
+      reduce_ranks<T, kOneshotBatch<T>>(W, a.op, acc, [&](int p) {
+        return (p == me) ? load_vec(in, j, count, al_in) : load_stage<T>(mine + (size_t)p * slot + j * 16);
+      });
       store_vec(out, j, count, al_out, finish_vec<T>(acc, a));
     }
   }
@@ -330,13 +339,10 @@ __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(const __grid_con
       const Range r = sub_slice(mylen);
       const size_t vb = base + (size_t)me * spr;
       for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
-        Vec<T> v[kMaxRanks];
-#pragma unroll
-        for (int p = 0; p < kMaxRanks; ++p) {
-          if (p < W) v[p] = (p == me) ? load_vec(in, vb + j, count, al_in) : load_stage<T>(regionA + ((size_t)p * stride_v + j) * 16);
-        }
         A acc[N];
-        reduce_ranks<T>(v, W, a.op, acc);
+        reduce_ranks<T>(W, a.op, acc, [&](int p) {
+          return (p == me) ? load_vec(in, vb + j, count, al_in) : load_stage<T>(regionA + ((size_t)p * stride_v + j) * 16);
+        });
         const Vec<T> res = finish_vec<T>(acc, a);
         store_stage(regionB + j * 16, res);
         if (gather_here) store_vec(out, vb + j, count, al_out, res);
@@ -614,13 +620,10 @@ __global__ void __launch_bounds__(512) reduce_scatter_kernel(const __grid_consta
       const Range r = sub_slice(clamp_len(nv, vb, stride_v));
       const char* regionA = sy.half(me, rd);
       for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
-        Vec<TIn> v[kMaxRanks];
-#pragma unroll
-        for (int p = 0; p < kMaxRanks; ++p) {
-          if (p < W) v[p] = (p == me) ? load_vec(mypiece, vb + j, mycount, al_mine) : load_stage<TIn>(regionA + ((size_t)p * stride_v + j) * 16);
-        }
         A acc[N];
-        reduce_ranks<TIn>(v, W, a.op, acc);
+        reduce_ranks<TIn>(W, a.op, acc, [&](int p) {
+          return (p == me) ? load_vec(mypiece, vb + j, mycount, al_mine) : load_stage<TIn>(regionA + ((size_t)p * stride_v + j) * 16);
+        });
         const size_t e0 = (vb + j) * N;
         if constexpr (sizeof(TOut) == sizeof(TIn)) {
           store_vec(reinterpret_cast<TIn*>(out), vb + j, mycount, al_out, finish_vec<TIn>(acc, a));
@@ -809,6 +812,28 @@ __global__ void __launch_bounds__(512) rooted_kernel(const __grid_constant__ Lau
         sy.signal_one(root, 1, rd);
         if (ok) ok = sy.wait_one(root, 2, rd);
       }
+    } else if (a.mode == kBroadcastSwitch) {
+      // The root stores each vector ONCE into the multicast address: the switch replicates it into
+      // every rank's arena (S bytes leave the root instead of (W-1) * S). All ranks exchange flags
+      // with all ranks, like the unrooted kernels, so no release step is needed.
+      T* buf = reinterpret_cast<T*>(a.out);
+      if (me == root && do_work) {
+        const size_t off0 = (size_t)sy.parity(rd) * ctx.half_bytes;
+        const bool al = is_aligned16(buf);
+        for (size_t j = r.j0 + threadIdx.x; j < r.j1; j += blockDim.x) {
+          const Vec<T> v = load_vec(const_cast<const T*>(buf), vb + j, bytes, al);
+          if constexpr (EMU) {
+#pragma unroll
+            for (int p = 0; p < kMaxRanks; ++p)
+              if (p < W) store_stage(ctx.data[p] + off0 + j * 16, v);
+          } else {
+            ptx::multimem_st_v4(ctx.mc_data + off0 + j * 16, *reinterpret_cast<const uint4*>(&v));
+          }
+        }
+      }
+      sy.signal_all(0, rd);
+      ok = sy.wait_all(0, rd);
+      if (ok && me != root && do_work) copy_stage_to_user(sy.half(me, rd), buf, bytes, vb, r);
     } else if (a.mode == kGather) {
       const T* in = reinterpret_cast<const T*>(a.in);
       if (me == root) {

@@ -24,7 +24,7 @@ __host__ __device__ inline int dtype_size(int dt) {
   }
 }
 
-enum RootedMode : int { kBroadcast = 0, kGather = 1, kScatter = 2 };
+enum RootedMode : int { kBroadcast = 0, kGather = 1, kScatter = 2, kBroadcastSwitch = 3 /* root writes all arenas with multimem.st */ };
 
 // Arguments of one rank. Piece tables are indexed by peer rank.
 struct CollArgs {

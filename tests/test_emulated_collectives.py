@@ -497,6 +497,35 @@ def test_reduce_scatter_switch_reduction_emulated(comms, world, dtype):
         assert not c.last_used_nvls
 
 
+@pytest.mark.parametrize("world,root", [(2, 1), (3, 0), (8, 5)])
+def test_broadcast_switch_multicast_emulated(comms, world, root):
+    """Broadcast whose root stores every vector once into the multicast address (played in software here), mixed with
+    the peer-store broadcast and an all_reduce so that the arena halves and epochs of consecutive kernels interleave."""
+    c = comms(world, 1 << 20)
+    n = 700001  # 2.8 MB of float32 through 1 MB halves: three rounds, ragged tail
+    xs = [rand(n, torch.float32, 40 + r) for r in range(world)]
+    bufs = [x.cuda() for x in xs]
+    c.broadcast(bufs, root, True)
+    torch.cuda.synchronize()
+    assert c.last_used_nvls and c.status()[0] == 0
+    for b in bufs:
+        assert torch.equal(b.cpu(), xs[root])
+    ys = [rand(1000, torch.float32, 90 + r).cuda() for r in range(world)]
+    other = (root + 1) % world
+    bytes8 = [rand(4099, torch.float32, 60 + r).view(torch.uint8)[:16385].clone() for r in range(world)]  # odd byte count
+    b8 = [t.cuda() for t in bytes8]
+    for _ in range(2):
+        c.allreduce(ys, ys, SUM, 1.0, 0, 0)
+        c.broadcast(b8, other, True)
+        c.broadcast(bufs, other, False)
+    torch.cuda.synchronize()
+    assert c.status()[0] == 0
+    for b in b8:
+        assert torch.equal(b.cpu(), bytes8[other])
+    for b in bufs:
+        assert torch.equal(b.cpu(), xs[root])  # every buffer already held the root's data
+
+
 @pytest.mark.parametrize("world", [2, 3, 8])
 def test_all_gather_switch_multicast_emulated(comms, world):
     c = comms(world, 1 << 20)

@@ -49,10 +49,13 @@ def _fused_ok(x, weight, group, rows_total):
     if dist.get_backend(group) != "ccl":
         return False
     w = _world(group)
-    # the kernels stage one full operand / result in the communicator's arena half (256 MB by default)
+    if not (rows_total % (128 * w) == 0 and weight.shape[1] % 8 == 0 and weight.shape[0] % 16 == 0 and x.dim() == 2):
+        return False
+    # the kernels stage one full operand / result in one half of the communicator's arena (CCL_ARENA_MB sets its size)
+    from .. import get_backend
+
     staged = rows_total * max(weight.shape[0], weight.shape[1]) * 2
-    return (rows_total % (128 * w) == 0 and weight.shape[1] % 8 == 0 and weight.shape[0] % 16 == 0 and x.dim() == 2
-            and staged <= (128 << 20))
+    return staged <= get_backend(group, "cuda").fused_gemm_capacity_bytes(x)
 
 
 class _GatherMatmul(torch.autograd.Function):
