@@ -170,7 +170,7 @@ void cu(cudaError_t e, const char* what) {
 }
 
 struct PyComm {
-  std::unique_ptr<CudaComm> comm;
+  std::shared_ptr<CudaComm> comm;   // shared with the deleters of symmetric tensors, which may outlive this object
 
   cudaStream_t stream() const { return c10::cuda::getCurrentCUDAStream(comm->device()).stream(); }
   void check_n(size_t n) const {
@@ -451,11 +451,11 @@ struct PyComm {
     const size_t off = static_cast<char*>(p0) - static_cast<char*>(comm->heap_base(0));
     std::vector<at::Tensor> out;
     auto opts = at::TensorOptions().dtype(at::kByte).device(at::kCUDA, comm->device());
-    CudaComm* c = comm.get();
+    std::shared_ptr<CudaComm> c = comm;
     for (int i = 0; i < comm->nctx(); ++i) {
       void* pi = static_cast<char*>(comm->heap_base(i)) + off;
       if (i == 0) out.push_back(at::from_blob(pi, {nbytes}, [c, p0](void*) { c->symm_free(p0); }, opts));
-      else out.push_back(at::from_blob(pi, {nbytes}, opts));
+      else out.push_back(at::from_blob(pi, {nbytes}, [c](void*) {}, opts));
     }
     return out;
   }

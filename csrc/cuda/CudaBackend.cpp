@@ -319,6 +319,7 @@ CudaComm& CudaBackendImpl::comm(const at::Device& device) {
     if (env.symm_heap_mb > 0) cfg.heap_bytes = (size_t)env.symm_heap_mb << 20;
     if (env.symm_min_bytes >= 0) cfg.symm_min_bytes = (size_t)env.symm_min_bytes;
     if (env.nvls_min_bytes >= 0) cfg.nvls_min_bytes = (size_t)env.nvls_min_bytes;
+    if (env.round_mb >= 0) cfg.round_bytes = (size_t)env.round_mb << 20;
     cfg.symm = parse_symm_kind(env.symm_mem);
     if (env.nvls || env.algo == "nvls") {
       // the multicast object binds driver virtual-memory allocations only

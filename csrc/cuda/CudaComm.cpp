@@ -81,6 +81,12 @@ CudaComm::CudaComm(int rank, int world, int device, const CommConfig& cfg, KvSto
   if (cfg_.oneshot_max_bytes == 0) cfg_.oneshot_max_bytes = default_oneshot_max(world_);
   if (cfg_.ag_push_max_bytes == 0) cfg_.ag_push_max_bytes = default_ag_push_max(world_);
   if (cfg_.symm_min_bytes == (size_t)-1) cfg_.symm_min_bytes = world_ <= 2 ? (16u << 20) : (512u << 10);
+  // Two ranks (measured, 512 MB bf16): the staged switch kernels LOSE to the peer-memory kernels (all_reduce 1736 vs
+  // 1320 us, reduce_scatter 1045 vs 786, all_gather 893 vs 510: the switch saves no NVLink bytes when there is one
+  // peer), so they are never the automatic choice; staging rounds of 128 MB instead of the arena half gain 5-9 %
+  // (all_reduce 1320 -> 1202 us, reduce_scatter 786 -> 731, all_to_all 680 -> 643; 64 MB and 32 MB rounds are slower).
+  if (cfg_.nvls_min_bytes == (size_t)-1) cfg_.nvls_min_bytes = world_ <= 2 ? ((size_t)1 << 62) : (2u << 20);
+  if (cfg_.round_bytes == (size_t)-1) cfg_.round_bytes = world_ <= 2 ? (128u << 20) : 0;
   arena_bytes_ = arena_size(cfg_.half_bytes);
   check(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped | cudaHostAllocPortable),
         "cudaHostAlloc(status)");
@@ -102,6 +108,12 @@ CudaComm::CudaComm(int world, int device, const CommConfig& cfg)
   if (cfg_.oneshot_max_bytes == 0) cfg_.oneshot_max_bytes = default_oneshot_max(world_);
   if (cfg_.ag_push_max_bytes == 0) cfg_.ag_push_max_bytes = default_ag_push_max(world_);
   if (cfg_.symm_min_bytes == (size_t)-1) cfg_.symm_min_bytes = world_ <= 2 ? (16u << 20) : (512u << 10);
+  // Two ranks (measured, 512 MB bf16): the staged switch kernels LOSE to the peer-memory kernels (all_reduce 1736 vs
+  // 1320 us, reduce_scatter 1045 vs 786, all_gather 893 vs 510: the switch saves no NVLink bytes when there is one
+  // peer), so they are never the automatic choice; staging rounds of 128 MB instead of the arena half gain 5-9 %
+  // (all_reduce 1320 -> 1202 us, reduce_scatter 786 -> 731, all_to_all 680 -> 643; 64 MB and 32 MB rounds are slower).
+  if (cfg_.nvls_min_bytes == (size_t)-1) cfg_.nvls_min_bytes = world_ <= 2 ? ((size_t)1 << 62) : (2u << 20);
+  if (cfg_.round_bytes == (size_t)-1) cfg_.round_bytes = world_ <= 2 ? (128u << 20) : 0;
   arena_bytes_ = arena_size(cfg_.half_bytes);
   for (int r = 0; r < world_; ++r) {
     void* base = nullptr;
@@ -242,6 +254,17 @@ static size_t compact_stride(size_t capacity_stride, size_t needed_vecs) {
   return want < capacity_stride ? want : capacity_stride;
 }
 
+// Optional cap on a staging round (CCL_ROUND_MB): `slots` slots of `stride` vectors make one round.
+// Smaller rounds keep what one phase stages in L2 for the next phase and let the CTAs of a kernel
+// drift into different phases (local copies overlap NVLink transfers); every extra round costs
+// its flag exchanges (about 10 us each at 2 GPUs).
+static size_t cap_stride(size_t stride, size_t slots, size_t round_bytes) {
+  if (round_bytes == 0) return stride;
+  size_t cap = round_bytes / 16 / std::max<size_t>(slots, 1) / 8 * 8;
+  if (cap < 8) cap = 8;
+  return std::min(stride, cap);
+}
+
 #define CCL_CHECK_ARGS(v)                                                             \
   if ((int)(v).size() != nctx()) return cudaErrorInvalidValue;
 
@@ -291,14 +314,14 @@ cudaError_t CudaComm::allreduce(int dtype, std::vector<CollArgs> args, cudaStrea
     lc = launch_cfg(blocks_for(nvec, cfg_.max_blocks), threads_for(nvec, blocks_for(nvec, cfg_.max_blocks), cfg_.threads), stream);
     e = launch_allreduce_oneshot(dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
   } else if (algo == Algo::kNvls) {
-    size_t stride = cfg_.half_bytes / (16 * (size_t)world_);
+    size_t stride = cap_stride(cfg_.half_bytes / (16 * (size_t)world_), world_, cfg_.round_bytes);
     stride = compact_stride(stride / 8 * 8, (nvec + world_ - 1) / world_);
     for (auto& a : args) a.chunk_vecs = stride;
     const size_t per_shard = (nvec + world_ - 1) / world_;
     lc = launch_cfg(blocks_for(per_shard, cfg_.max_blocks), threads_for(per_shard, blocks_for(per_shard, cfg_.max_blocks), cfg_.threads), stream);
     e = launch_allreduce_nvls(dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
   } else {
-    size_t stride = cfg_.half_bytes / (16 * (size_t)(world_ + 1));
+    size_t stride = cap_stride(cfg_.half_bytes / (16 * (size_t)(world_ + 1)), world_, cfg_.round_bytes);
     stride = compact_stride(stride / 8 * 8, (nvec + world_ - 1) / world_);
     for (auto& a : args) a.chunk_vecs = stride;
     lc = launch_cfg(blocks_for((nvec + world_ - 1) / world_, cfg_.max_blocks), threads_for((nvec + world_ - 1) / world_, blocks_for((nvec + world_ - 1) / world_, cfg_.max_blocks), cfg_.threads), stream);
@@ -350,7 +373,7 @@ cudaError_t CudaComm::reduce_scatter(int in_dtype, int out_dtype, std::vector<Co
     if (symm) return reduce_scatter_symm(in_dtype, out_dtype, in_off, outs, cnt, args[0].op, args[0].scale, args[0].has_scale, true, stream);
   }
   const size_t per_vec = 16 / esz;
-  size_t stride = cfg_.half_bytes / (16 * (size_t)world_);
+  size_t stride = cap_stride(cfg_.half_bytes / (16 * (size_t)world_), world_, cfg_.round_bytes);
   stride = stride / 8 * 8;
   size_t maxv = 0;
   for (auto& a : args)
@@ -411,6 +434,11 @@ cudaError_t CudaComm::all_gather(std::vector<CollArgs> args, cudaStream_t stream
   last_algo_ = use_nvls ? Algo::kNvls : Algo::kTwoShot;
   const int mode = (use_nvls || maxb <= cfg_.ag_push_max_bytes) ? 1 : 0;  // NVLS uses the push layout: one slot per source
   size_t stride = mode == 1 ? cfg_.half_bytes / (16 * (size_t)world_) : cfg_.half_bytes / 16;
+  // Pull mode stages the own piece locally and lets the peers read it: rounds of at most 32 MB keep the staged
+  // round in L2 for the readers and let the CTAs drift apart, so that one CTA's staging overlaps another's reads
+  // (2 GPUs, 2 x 256 MB: 653 us with 256 MB rounds, 530 us with 64 MB, 553 us with 16 MB; NCCL 627 us).
+  if (mode == 0) stride = cap_stride(stride, 1, cfg_.round_bytes ? cfg_.round_bytes : (size_t)(32u << 20));
+  else stride = cap_stride(stride, world_, cfg_.round_bytes);
   stride = compact_stride(stride / 8 * 8, maxv);
   const int rounds = (int)((maxv + stride - 1) / stride);
   for (auto& a : args) {
@@ -430,7 +458,7 @@ cudaError_t CudaComm::all_to_all(std::vector<CollArgs> args, bool uneven, cudaSt
   CCL_CHECK_ARGS(args)
   DeviceGuard g(device_);
   enter_stream(stream);
-  size_t stride = cfg_.half_bytes / (16 * (size_t)world_);
+  size_t stride = cap_stride(cfg_.half_bytes / (16 * (size_t)world_), world_, uneven ? 0 : cfg_.round_bytes);
   stride = stride / 8 * 8;
   size_t maxb = 0;
   for (auto& a : args)

@@ -45,7 +45,7 @@ struct CommConfig {
   // NVLS: bind the arenas to an NVLink multicast object (needs symm = kVmm and device support) and
   // route SUM all_reduces of bf16 / f16 / f32 of at least nvls_min_bytes through the switch.
   bool nvls = false;                  // CCL_NVLS
-  size_t nvls_min_bytes = 2u << 20;    // measured at 8 ranks: the staged switch kernel wins from 2 MB (28 vs 40 us)
+  size_t nvls_min_bytes = (size_t)-1;  // -1: built-in (2 MB, measured at 8 ranks: the staged switch kernel wins from there, 28 vs 40 us; never for two ranks)
   // Symmetric heap: memory for user tensors that every rank maps (allocate through the backend's
   // allocateTensor / symm_empty). Collectives on such tensors run zero-copy: no staging through the
   // arena. Created at the first allocation; bound to a multicast object when `nvls` is set.
@@ -53,6 +53,7 @@ struct CommConfig {
   // smaller symmetric messages still take the staged one-shot kernel. Measured at 8 ranks: zero-copy 16.9 us
   // against 18.7 us at 512 KB, 17.6 against 24.5 us at 1 MB, 36.6 against 48.4 us at 8 MB; below 512 KB a tie.
   // (2 ranks: the staged one-shot kernel stays ahead up to 16 MB; a tuning file can raise the threshold there.)
+  size_t round_bytes = (size_t)-1;     // cap on the bytes one staging round moves per rank (0: the arena half; -1: built-in, 128 MB for two ranks); see cap_stride
   size_t symm_min_bytes = (size_t)-1;  // -1: built-in (512 KB; 16 MB for two ranks)
 };
 

@@ -113,6 +113,15 @@ def _nvls(rank, world):
         gathered = torch.empty(n * world, device="cuda", dtype=torch.bfloat16)
         dist.all_gather_into_tensor(gathered, part)
         assert torch.equal(gathered, want)
+        # broadcast above the switch-over: the root stores once into the multicast address (several rounds through
+        # the 64 MB arena halves for the first tensor; an odd byte count for the second)
+        root = world - 1
+        big = torch.full((40 << 20,), rank + 1, device="cuda", dtype=torch.int32)
+        dist.broadcast(big, src=root)
+        assert int(big.min()) == root + 1 and int(big.max()) == root + 1
+        odd = ((torch.arange((3 << 20) + 5, device="cuda") % 251) + (7 if rank == 0 else rank * 31)).to(torch.uint8)
+        dist.broadcast(odd, src=0)
+        assert torch.equal(odd, ((torch.arange((3 << 20) + 5, device="cuda") % 251) + 7).to(torch.uint8))
         t = torch.full((4 << 20,), float(rank + 1), device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.AVG)
         assert torch.allclose(t, torch.full_like(t, (world + 1) / 2))
@@ -138,7 +147,9 @@ def _nvls(rank, world):
 def test_switch_reduction_all_reduce():
     """CCL_NVLS=1: large SUM all_reduces go through the NVLink multicast object (multimem.ld_reduce
     + multimem.st); exact integer-valued inputs, so the result is compared bit for bit."""
-    run_ranks(_nvls, world=min(torch.cuda.device_count(), 8), device="cuda", env={"CCL_NVLS": "1", "CCL_ARENA_MB": "64"})
+    # two ranks never pick the switch kernels by themselves (they lose there): the threshold is given explicitly
+    run_ranks(_nvls, world=min(torch.cuda.device_count(), 8), device="cuda",
+              env={"CCL_NVLS": "1", "CCL_ARENA_MB": "64", "CCL_NVLS_MIN_BYTES": str(2 << 20)})
 
 
 @pytest.mark.gpu
