@@ -190,16 +190,49 @@ void Watchdog::loop() {
     l.unlock();
     try {
       // works complete in stream order, so waiting on the oldest one first is enough
-      // a coarse poll: waiters use the event directly, the watchdog only retires work
-      while (!it.end->query()) std::this_thread::sleep_for(std::chrono::microseconds(200));
-      std::string m = it.comm ? status_message(*it.comm) : std::string();
+      // a coarse poll: waiters use the event directly, the watchdog only retires work.
+      // Deadline: every device wait of the library is bounded (spin budget <= the group's timeout), so a work
+      // normally ends or fails by itself. The deadline is the backstop for a spin budget configured longer than
+      // the timeout: kGrace after the timeout the watchdog raises the communicator's abort word (every bounded
+      // wait samples it and returns within about a millisecond, status "aborted"); if the event has not fired
+      // kGiveUp later either, the work is failed without it and its tensors are leaked rather than freed under
+      // a kernel that may still run.
+      constexpr auto kGrace = std::chrono::seconds(2), kGiveUp = std::chrono::seconds(10);
+      const auto t0 = std::chrono::steady_clock::now();
+      bool raised = false, gave_up = false;
+      while (!it.end->query()) {
+        if (it.timeout.count() > 0) {
+          const auto waited = std::chrono::steady_clock::now() - t0;
+          if (!raised && waited > it.timeout + kGrace) {
+            raised = true;
+            std::cerr << "[ccl] watchdog: work " << it.seq << " is past its timeout of " << it.timeout.count()
+                      << " ms; aborting the communicator\n" << Telemetry::get().dump_flight();
+            if (it.comm) it.comm->abort();
+          }
+          if (raised && waited > it.timeout + kGrace + kGiveUp) {
+            gave_up = true;
+            break;
+          }
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(200));
+      }
       Telemetry::get().record_complete(it.work->flight_slot, it.seq);
-      if (m.empty()) {
-        it.work->finishOk();
+      if (gave_up) {
+        static std::vector<std::vector<at::Tensor>>* leaked = new std::vector<std::vector<at::Tensor>>();
+        leaked->push_back(std::move(it.keep));
+        it.work->finishError(std::make_exception_ptr(c10::DistBackendError(
+            c10::SourceLocation{"ccl", __FILE__, __LINE__},
+            "ccl: watchdog gave up on work " + std::to_string(it.seq) + " after its timeout of " +
+                std::to_string(it.timeout.count()) + " ms (the kernel did not end after the abort)")));
       } else {
-        std::cerr << "[ccl] " << m << "\n" << Telemetry::get().dump_flight();
-        it.work->finishError(std::make_exception_ptr(
-            c10::DistBackendError(c10::SourceLocation{"ccl", __FILE__, __LINE__}, m)));
+        std::string m = it.comm ? status_message(*it.comm) : std::string();
+        if (m.empty()) {
+          it.work->finishOk();
+        } else {
+          std::cerr << "[ccl] " << m << "\n" << Telemetry::get().dump_flight();
+          it.work->finishError(std::make_exception_ptr(
+              c10::DistBackendError(c10::SourceLocation{"ccl", __FILE__, __LINE__}, m)));
+        }
       }
     } catch (...) {
       it.work->finishError(std::current_exception());
@@ -442,6 +475,7 @@ c10::intrusive_ptr<c10d::Work> CudaBackendImpl::run(c10d::OpType type, const cha
   item.comm = comm_;
   item.keep = keep;  // keeps the tensors alive until the kernels have run (instead of record_stream)
   item.seq = seq;
+  item.timeout = pg_->timeout();
   Watchdog::get().enqueue(std::move(item));
   return work;
 }
@@ -518,6 +552,7 @@ c10::intrusive_ptr<c10d::Work> CudaBackendImpl::p2p(bool is_send, at::Tensor& te
   item.end = w->end_;
   item.keep = {tensor};
   item.seq = seq;
+  item.timeout = pg_->timeout();
   Watchdog::get().enqueue(std::move(item));
   return w;
 }
@@ -547,6 +582,7 @@ c10::intrusive_ptr<c10d::Work> CudaBackendImpl::p2p_group_end() {
   item.keep = std::move(p2p_batch_tensors_);
   p2p_batch_tensors_.clear();
   item.seq = seq;
+  item.timeout = pg_->timeout();
   Watchdog::get().enqueue(std::move(item));
   return w;
 }

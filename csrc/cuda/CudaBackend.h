@@ -89,6 +89,7 @@ class Watchdog {
     std::shared_ptr<CudaComm> comm;
     std::vector<at::Tensor> keep;
     uint64_t seq;
+    std::chrono::milliseconds timeout{0};  // the group's timeout; 0 = no deadline (see Watchdog::loop)
   };
   void enqueue(Item item);
   void drain();  // blocks until every queued work has completed

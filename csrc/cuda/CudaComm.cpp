@@ -71,6 +71,23 @@ void fill_ctx(RankCtx& c, int rank, int world, const std::vector<void*>& bases, 
 
 }  // namespace
 
+// Built-in thresholds for the knobs left at "-1", from `bench/tune.py` and `bench/sweep.py` on B200 + NVSwitch:
+//  * zero-copy path for symmetric tensors: from 512 KB at 8 ranks (16.9 vs 18.7 us), 2 MB at 4 ranks (18.2 vs 25.8 us;
+//    below it the staged one-shot kernel is 1-3 us faster), 16 MB at 2 ranks (nothing to save with one peer);
+//  * staged switch (NVLS) kernels: from 2 MB at 8 ranks (28 vs 40 us), 8 MB at 4 ranks (44.5 vs 58 us; two-shot wins at
+//    4 MB, 30 vs 34 us), never at 2 ranks (512 MB: all_reduce 1736 vs 1320 us, reduce_scatter 1045 vs 786, all_gather
+//    893 vs 510 - with one peer the switch saves no NVLink bytes);
+//  * staging rounds: 128 MB for the peer-memory kernels (512 MB bf16 at 2 / 4 ranks: all_reduce 1320 -> 1202 / 1635 ->
+//    1532 us, reduce_scatter 786 -> 731 / 927 -> 879, all_to_all 680 -> 643 / 819 -> 798; 64 MB and 32 MB are slower),
+//    64 MB for the switch kernels (4 ranks: all_reduce 1522 -> 1417 us, reduce_scatter 904 -> 844 against 128 MB rounds).
+void CudaComm::apply_builtin_thresholds() {
+  if (cfg_.symm_min_bytes == (size_t)-1) cfg_.symm_min_bytes = world_ <= 2 ? (16u << 20) : world_ <= 4 ? (2u << 20) : (512u << 10);
+  if (cfg_.nvls_min_bytes == (size_t)-1) cfg_.nvls_min_bytes = world_ <= 2 ? ((size_t)1 << 62) : world_ <= 4 ? (8u << 20) : (2u << 20);
+  if (cfg_.nvls_round_bytes == (size_t)-1) cfg_.nvls_round_bytes = cfg_.round_bytes != (size_t)-1 ? cfg_.round_bytes : (64u << 20);
+  if (cfg_.ag_pull_round_bytes == (size_t)-1) cfg_.ag_pull_round_bytes = cfg_.round_bytes != (size_t)-1 ? cfg_.round_bytes : (32u << 20);
+  if (cfg_.round_bytes == (size_t)-1) cfg_.round_bytes = 128u << 20;
+}
+
 CudaComm::CudaComm(int rank, int world, int device, const CommConfig& cfg, KvStore kv,
                    const std::string& prefix)
     : rank_(rank), world_(world), device_(device), emulated_(false), cfg_(cfg), kv_(std::move(kv)),
@@ -80,13 +97,7 @@ CudaComm::CudaComm(int rank, int world, int device, const CommConfig& cfg, KvSto
   cfg_.half_bytes = round_up(cfg_.half_bytes, 1 << 20);
   if (cfg_.oneshot_max_bytes == 0) cfg_.oneshot_max_bytes = default_oneshot_max(world_);
   if (cfg_.ag_push_max_bytes == 0) cfg_.ag_push_max_bytes = default_ag_push_max(world_);
-  if (cfg_.symm_min_bytes == (size_t)-1) cfg_.symm_min_bytes = world_ <= 2 ? (16u << 20) : (512u << 10);
-  // Two ranks (measured, 512 MB bf16): the staged switch kernels LOSE to the peer-memory kernels (all_reduce 1736 vs
-  // 1320 us, reduce_scatter 1045 vs 786, all_gather 893 vs 510: the switch saves no NVLink bytes when there is one
-  // peer), so they are never the automatic choice; staging rounds of 128 MB instead of the arena half gain 5-9 %
-  // (all_reduce 1320 -> 1202 us, reduce_scatter 786 -> 731, all_to_all 680 -> 643; 64 MB and 32 MB rounds are slower).
-  if (cfg_.nvls_min_bytes == (size_t)-1) cfg_.nvls_min_bytes = world_ <= 2 ? ((size_t)1 << 62) : (2u << 20);
-  if (cfg_.round_bytes == (size_t)-1) cfg_.round_bytes = world_ <= 2 ? (128u << 20) : 0;
+  apply_builtin_thresholds();
   arena_bytes_ = arena_size(cfg_.half_bytes);
   check(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped | cudaHostAllocPortable),
         "cudaHostAlloc(status)");
@@ -107,13 +118,7 @@ CudaComm::CudaComm(int world, int device, const CommConfig& cfg)
   cfg_.half_bytes = round_up(cfg_.half_bytes, 1 << 20);
   if (cfg_.oneshot_max_bytes == 0) cfg_.oneshot_max_bytes = default_oneshot_max(world_);
   if (cfg_.ag_push_max_bytes == 0) cfg_.ag_push_max_bytes = default_ag_push_max(world_);
-  if (cfg_.symm_min_bytes == (size_t)-1) cfg_.symm_min_bytes = world_ <= 2 ? (16u << 20) : (512u << 10);
-  // Two ranks (measured, 512 MB bf16): the staged switch kernels LOSE to the peer-memory kernels (all_reduce 1736 vs
-  // 1320 us, reduce_scatter 1045 vs 786, all_gather 893 vs 510: the switch saves no NVLink bytes when there is one
-  // peer), so they are never the automatic choice; staging rounds of 128 MB instead of the arena half gain 5-9 %
-  // (all_reduce 1320 -> 1202 us, reduce_scatter 786 -> 731, all_to_all 680 -> 643; 64 MB and 32 MB rounds are slower).
-  if (cfg_.nvls_min_bytes == (size_t)-1) cfg_.nvls_min_bytes = world_ <= 2 ? ((size_t)1 << 62) : (2u << 20);
-  if (cfg_.round_bytes == (size_t)-1) cfg_.round_bytes = world_ <= 2 ? (128u << 20) : 0;
+  apply_builtin_thresholds();
   arena_bytes_ = arena_size(cfg_.half_bytes);
   for (int r = 0; r < world_; ++r) {
     void* base = nullptr;
@@ -314,7 +319,7 @@ cudaError_t CudaComm::allreduce(int dtype, std::vector<CollArgs> args, cudaStrea
     lc = launch_cfg(blocks_for(nvec, cfg_.max_blocks), threads_for(nvec, blocks_for(nvec, cfg_.max_blocks), cfg_.threads), stream);
     e = launch_allreduce_oneshot(dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
   } else if (algo == Algo::kNvls) {
-    size_t stride = cap_stride(cfg_.half_bytes / (16 * (size_t)world_), world_, cfg_.round_bytes);
+    size_t stride = cap_stride(cfg_.half_bytes / (16 * (size_t)world_), world_, cfg_.nvls_round_bytes);
     stride = compact_stride(stride / 8 * 8, (nvec + world_ - 1) / world_);
     for (auto& a : args) a.chunk_vecs = stride;
     const size_t per_shard = (nvec + world_ - 1) / world_;
@@ -373,12 +378,17 @@ cudaError_t CudaComm::reduce_scatter(int in_dtype, int out_dtype, std::vector<Co
     if (symm) return reduce_scatter_symm(in_dtype, out_dtype, in_off, outs, cnt, args[0].op, args[0].scale, args[0].has_scale, true, stream);
   }
   const size_t per_vec = 16 / esz;
-  size_t stride = cap_stride(cfg_.half_bytes / (16 * (size_t)world_), world_, cfg_.round_bytes);
-  stride = stride / 8 * 8;
   size_t maxv = 0;
   for (auto& a : args)
     for (int p = 0; p < world_; ++p) maxv = std::max(maxv, ((size_t)a.in_cnt[p] + per_vec - 1) / per_vec);
-  stride = compact_stride(stride, maxv);
+  // in-switch reduction: SUM of bf16 / f16 / f32 into the same dtype (the switch returns the sum rounded to the
+  // input type, so the widened bf16 -> fp32 gradient path stays on the peer-load kernel, which keeps fp32)
+  const bool nvls_ok = (emulated_ ? world_ > 1 : nvls_available()) && args[0].op == kSum && in_dtype == out_dtype &&
+                       (in_dtype == kBF16 || in_dtype == kF16 || in_dtype == kF32);
+  const bool use_nvls = nvls_ok && (cfg_.algo == Algo::kNvls || (!emulated_ && cfg_.nvls && cfg_.algo == Algo::kAuto &&
+                                                                  maxv * 16 * world_ >= cfg_.nvls_min_bytes));
+  size_t stride = cap_stride(cfg_.half_bytes / (16 * (size_t)world_), world_, use_nvls ? cfg_.nvls_round_bytes : cfg_.round_bytes);
+  stride = compact_stride(stride / 8 * 8, maxv);
   const int rounds = (int)((maxv + stride - 1) / stride);
   for (auto& a : args) {
     a.chunk_vecs = stride;
@@ -386,12 +396,6 @@ cudaError_t CudaComm::reduce_scatter(int in_dtype, int out_dtype, std::vector<Co
     a.ablate = cfg_.ablate;
   }
   LaunchCfg lc = launch_cfg(blocks_for(std::min(maxv, stride), cfg_.max_blocks), threads_for(std::min(maxv, stride), blocks_for(std::min(maxv, stride), cfg_.max_blocks), cfg_.threads), stream);
-  // in-switch reduction: SUM of bf16 / f16 / f32 into the same dtype (the switch returns the sum rounded to the
-  // input type, so the widened bf16 -> fp32 gradient path stays on the peer-load kernel, which keeps fp32)
-  const bool nvls_ok = (emulated_ ? world_ > 1 : nvls_available()) && args[0].op == kSum && in_dtype == out_dtype &&
-                       (in_dtype == kBF16 || in_dtype == kF16 || in_dtype == kF32);
-  const bool use_nvls = nvls_ok && (cfg_.algo == Algo::kNvls || (!emulated_ && cfg_.nvls && cfg_.algo == Algo::kAuto &&
-                                                                  maxv * 16 * world_ >= cfg_.nvls_min_bytes));
   last_algo_ = use_nvls ? Algo::kNvls : Algo::kTwoShot;
   if (use_nvls) {
     cudaError_t en = launch_reduce_scatter_nvls(in_dtype, emulated_ ? dev_ctx_table_ : host_ctx_.data(), upload(args, stream), lc);
@@ -429,16 +433,19 @@ cudaError_t CudaComm::all_gather(std::vector<CollArgs> args, cudaStream_t stream
     for (int p = 0; p < world_; ++p) maxb = std::max(maxb, (size_t)a.out_cnt[p]);
   const size_t maxv = (maxb + 15) / 16;
   const bool nvls_ok = emulated_ ? world_ > 1 : nvls_available();
+  // The switch variant (one multimem.st per vector, then a local copy-out of everything) wins in the middle range; for
+  // large outputs the pull mode, whose reads land straight in the user tensor, is faster (4 ranks, 512 MB: 671 vs 878 us).
   const bool use_nvls = nvls_ok && (cfg_.algo == Algo::kNvls || (!emulated_ && cfg_.nvls && cfg_.algo == Algo::kAuto &&
-                                                                  maxb * world_ >= cfg_.nvls_min_bytes));
+                                                                  maxb * world_ >= cfg_.nvls_min_bytes &&
+                                                                  maxb * world_ < cfg_.ag_nvls_max_bytes));
   last_algo_ = use_nvls ? Algo::kNvls : Algo::kTwoShot;
   const int mode = (use_nvls || maxb <= cfg_.ag_push_max_bytes) ? 1 : 0;  // NVLS uses the push layout: one slot per source
   size_t stride = mode == 1 ? cfg_.half_bytes / (16 * (size_t)world_) : cfg_.half_bytes / 16;
   // Pull mode stages the own piece locally and lets the peers read it: rounds of at most 32 MB keep the staged
   // round in L2 for the readers and let the CTAs drift apart, so that one CTA's staging overlaps another's reads
   // (2 GPUs, 2 x 256 MB: 653 us with 256 MB rounds, 530 us with 64 MB, 553 us with 16 MB; NCCL 627 us).
-  if (mode == 0) stride = cap_stride(stride, 1, cfg_.round_bytes ? cfg_.round_bytes : (size_t)(32u << 20));
-  else stride = cap_stride(stride, world_, cfg_.round_bytes);
+  if (mode == 0) stride = cap_stride(stride, 1, cfg_.ag_pull_round_bytes);
+  else stride = cap_stride(stride, world_, use_nvls ? cfg_.nvls_round_bytes : cfg_.round_bytes);
   stride = compact_stride(stride / 8 * 8, maxv);
   const int rounds = (int)((maxv + stride - 1) / stride);
   for (auto& a : args) {

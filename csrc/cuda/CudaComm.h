@@ -53,7 +53,12 @@ struct CommConfig {
   // smaller symmetric messages still take the staged one-shot kernel. Measured at 8 ranks: zero-copy 16.9 us
   // against 18.7 us at 512 KB, 17.6 against 24.5 us at 1 MB, 36.6 against 48.4 us at 8 MB; below 512 KB a tie.
   // (2 ranks: the staged one-shot kernel stays ahead up to 16 MB; a tuning file can raise the threshold there.)
-  size_t round_bytes = (size_t)-1;     // cap on the bytes one staging round moves per rank (0: the arena half; -1: built-in, 128 MB for two ranks); see cap_stride
+  // Caps on the bytes one staging round moves per rank (0: the arena half; -1: built-in, see apply_builtin_thresholds).
+  // Setting round_bytes (CCL_ROUND_MB) also sets the two special cases that are left at -1.
+  size_t round_bytes = (size_t)-1;          // peer-memory kernels (built-in 128 MB)
+  size_t nvls_round_bytes = (size_t)-1;     // staged switch kernels (built-in 64 MB)
+  size_t ag_pull_round_bytes = (size_t)-1;  // all_gather pull mode (built-in 32 MB)
+  size_t ag_nvls_max_bytes = 128u << 20;    // all_gather outputs from this size use the pull mode even when the switch is enabled
   size_t symm_min_bytes = (size_t)-1;  // -1: built-in (512 KB; 16 MB for two ranks)
 };
 
@@ -170,6 +175,7 @@ class CudaComm {
 
   uint64_t launches() const { return launches_; }
   // Whether the last reduce_scatter / all_gather went through the multicast object.
+  void apply_builtin_thresholds();   // resolves the -1 knobs from the world size (measured tables)
   bool last_used_nvls() const { return last_algo_ == Algo::kNvls; }
 
  private:

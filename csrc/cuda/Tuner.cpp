@@ -8,7 +8,7 @@ namespace ccl {
 
 namespace {
 
-const char* const kKeys[] = {"oneshot_max_bytes", "ag_push_max_bytes", "max_blocks", "threads", "nvls_min_bytes", "symm_min_bytes", "round_bytes"};
+const char* const kKeys[] = {"oneshot_max_bytes", "ag_push_max_bytes", "max_blocks", "threads", "nvls_min_bytes", "symm_min_bytes", "round_bytes", "nvls_round_bytes", "ag_pull_round_bytes", "ag_nvls_max_bytes"};
 
 bool known_key(const std::string& k) {
   for (const char* s : kKeys)
@@ -85,6 +85,9 @@ bool apply_tuning(const std::map<int, TuneEntry>& table, int world, CommConfig* 
     else if (kv.first == "nvls_min_bytes") cfg->nvls_min_bytes = (size_t)kv.second;
     else if (kv.first == "symm_min_bytes") cfg->symm_min_bytes = (size_t)kv.second;
     else if (kv.first == "round_bytes") cfg->round_bytes = (size_t)kv.second;
+    else if (kv.first == "nvls_round_bytes") cfg->nvls_round_bytes = (size_t)kv.second;
+    else if (kv.first == "ag_pull_round_bytes") cfg->ag_pull_round_bytes = (size_t)kv.second;
+    else if (kv.first == "ag_nvls_max_bytes") cfg->ag_nvls_max_bytes = (size_t)kv.second;
   }
   return true;
 }

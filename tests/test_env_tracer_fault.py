@@ -1,6 +1,7 @@
 """Environment knobs, the verbose tracer's line format, statistics / flight recorder, and
 host-side failure detection (a rank that never joins a collective; a rank that leaves between
-steps). No GPU is faulted or hung anywhere: failures are made on the host, on CPU ranks."""
+steps). No GPU is faulted or hung anywhere: failures are made on the host (CPU ranks; on GPUs a rank that
+does not join one collective, which its peer's kernel answers with a bounded wait and a status word)."""
 import os
 import re
 import subprocess
@@ -93,6 +94,46 @@ def _missing_rank(rank, world):
 
 def test_rank_that_never_joins_times_out_on_peers():
     run_ranks(_missing_rank, world=2, env={"CCL_TEST_TIMEOUT_S": "1.5", "CCL_TEST_NO_DESTROY": "1"})
+
+
+def _watchdog_deadline_cuda(rank, world):
+    """Rank 1 does not join one all_reduce. Rank 0's kernel waits for it with a budget of 12 s (set far above the
+    group's timeout of 1.5 s on purpose), so only the watchdog's own deadline can end the work early: it raises the
+    communicator's abort word, the kernel's wait samples it and returns with status 'aborted', the context stays
+    usable. Rank 1 leaves after rank 0 has seen the failure, with no kernel of its own in flight."""
+    import datetime
+
+    t = torch.ones(1 << 16, device="cuda")
+    dist.all_reduce(t)
+    torch.cuda.synchronize()
+    store = dist.distributed_c10d._get_default_store()
+    if rank != 0:
+        store.wait(["watchdog_seen"], datetime.timedelta(seconds=60))
+        return
+    t0 = time.time()
+    try:
+        w = dist.all_reduce(t, async_op=True)
+        while not w.is_completed() and time.time() - t0 < 40:
+            time.sleep(0.05)
+        dt = time.time() - t0
+        time.sleep(0.5)  # the watchdog retires the work right after the event fires
+        with pytest.raises(dist.DistBackendError, match="abort"):
+            w.wait()
+        assert 1.5 < dt < 9, dt
+        torch.cuda.synchronize()  # the context survived
+        assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0
+        with pytest.raises(dist.DistBackendError):
+            dist.all_reduce(t)  # the communicator stays failed
+    finally:
+        store.set("watchdog_seen", "1")
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_watchdog_deadline_aborts_a_work_past_its_timeout():
+    run_ranks(_watchdog_deadline_cuda, world=2, device="cuda",
+              env={"CCL_TEST_TIMEOUT_S": "1.5", "CCL_SPIN_TIMEOUT_MS": "12000", "CCL_TEST_NO_DESTROY": "1",
+                   "NCCL_NVLS_ENABLE": "0", "CCL_NVLS": "0"})
 
 
 def _leaves_between_steps(rank, world):
