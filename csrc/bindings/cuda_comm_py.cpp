@@ -529,6 +529,19 @@ void bind_cuda_comm(py::module& m) {
     }
     return out;
   });
+  m.def("builtin_thresholds", [](int world, int64_t round_mb) {
+    ccl::CommConfig cfg;
+    if (round_mb >= 0) cfg.round_bytes = (size_t)round_mb << 20;
+    ccl::resolve_builtin_thresholds(world, &cfg);
+    py::dict d;
+    d["symm_min_bytes"] = cfg.symm_min_bytes;
+    d["nvls_min_bytes"] = cfg.nvls_min_bytes;
+    d["round_bytes"] = cfg.round_bytes;
+    d["nvls_round_bytes"] = cfg.nvls_round_bytes;
+    d["ag_pull_round_bytes"] = cfg.ag_pull_round_bytes;
+    d["ag_nvls_max_bytes"] = cfg.ag_nvls_max_bytes;
+    return d;
+  }, py::arg("world"), py::arg("round_mb") = (int64_t)-1);
   m.def("emu_missing_peer_probe", [](PyComm& c) {
     return c.comm->barrier_single_rank(0, c.stream()) == cudaSuccess;
   });

@@ -1,4 +1,5 @@
 #include "cuda/CudaComm.h"
+#include "cuda/Tuner.h"
 
 #include <algorithm>
 #include <chrono>
@@ -71,22 +72,7 @@ void fill_ctx(RankCtx& c, int rank, int world, const std::vector<void*>& bases, 
 
 }  // namespace
 
-// Built-in thresholds for the knobs left at "-1", from `bench/tune.py` and `bench/sweep.py` on B200 + NVSwitch:
-//  * zero-copy path for symmetric tensors: from 512 KB at 8 ranks (16.9 vs 18.7 us), 2 MB at 4 ranks (18.2 vs 25.8 us;
-//    below it the staged one-shot kernel is 1-3 us faster), 16 MB at 2 ranks (nothing to save with one peer);
-//  * staged switch (NVLS) kernels: from 2 MB at 8 ranks (28 vs 40 us), 8 MB at 4 ranks (44.5 vs 58 us; two-shot wins at
-//    4 MB, 30 vs 34 us), never at 2 ranks (512 MB: all_reduce 1736 vs 1320 us, reduce_scatter 1045 vs 786, all_gather
-//    893 vs 510 - with one peer the switch saves no NVLink bytes);
-//  * staging rounds: 128 MB for the peer-memory kernels (512 MB bf16 at 2 / 4 ranks: all_reduce 1320 -> 1202 / 1635 ->
-//    1532 us, reduce_scatter 786 -> 731 / 927 -> 879, all_to_all 680 -> 643 / 819 -> 798; 64 MB and 32 MB are slower),
-//    64 MB for the switch kernels (4 ranks: all_reduce 1522 -> 1417 us, reduce_scatter 904 -> 844 against 128 MB rounds).
-void CudaComm::apply_builtin_thresholds() {
-  if (cfg_.symm_min_bytes == (size_t)-1) cfg_.symm_min_bytes = world_ <= 2 ? (16u << 20) : world_ <= 4 ? (2u << 20) : (512u << 10);
-  if (cfg_.nvls_min_bytes == (size_t)-1) cfg_.nvls_min_bytes = world_ <= 2 ? ((size_t)1 << 62) : world_ <= 4 ? (8u << 20) : (2u << 20);
-  if (cfg_.nvls_round_bytes == (size_t)-1) cfg_.nvls_round_bytes = cfg_.round_bytes != (size_t)-1 ? cfg_.round_bytes : (64u << 20);
-  if (cfg_.ag_pull_round_bytes == (size_t)-1) cfg_.ag_pull_round_bytes = cfg_.round_bytes != (size_t)-1 ? cfg_.round_bytes : (32u << 20);
-  if (cfg_.round_bytes == (size_t)-1) cfg_.round_bytes = 128u << 20;
-}
+void CudaComm::apply_builtin_thresholds() { resolve_builtin_thresholds(world_, &cfg_); }
 
 CudaComm::CudaComm(int rank, int world, int device, const CommConfig& cfg, KvStore kv,
                    const std::string& prefix)

@@ -92,4 +92,21 @@ bool apply_tuning(const std::map<int, TuneEntry>& table, int world, CommConfig* 
   return true;
 }
 
+// Built-in thresholds for the knobs left at "-1", from `bench/tune.py` and `bench/sweep.py` on B200 + NVSwitch:
+//  * zero-copy path for symmetric tensors: from 512 KB at 8 ranks (16.9 vs 18.7 us), 2 MB at 4 ranks (18.2 vs 25.8 us;
+//    below it the staged one-shot kernel is 1-3 us faster), 16 MB at 2 ranks (nothing to save with one peer);
+//  * staged switch (NVLS) kernels: from 2 MB at 8 ranks (28 vs 40 us), 8 MB at 4 ranks (44.5 vs 58 us; two-shot wins at
+//    4 MB, 30 vs 34 us), never at 2 ranks (512 MB: all_reduce 1736 vs 1320 us, reduce_scatter 1045 vs 786, all_gather
+//    893 vs 510 - with one peer the switch saves no NVLink bytes);
+//  * staging rounds: 128 MB for the peer-memory kernels (512 MB bf16 at 2 / 4 ranks: all_reduce 1320 -> 1202 / 1635 ->
+//    1532 us, reduce_scatter 786 -> 731 / 927 -> 879, all_to_all 680 -> 643 / 819 -> 798; 64 MB and 32 MB are slower),
+//    64 MB for the switch kernels (4 ranks: all_reduce 1522 -> 1417 us, reduce_scatter 904 -> 844 against 128 MB rounds).
+void resolve_builtin_thresholds(int world, CommConfig* cfg) {
+  if (cfg->symm_min_bytes == (size_t)-1) cfg->symm_min_bytes = world <= 2 ? (16u << 20) : world <= 4 ? (2u << 20) : (512u << 10);
+  if (cfg->nvls_min_bytes == (size_t)-1) cfg->nvls_min_bytes = world <= 2 ? ((size_t)1 << 62) : world <= 4 ? (8u << 20) : (2u << 20);
+  if (cfg->nvls_round_bytes == (size_t)-1) cfg->nvls_round_bytes = cfg->round_bytes != (size_t)-1 ? cfg->round_bytes : (64u << 20);
+  if (cfg->ag_pull_round_bytes == (size_t)-1) cfg->ag_pull_round_bytes = cfg->round_bytes != (size_t)-1 ? cfg->round_bytes : (32u << 20);
+  if (cfg->round_bytes == (size_t)-1) cfg->round_bytes = 128u << 20;
+}
+
 }  // namespace ccl

@@ -27,4 +27,7 @@ std::map<int, TuneEntry> parse_tune_file(const std::string& path);
 // Applies the line for `world` (if any) to `cfg`; returns true when a line matched.
 bool apply_tuning(const std::map<int, TuneEntry>& table, int world, CommConfig* cfg);
 
+// Replaces every threshold of `cfg` that is still at its "-1 = built-in" value by the measured default for `world` ranks.
+void resolve_builtin_thresholds(int world, CommConfig* cfg);
+
 }  // namespace ccl

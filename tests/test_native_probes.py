@@ -63,6 +63,30 @@ def test_probe_runs(mode):
     assert r.returncode == 0 and "PASS" in r.stdout, r.stdout + r.stderr
 
 
+PEER_BW = os.path.join(HERE, "peer_bw")
+
+
+def _build_peer_bw():
+    src = os.path.join(HERE, "peer_bw.cu")
+    if os.path.exists(PEER_BW) and os.path.getmtime(PEER_BW) >= os.path.getmtime(src):
+        return
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O2", "-lineinfo", "-o", PEER_BW, src], check=True)
+
+
+def test_peer_bandwidth_probe_builds_for_sm100a():
+    _build_peer_bw()
+    assert os.access(PEER_BW, os.X_OK)
+
+
+@pytest.mark.gpu
+def test_peer_bandwidth_probe_runs():
+    """16 MB copies, 2 launches each, load-flavour table only: a few seconds. With one GPU the probe says so and exits 0."""
+    _build_peer_bw()
+    r = subprocess.run([PEER_BW, "16", "2", "quick"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and ("done" in r.stdout or "skipped" in r.stdout), r.stdout + r.stderr
+
+
 def _build_shm_stress(tag, flags):
     import torch
 

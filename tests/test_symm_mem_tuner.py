@@ -35,11 +35,32 @@ def test_tune_text_parser():
 
     t = C.parse_tune_text("# measured on 8 GPUs\n8 oneshot_max_bytes=524288 max_blocks=128  # x\n\n2 threads=256 ag_push_max_bytes=0\n")
     assert t == {8: {"oneshot_max_bytes": 524288, "max_blocks": 128}, 2: {"threads": 256, "ag_push_max_bytes": 0}}
+    t = C.parse_tune_text("4 nvls_min_bytes=8388608 symm_min_bytes=2097152 round_bytes=134217728 nvls_round_bytes=67108864 "
+                          "ag_pull_round_bytes=33554432 ag_nvls_max_bytes=134217728\n")
+    assert t[4]["nvls_round_bytes"] == 64 << 20 and t[4]["ag_pull_round_bytes"] == 32 << 20 and len(t[4]) == 6
     for bad, msg in [("8 foo=1", "unknown key"), ("9 threads=64", "world size"), ("8 threads=100", "out of range"),
                      ("8 threads", "key=value"), ("8", "no key=value"), ("8 threads=64\n8 threads=64", "twice"),
                      ("8 max_blocks=9999", "out of range"), ("x threads=64", "world size")]:
         with pytest.raises(RuntimeError, match=msg):
             C.parse_tune_text(bad)
+
+
+def test_builtin_thresholds_follow_the_measured_tables():
+    """The thresholds left to the library depend on the number of ranks: the values are the crossovers that the tuner
+    and the sweep measured at 2, 4 and 8 GPUs. An explicit round size (CCL_ROUND_MB) also sets the two special cases."""
+    import torch_ccl_b200._C as C
+
+    t2, t4, t8 = (C.builtin_thresholds(w) for w in (2, 4, 8))
+    assert t2["nvls_min_bytes"] > 1 << 50, "two ranks never pick the switch kernels by themselves"
+    assert (t4["nvls_min_bytes"], t8["nvls_min_bytes"]) == (8 << 20, 2 << 20)
+    assert (t2["symm_min_bytes"], t4["symm_min_bytes"], t8["symm_min_bytes"]) == (16 << 20, 2 << 20, 512 << 10)
+    for t in (t2, t4, t8):
+        assert (t["round_bytes"], t["nvls_round_bytes"], t["ag_pull_round_bytes"]) == (128 << 20, 64 << 20, 32 << 20)
+        assert t["ag_nvls_max_bytes"] == 128 << 20
+    e = C.builtin_thresholds(8, 16)
+    assert (e["round_bytes"], e["nvls_round_bytes"], e["ag_pull_round_bytes"]) == (16 << 20, 16 << 20, 16 << 20)
+    off = C.builtin_thresholds(4, 0)  # 0: rounds of the whole arena half
+    assert (off["round_bytes"], off["nvls_round_bytes"], off["ag_pull_round_bytes"]) == (0, 0, 0)
 
 
 def _symm(rank, world, kind):
