@@ -100,7 +100,9 @@ bool apply_tuning(const std::map<int, TuneEntry>& table, int world, CommConfig* 
 //    893 vs 510 - with one peer the switch saves no NVLink bytes);
 //  * staging rounds: 128 MB for the peer-memory kernels (512 MB bf16 at 2 / 4 ranks: all_reduce 1320 -> 1202 / 1635 ->
 //    1532 us, reduce_scatter 786 -> 731 / 927 -> 879, all_to_all 680 -> 643 / 819 -> 798; 64 MB and 32 MB are slower),
-//    64 MB for the switch kernels (4 ranks: all_reduce 1522 -> 1417 us, reduce_scatter 904 -> 844 against 128 MB rounds).
+//    64 MB for the switch kernels (4 ranks: all_reduce 1522 -> 1417 us, reduce_scatter 904 -> 844 against 128 MB rounds;
+//    8 ranks against rounds of the whole 256 MB arena half: all_reduce 1533 -> 1305 us, reduce_scatter 923 -> 835,
+//    all_gather 809 -> 783 with its outputs >= 128 MB on the pull mode in 32 MB rounds).
 void resolve_builtin_thresholds(int world, CommConfig* cfg) {
   if (cfg->symm_min_bytes == (size_t)-1) cfg->symm_min_bytes = world <= 2 ? (16u << 20) : world <= 4 ? (2u << 20) : (512u << 10);
   if (cfg->nvls_min_bytes == (size_t)-1) cfg->nvls_min_bytes = world <= 2 ? ((size_t)1 << 62) : world <= 4 ? (8u << 20) : (2u << 20);
