@@ -12,7 +12,10 @@
 //   * all_gather (pull): stage locally, signal all, wait all, read every peer's half, exit
 //     without a trailing synchronisation;
 //   * broadcast: root pushes and signals; the others copy out and acknowledge; the root waits
-//     for every acknowledgement and then RELEASES the others, who wait for that release.
+//     for every acknowledgement and then RELEASES the others, who wait for that release;
+//   * broadcast through the switch: the root stores into EVERY rank's half (its own included, as
+//     multimem.st does), then all ranks signal all and wait for all, like the unrooted kernels,
+//     and the others copy out of their own half; no acknowledgement and no release.
 //
 // The release step is what makes "a rank has left kernel k" imply "every rank has entered
 // kernel k" also for rooted kernels. Without it (run with `norelease`) this sequence corrupts
@@ -47,7 +50,7 @@ struct Rank {
   }
 };
 
-enum Op { kAllReduce, kAllGather, kBroadcast };
+enum Op { kAllReduce, kAllGather, kBroadcast, kBroadcastSwitch, kNumOps };
 struct Step {
   Op op;
   int root;
@@ -122,6 +125,20 @@ void rank_main(World* wp, int me, const std::vector<Step>* prog) {
         for (size_t i = 0; i < kSlot; ++i)
           if (w.ranks[p].half[h][i] != payload(p, (int)s, i)) w.failures.fetch_add(1);
       }
+    } else if (st.op == kBroadcastSwitch) {
+      const int root = st.root;
+      if (me == root)
+        for (int p = 0; p < W; ++p)
+          for (size_t i = 0; i < kSlot; ++i) w.ranks[p].half[h][i] = payload(root, (int)s, i);
+      for (int p = 0; p < W; ++p)
+        if (p != me) signal(w, me, p, 0, tag);
+      for (int p = 0; p < W; ++p)
+        if (p != me && !wait_flag(w, me, 0, p, tag)) return;
+      if (me != root) {
+        if (st.slow_rank == me) std::this_thread::sleep_for(std::chrono::milliseconds(30));
+        for (size_t i = 0; i < kSlot; ++i)
+          if (w.ranks[me].half[h][i] != payload(root, (int)s, i)) w.failures.fetch_add(1);
+      }
     } else {  // broadcast
       const int root = st.root;
       if (me == root) {
@@ -171,11 +188,14 @@ int main(int argc, char** argv) {
   int bad = 0;
   // the same sequence with the release step, then random programs with random slow ranks
   bad += run(3, true, {{kAllGather, 0, 2}, {kBroadcast, 1, -1}, {kBroadcast, 0, -1}}) != 0;
+  // the switch broadcast has no release step and must not need one: slow readers between broadcasts of changing roots
+  bad += run(3, true, {{kAllGather, 0, 2}, {kBroadcastSwitch, 1, 2}, {kBroadcastSwitch, 0, 1}, {kBroadcast, 2, 0}, {kBroadcastSwitch, 2, 0},
+                       {kAllReduce, 0, 1}, {kBroadcastSwitch, 1, -1}}) != 0;
   std::mt19937 rng(1234);
   for (int W : {2, 3, 5, 8}) {
     for (int trial = 0; trial < 6; ++trial) {
       std::vector<Step> prog;
-      for (int s = 0; s < 40; ++s) prog.push_back({(Op)(rng() % 3), (int)(rng() % W), (rng() % 5 == 0) ? (int)(rng() % W) : -1});
+      for (int s = 0; s < 40; ++s) prog.push_back({(Op)(rng() % kNumOps), (int)(rng() % W), (rng() % 5 == 0) ? (int)(rng() % W) : -1});
       const int rc = run(W, true, prog);
       if (rc) std::printf("world %d trial %d: rc %d\n", W, trial, rc);
       bad += rc != 0;

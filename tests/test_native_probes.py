@@ -116,8 +116,9 @@ def test_cpu_backend_under_sanitizers(tag, flags):
 
 def test_epoch_protocol_model_under_tsan():
     """Host-thread model of the flag / epoch / parity protocol: random programs of all_reduce,
-    all_gather and broadcast with slow ranks are race-free under ThreadSanitizer, and the same model
-    without the broadcast release step shows the corruption that the step prevents."""
+    all_gather, broadcast and broadcast through the switch with slow ranks are race-free under
+    ThreadSanitizer, and the same model without the broadcast release step shows the corruption
+    that the step prevents."""
     src = os.path.join(HERE, "epoch_model.cpp")
     exe = os.path.join(HERE, "epoch_model_tsan")
     if not (os.path.exists(exe) and os.path.getmtime(exe) >= os.path.getmtime(src)):
