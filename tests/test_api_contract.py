@@ -174,6 +174,39 @@ def test_ddp_and_subgroups_world4():
     run_ranks(_ddp_and_subgroups, world=4)
 
 
+def _two_virtual_nodes(rank, world):
+    """Two 'nodes' of world/2 ranks each as separate communicators on one machine, plus the cross-node groups that pair
+    equal local ranks: the hierarchical all_reduce (reduce_scatter inside the node, all_reduce across nodes, all_gather
+    inside the node) must equal the flat one. This is the communicator layout a multi-node run would use."""
+    per = world // 2
+    node = rank // per
+    local = rank % per
+    node_groups = [dist.new_group(list(range(n * per, (n + 1) * per))) for n in range(2)]
+    cross_groups = [dist.new_group([l, per + l]) for l in range(per)]
+    intra, cross = node_groups[node], cross_groups[local]
+    torch.manual_seed(7 + rank)
+    x = torch.randn(per * 300)
+    flat = x.clone()
+    dist.all_reduce(flat)
+    shard = torch.empty(300)
+    dist.reduce_scatter_tensor(shard, x.clone(), group=intra)
+    dist.all_reduce(shard, group=cross)
+    out = torch.empty(per * 300)
+    dist.all_gather_into_tensor(out, shard, group=intra)
+    torch.testing.assert_close(out, flat, rtol=1e-5, atol=1e-5)
+    # a broadcast that crosses the nodes first and fans out inside them afterwards
+    b = torch.full((64,), float(rank))
+    if local == 0:
+        dist.broadcast(b, src=0, group=cross_groups[0])
+    dist.broadcast(b, src=node * per, group=intra)
+    assert torch.all(b == 0.0)
+    dist.barrier()
+
+
+def test_two_virtual_nodes_hierarchical_collectives():
+    run_ranks(_two_virtual_nodes, world=4)
+
+
 def _p2p_patterns(rank, world):
     # relay 0 -> 1 -> 2 and all-pairs exchange with tags (accepted and ignored, like the reference)
     if rank == 0:
