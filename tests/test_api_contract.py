@@ -207,6 +207,46 @@ def test_two_virtual_nodes_hierarchical_collectives():
     run_ranks(_two_virtual_nodes, world=4)
 
 
+def _hierarchical_helper(rank, world, per):
+    from torch_ccl_b200.parallel.hierarchical import HierarchicalGroups
+
+    h = HierarchicalGroups(per)
+    assert (h.nodes, h.node, h.local) == (world // per, rank // per, rank % per)
+    torch.manual_seed(100 + rank)
+    for n in (1, 7, 1000, 4099):  # not multiples of ranks_per_node: the helper pads
+        x = torch.randn(n)
+        flat = x.clone()
+        dist.all_reduce(flat)
+        h.all_reduce(x)
+        torch.testing.assert_close(x, flat, rtol=1e-5, atol=1e-5)
+    m = torch.randn(6, 10)
+    want = m.t().contiguous()
+    dist.all_reduce(want, op=dist.ReduceOp.MAX)
+    view = m.t()  # non-contiguous
+    h.all_reduce(view, op=dist.ReduceOp.MAX)
+    assert torch.equal(view, want)
+    for src in range(world):
+        b = torch.full((33,), float(rank))
+        h.broadcast(b, src)
+        assert torch.all(b == float(src)), (src, b[0])
+    piece = torch.arange(5.0) + 10 * rank
+    got = torch.empty(5 * world)
+    h.all_gather_into_tensor(got, piece)
+    assert torch.equal(got, torch.cat([torch.arange(5.0) + 10 * r for r in range(world)]))
+    full = torch.randn(world * 12)
+    ref = full.clone()
+    dist.all_reduce(ref)
+    out = torch.empty(12)
+    h.reduce_scatter_tensor(out, full)
+    torch.testing.assert_close(out, ref[rank * 12:(rank + 1) * 12], rtol=1e-5, atol=1e-5)
+    dist.barrier()
+
+
+@pytest.mark.parametrize("per", [1, 2, 4])
+def test_hierarchical_groups_match_flat_collectives(per):
+    run_ranks(_hierarchical_helper, world=4, args=(per,))
+
+
 def _p2p_patterns(rank, world):
     # relay 0 -> 1 -> 2 and all-pairs exchange with tags (accepted and ignored, like the reference)
     if rank == 0:
