@@ -15,7 +15,19 @@
 //     for every acknowledgement and then RELEASES the others, who wait for that release;
 //   * broadcast through the switch: the root stores into EVERY rank's half (its own included, as
 //     multimem.st does), then all ranks signal all and wait for all, like the unrooted kernels,
-//     and the others copy out of their own half; no acknowledgement and no release.
+//     and the others copy out of their own half; no acknowledgement and no release;
+//   * low-latency exchange (the fused decode kernels, ll_norm.cuh): every 8-byte unit carries
+//     {payload, flag of the round}; a rank stores its units into slot [parity][own rank] of EVERY
+//     rank (itself included) and then polls the units of all sources until they carry the flag.
+//     No separate flag, no trailing synchronisation: a slot of parity p is rewritten two launches
+//     later, which its writer can only reach after the launch in between, whose gather needed a
+//     unit from every rank, i.e. after every rank has finished reading the older round. A unit
+//     that was overwritten too early would carry a newer flag and the poll would time out.
+//     On the device these stores and loads are plain / volatile; what orders them against the
+//     NEIGHBOURING kernels is the kernel boundary (a kernel's peer accesses start after
+//     griddepcontrol.wait, i.e. after the previous kernel of the stream has completed and flushed).
+//     The model has no kernel boundaries, so it gives the unit store release and the unit load
+//     acquire semantics to stand for them.
 //
 // The release step is what makes "a rank has left kernel k" imply "every rank has entered
 // kernel k" also for rooted kernels. Without it (run with `norelease`) this sequence corrupts
@@ -39,18 +51,22 @@ namespace {
 constexpr int kPhases = 3;
 constexpr int kMaxW = 8;
 constexpr size_t kSlot = 256;  // words per rank slot inside a half
+constexpr size_t kLL = 64;     // 8-byte units per source in a low-latency slot
 
 struct Rank {
   std::vector<uint32_t> half[2];
   std::atomic<uint32_t> flags[kPhases][kMaxW];
-  Rank() {
+  std::vector<std::atomic<uint64_t>> ll[2];  // [parity][source * kLL + unit] = payload | flag << 32
+  Rank() : ll{std::vector<std::atomic<uint64_t>>(kLL * kMaxW), std::vector<std::atomic<uint64_t>>(kLL * kMaxW)} {
+    for (auto& v : ll)
+      for (auto& u : v) u.store(0);
     for (auto& h : half) h.assign(kSlot * kMaxW, 0);
     for (auto& p : flags)
       for (auto& f : p) f.store(0);
   }
 };
 
-enum Op { kAllReduce, kAllGather, kBroadcast, kBroadcastSwitch, kNumOps };
+enum Op { kAllReduce, kAllGather, kBroadcast, kBroadcastSwitch, kLowLatency, kNumOps };
 struct Step {
   Op op;
   int root;
@@ -125,6 +141,25 @@ void rank_main(World* wp, int me, const std::vector<Step>* prog) {
         for (size_t i = 0; i < kSlot; ++i)
           if (w.ranks[p].half[h][i] != payload(p, (int)s, i)) w.failures.fetch_add(1);
       }
+    } else if (st.op == kLowLatency) {
+      for (int p = 0; p < W; ++p)
+        for (size_t i = 0; i < kLL; ++i)
+          w.ranks[p].ll[h][me * kLL + i].store((uint64_t)payload(me, (int)s, i) | ((uint64_t)tag << 32), std::memory_order_release);
+      const auto t0 = std::chrono::steady_clock::now();
+      for (int p = 0; p < W; ++p) {
+        if (st.slow_rank == me && p == W / 2) std::this_thread::sleep_for(std::chrono::milliseconds(30));
+        for (size_t i = 0; i < kLL; ++i) {
+          uint64_t u;
+          while (((u = w.ranks[me].ll[h][p * kLL + i].load(std::memory_order_acquire)) >> 32) != tag) {
+            if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(20)) {
+              w.timeouts.fetch_add(1);
+              return;
+            }
+            std::this_thread::yield();
+          }
+          if ((uint32_t)u != payload(p, (int)s, i)) w.failures.fetch_add(1);
+        }
+      }
     } else if (st.op == kBroadcastSwitch) {
       const int root = st.root;
       if (me == root)
@@ -191,6 +226,9 @@ int main(int argc, char** argv) {
   // the switch broadcast has no release step and must not need one: slow readers between broadcasts of changing roots
   bad += run(3, true, {{kAllGather, 0, 2}, {kBroadcastSwitch, 1, 2}, {kBroadcastSwitch, 0, 1}, {kBroadcast, 2, 0}, {kBroadcastSwitch, 2, 0},
                        {kAllReduce, 0, 1}, {kBroadcastSwitch, 1, -1}}) != 0;
+  // low-latency exchanges back to back (decode: two per layer) with slow readers, then mixed with the staged kernels
+  bad += run(4, true, {{kLowLatency, 0, 1}, {kLowLatency, 0, 2}, {kLowLatency, 0, 1}, {kLowLatency, 0, 3}, {kAllGather, 0, 0},
+                       {kLowLatency, 0, 2}, {kBroadcastSwitch, 3, 1}, {kLowLatency, 0, 0}, {kLowLatency, 0, 3}}) != 0;
   std::mt19937 rng(1234);
   for (int W : {2, 3, 5, 8}) {
     for (int trial = 0; trial < 6; ++trial) {
