@@ -404,7 +404,16 @@ at::Tensor ProcessGroupCCL::allocateTensor(long size, at::TensorOptions options)
   TORCH_CHECK(size >= 0, "allocateTensor: negative size");
   const at::Device dev = options.has_device() && options.device().is_cuda() && options.device().has_index()
                              ? options.device() : at::Device(at::kCUDA, c10::cuda::current_device());
-  return cudaImpl(dev).symm_empty(size, options);
+  at::Tensor t = cudaImpl(dev).symm_empty(size, options);
+  // Symmetric allocation is collective in order: a rank that allocates in another order would address other memory
+  // of its peers than they do. With CCL_DEBUG_CHECKS=1 the ranks compare {heap offset, bytes} of every allocation.
+  if (Env::get().debug_checks && size_ > 1) {
+    size_t off = 0;
+    cudaImpl(dev).comm_ptr(dev)->symm_offset(t.data_ptr(), t.nbytes(), &off);
+    const std::string what = "symm_alloc[heap offset " + std::to_string(off) + ", " + std::to_string(t.nbytes()) + " bytes]";
+    debugConsistencyCheck(what.c_str(), t.scalar_type(), 0);
+  }
+  return t;
 }
 
 namespace {
