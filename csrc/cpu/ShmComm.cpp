@@ -92,10 +92,15 @@ ShmComm::ShmComm(ShmStore store, int rank, int world, size_t slot_bytes, std::ch
   // everyone has mapped the segment -> the name can disappear (no stale segment after a crash)
   store.add("shm/mapped", 1);
   const auto t0 = std::chrono::steady_clock::now();
-  while (store.add("shm/mapped", 0) < world_) {
+  int64_t mapped = 0;
+  while ((mapped = store.add("shm/mapped", 0)) < world_) {
     if (std::chrono::steady_clock::now() - t0 > init_timeout) {
       if (rank_ == 0) shm_unlink(name_.c_str());
-      throw ShmTimeout("ccl: timeout while waiting for all ranks to map the shared-memory segment");
+      munmap(base_, total_bytes_);  // the destructor does not run for an object whose constructor throws
+      base_ = nullptr;
+      throw ShmTimeout("ccl: communicator bring-up timed out after " + std::to_string(init_timeout.count()) + " ms on rank " +
+                       std::to_string(rank_) + ": " + std::to_string(mapped) + " of " + std::to_string(world_) +
+                       " ranks mapped the shared-memory segment (does every rank of the group run and reach its first CPU collective?)");
     }
     std::this_thread::sleep_for(std::chrono::milliseconds(1));
   }

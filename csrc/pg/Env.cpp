@@ -61,6 +61,7 @@ Env parse() {
   e.symm_min_bytes = parse_env_int("CCL_SYMM_MIN_BYTES", -1);
   e.nvls_min_bytes = parse_env_int("CCL_NVLS_MIN_BYTES", -1);
   e.round_mb = parse_env_int("CCL_ROUND_MB", -1);
+  e.init_timeout_ms = parse_env_int("CCL_INIT_TIMEOUT_MS", -1);
   e.shm_slot_mb = parse_env_int("CCL_SHM_SLOT_MB", 4);
   e.max_blocks = (int)parse_env_int("CCL_MAX_BLOCKS", -1);
   e.threads = (int)parse_env_int("CCL_THREADS", -1);

@@ -35,6 +35,7 @@ struct Env {
   int64_t arena_mb = 256;      // CCL_ARENA_MB: one staging half per rank
   int64_t symm_heap_mb = 1024; // CCL_SYMM_HEAP_MB: symmetric heap for tensors allocated through the backend (created on first use)
   int64_t symm_min_bytes = -1; // CCL_SYMM_MIN_BYTES: smallest symmetric message that takes the zero-copy kernels (-1: built-in / tuning file)
+  int64_t init_timeout_ms = -1; // CCL_INIT_TIMEOUT_MS: how long a rank waits for the others when the CPU communicator is built (-1: max(group timeout, 30 s))
   int64_t round_mb = -1;       // CCL_ROUND_MB: cap on the megabytes one staging round moves per rank (-1: built-in, 0: the arena half)
   int64_t nvls_min_bytes = -1; // CCL_NVLS_MIN_BYTES: smallest staged message that goes through the switch when CCL_NVLS=1 (-1: built-in / tuning file)
   int64_t shm_slot_mb = 4;     // CCL_SHM_SLOT_MB: CPU shared-memory slot per rank

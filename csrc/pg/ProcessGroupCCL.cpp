@@ -234,8 +234,15 @@ ccl::cpu::ShmComm& ProcessGroupCCL::shm() {
     s.set = [store](const std::string& k, const std::vector<uint8_t>& v) { store->set("ccl/" + k, v); };
     s.get = [store](const std::string& k) { return store->get("ccl/" + k); };
     s.add = [store](const std::string& k, int64_t v) { return store->add("ccl/" + k, v); };
-    shm_ = std::make_unique<ccl::cpu::ShmComm>(s, rank_, size_, (size_t)Env::get().shm_slot_mb << 20,
-                                               std::max(timeout_, std::chrono::milliseconds(30000)));
+    // ranks reach their first CPU collective at different times (imports, data loading): never less than 30 s
+    try {
+      const int64_t init_ms = Env::get().init_timeout_ms;
+      shm_ = std::make_unique<ccl::cpu::ShmComm>(s, rank_, size_, (size_t)Env::get().shm_slot_mb << 20,
+                                                 init_ms >= 0 ? std::chrono::milliseconds(init_ms)
+                                                              : std::max(timeout_, std::chrono::milliseconds(30000)));
+    } catch (const ccl::cpu::ShmTimeout& e) {
+      C10_THROW_ERROR(DistBackendError, e.what());
+    }
     cpu_worker_ = std::make_unique<ccl::TaskThread>();
   }
   return *shm_;

@@ -96,6 +96,30 @@ def test_rank_that_never_joins_times_out_on_peers():
     run_ranks(_missing_rank, world=2, env={"CCL_TEST_TIMEOUT_S": "1.5", "CCL_TEST_NO_DESTROY": "1"})
 
 
+def test_bring_up_without_the_peer_fails_with_a_named_count():
+    """Bootstrap failure made on the host: rank 0 of a two-rank group runs alone (its peer never starts). The first CPU
+    collective builds the communicator, waits CCL_INIT_TIMEOUT_MS for the other rank and fails with a DistBackendError that
+    says how many ranks showed up; nothing hangs."""
+    code = (
+        "import datetime, os, sys, tempfile, time\n"
+        "import torch, torch.distributed as dist\n"
+        "import oneccl_bindings_for_pytorch\n"
+        "store = dist.FileStore(os.path.join(tempfile.mkdtemp(), 's'), 2)\n"
+        "dist.init_process_group('ccl', store=store, rank=0, world_size=2, timeout=datetime.timedelta(seconds=2))\n"
+        "t0 = time.time()\n"
+        "try:\n"
+        "    dist.all_reduce(torch.ones(4))\n"
+        "    print('NO ERROR')\n"
+        "except dist.DistBackendError as e:\n"
+        "    print('RAISED %.1f %s' % (time.time() - t0, e))\n"
+        "os._exit(0)\n"
+    )
+    r = _run_py(code, env={"CCL_INIT_TIMEOUT_MS": "1500"})
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "RAISED" in r.stdout and "1 of 2 ranks" in r.stdout, r.stdout + r.stderr[-2000:]
+    assert float(r.stdout.split("RAISED ")[1].split()[0]) < 10
+
+
 def _watchdog_deadline_cuda(rank, world):
     """Rank 1 does not join one all_reduce. Rank 0's kernel waits for it with a budget of 12 s (set far above the
     group's timeout of 3 s on purpose), so only the watchdog's own deadline can end the work early: it raises the
