@@ -47,6 +47,11 @@ def test_meta_kernels_give_shapes(one_rank_group):
     assert rows.shape == (64, 256) and meta.shape == (64, 3) and count.dtype == torch.int32
     gate = torch.empty(32, 2, device="meta")
     assert torch.ops.ccl.moe_combine(rows, meta, count, gate, g).shape == (32, 256)
+    # the two in-place ops return nothing and accept meta tensors
+    assert torch.ops.ccl.all_reduce_scaled(torch.empty(1000, **m), 0.125, g) is None
+    assert torch.ops.ccl.all_gather_copy_out(torch.empty(64, **m), [torch.empty(64, **m)], g) is None
+    with pytest.raises(RuntimeError, match="one destination per rank"):
+        torch.ops.ccl.all_gather_copy_out(torch.empty(64, **m), [torch.empty(40, **m), torch.empty(24, **m)], g)
     with pytest.raises(RuntimeError, match="shape mismatch"):
         torch.ops.ccl.allreduce_residual_rmsnorm(x, torch.empty(8, 4096, **m), w, 1e-5, g)
 
