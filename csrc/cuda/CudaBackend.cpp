@@ -66,7 +66,7 @@ std::string status_message(CudaComm& c) {
   if (code == 0) return "";
   if (code == kStatusAborted)
     return "ccl: collective aborted: rank " + std::to_string(r) + " gave up waiting for rank " + std::to_string(p) +
-           " because abort() was called on the process group";
+           " because the communicator was aborted (abort() on the process group, or its watchdog after the group's timeout)";
   return "ccl: device-side wait expired (code " + std::to_string(code) + "): rank " + std::to_string(r) +
          " waited for rank " + std::to_string(p) + " in phase " + std::to_string(ph) +
          "; the communicator is unusable, destroy the process group";
