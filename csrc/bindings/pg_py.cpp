@@ -121,6 +121,7 @@ void bind_process_group(py::module& m) {
       .def("is_symmetric", [](ProcessGroupCCL& pg, const at::Tensor& t) {
         return t.is_cuda() && cuda_comm_of(pg, t).symm_offset(t.data_ptr(), t.nbytes(), nullptr);
       })
+      .def("wait_for_pending_works", &ProcessGroupCCL::waitForPendingWorks, py::call_guard<py::gil_scoped_release>())
       .def("symm_heap_info", [](ProcessGroupCCL& pg, const at::Tensor& like) {
         auto& c = cuda_comm_of(pg, like);
         py::dict d;

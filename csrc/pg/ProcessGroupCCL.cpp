@@ -1,5 +1,6 @@
 #include "pg/ProcessGroupCCL.hpp"
 
+#include <future>
 #include <ATen/record_function.h>
 #include <c10/util/Exception.h>
 #include <torch/csrc/distributed/c10d/Utils.hpp>
@@ -256,6 +257,26 @@ ccl::CudaBackendImpl& ProcessGroupCCL::cudaImpl(const at::Device& device) {
 
 void ProcessGroupCCL::eagerConnectSingleDevice(at::Device device) {
   if (device.is_cuda()) (void)cudaImpl(device).comm(device);
+}
+
+void ProcessGroupCCL::waitForPendingWorks() {
+  // The host workers are FIFO: a marker task that has run means everything posted before it has run.
+  std::vector<ccl::TaskThread*> workers;
+  {
+    std::lock_guard<std::mutex> g(init_mu_);
+    if (cpu_worker_) workers.push_back(cpu_worker_.get());
+    for (auto& kv : p2p_send_workers_) workers.push_back(kv.second.get());
+    for (auto& kv : p2p_recv_workers_) workers.push_back(kv.second.get());
+  }
+  std::vector<std::future<void>> done;
+  for (ccl::TaskThread* w : workers) {
+    auto marker = std::make_shared<std::promise<void>>();
+    done.push_back(marker->get_future());
+    w->post([marker] { marker->set_value(); });
+  }
+  for (auto& f : done) f.wait();
+  // CUDA works are retired by the process-wide watchdog, in issue order
+  if (cuda_) ccl::Watchdog::get().drain();
 }
 
 void ProcessGroupCCL::abort() {

@@ -128,6 +128,7 @@ class ProcessGroupCCL : public Backend {
   void setSequenceNumberForGroup() override {}
   uint64_t getSequenceNumberForGroup() override { return seq_.load(); }
   void enableCollectivesTiming() override { timing_enabled_ = true; }
+  void waitForPendingWorks() override;   // returns when every Work issued so far has been completed (or failed)
   void eagerConnectSingleDevice(at::Device device) override;
   void abort() override;
   void shutdown() override;

@@ -189,3 +189,33 @@ def _edge_cases(rank, world):
 
 def test_edge_cases_world3():
     run_ranks(_edge_cases, world=3)
+
+
+def _pending_works(rank, world):
+    """waitForPendingWorks: after it returns, every Work issued before it is complete (collectives on the FIFO worker,
+    sends and receives on their per-peer workers), without waiting on the Works one by one."""
+    works, tensors = [], []
+    for i in range(40):
+        t = torch.full((4096,), float(rank + i))
+        tensors.append(t)
+        works.append(dist.all_reduce(t, async_op=True))
+    peer = (rank + 1) % world
+    if rank % 2 == 0:
+        works.append(dist.isend(torch.arange(1000.0), peer))
+    else:
+        r = torch.empty(1000)
+        tensors.append(r)
+        works.append(dist.irecv(r, (rank - 1) % world))
+    dist.group.WORLD._wait_for_pending_works()
+    assert all(w.is_completed() for w in works)
+    for i in range(40):
+        assert torch.all(tensors[i] == float(sum(r + i for r in range(world))))
+    if rank % 2 == 1:
+        assert torch.equal(tensors[-1], torch.arange(1000.0))
+    be = dist.group.WORLD._get_backend(torch.device("cpu"))
+    be.wait_for_pending_works()  # nothing pending: returns at once
+    dist.barrier()
+
+
+def test_wait_for_pending_works_world2():
+    run_ranks(_pending_works, world=2)
